@@ -1,0 +1,194 @@
+/*
+ * wr_cuda.h — C-ABI of the B200 (sm_100a) attention hot path for wayruntime.
+ *
+ * This is the seam the reference's C11 host code (src/core/session.c,
+ * src/core/batch.c) calls in place of its CPU ops:
+ *
+ *   wr_cuda_kv_append     <- wri_op_rope on Q and K + kv_append_row on K and V
+ *                            (src/core/session.c:471-487, kernels.c:1356,
+ *                             session.c:139)
+ *   wr_cuda_attn_decode   <- wri_op_gqa_attention with seq_q = 1, once per
+ *                            session (src/core/session.c:490-496,
+ *                             kernels.c:1414; batched: batch.c:152-164)
+ *   wr_cuda_attn_prefill  <- the wri_session_prefill loop of single-token
+ *                            attention calls (src/core/session.c:599-630)
+ *
+ * Plain pointers and sizes only.  Every function returns a wr_status value
+ * (include/wayruntime/wayruntime.h:82-107): 0 or a negative code; nothing
+ * aborts, prints or falls back to the CPU.  There is no CPU path: without an
+ * sm_100 device every entry point fails with WR_CUDA_ERR_UNSUPPORTED.
+ *
+ * Threading: a context serialises its own calls with a mutex, so distinct
+ * sessions may be driven from distinct threads (wayruntime.h:29-40).
+ */
+#ifndef WR_CUDA_H
+#define WR_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* wr_status values used here (wayruntime.h:82-107). */
+#define WR_CUDA_OK               0
+#define WR_CUDA_ERR_UNSUPPORTED (-3)
+#define WR_CUDA_ERR_INVAL       (-4)
+#define WR_CUDA_ERR_NOMEM       (-5)
+#define WR_CUDA_ERR_CTX_FULL    (-6)
+#define WR_CUDA_ERR_STATE       (-7)
+#define WR_CUDA_ERR_LIMIT       (-8)
+#define WR_CUDA_ERR_INTERNAL    (-10)
+
+/* Where the caller's Q / K / V / output buffers live. */
+#define WR_CUDA_MEM_HOST   0   /* host memory; the call copies and synchronises */
+#define WR_CUDA_MEM_DEVICE 1   /* device memory; the call only enqueues */
+
+/* Element types (values of wr_dtype, src/core/internal.h:53-55). */
+#define WR_CUDA_F32 0
+#define WR_CUDA_F16 1
+
+/* wr_cuda_kv_append flags. */
+#define WR_CUDA_APPEND_ROPE 1u  /* rotate K (and Q when given) before storing */
+
+#define WR_CUDA_BATCH_MAX        16    /* WR_BATCH_MAX, wayruntime.h:423 */
+#define WR_CUDA_ATTN_MAX_SEQ     4096  /* default cap, WR_ATTN_MAX_SEQ (internal.h:186) */
+#define WR_CUDA_ATTN_MAX_SEQ_TOP 1048576
+#define WR_CUDA_HEAD_DIM_MAX     1024  /* WR_FLASH_D_MAX (internal.h:197) */
+#define WR_CUDA_PAGE_TOKENS      64    /* tokens per KV page = WR_FLASH_BLOCK */
+#define WR_CUDA_TRIPLE_PAD       4     /* floats before o[] in a split-KV triple */
+
+typedef struct wr_cuda_ctx wr_cuda_ctx;  /* one device, one stream, one page pool */
+typedef struct wr_cuda_kv  wr_cuda_kv;   /* one session's paged F16 K/V cache   */
+
+/* ---- device / context -------------------------------------------------- */
+
+/* WR_CUDA_OK when `device` exists and is compute capability 10.x.  This is
+ * the check wr_engine_create makes beside its endian probe
+ * (src/core/engine.c:130): no B200 bound -> WR_ERR_UNSUPPORTED. */
+int wr_cuda_device_check(int device);
+
+int  wr_cuda_ctx_create(int device, wr_cuda_ctx **out);
+void wr_cuda_ctx_destroy(wr_cuda_ctx *ctx);
+
+/* Wait for everything enqueued on the context's stream.  Also reports (and
+ * clears) a device-side error flag: a bounded wait that gave up inside a
+ * kernel surfaces here as WR_CUDA_ERR_INTERNAL. */
+int  wr_cuda_ctx_sync(wr_cuda_ctx *ctx);
+
+/* The context's cudaStream_t, for callers that time or order against it. */
+void *wr_cuda_ctx_stream(wr_cuda_ctx *ctx);
+
+/* Sequence cap for sessions and attention calls on this context; the
+ * reference's WR_ATTN_MAX_SEQ is a compile-time constant (internal.h:186),
+ * here it is a setting so long-context shards need no rebuild. */
+int  wr_cuda_ctx_set_attn_max_seq(wr_cuda_ctx *ctx, uint32_t max_seq);
+
+/* Number of kernels this library has launched on the context so far. */
+uint64_t wr_cuda_ctx_launch_count(wr_cuda_ctx *ctx);
+
+/* ---- KV cache (session_build / wr_session_create, session.c:640-814) ---- */
+
+/* All pages of the session are taken from the context's pool here, once:
+ * no allocation happens during decode.  max_ctx above the context's cap is
+ * WR_CUDA_ERR_LIMIT (session.c:755). */
+int  wr_cuda_kv_create(wr_cuda_ctx *ctx, uint32_t n_layers, uint32_t n_kv_heads,
+                       uint32_t head_dim, uint32_t max_ctx, wr_cuda_kv **out);
+void wr_cuda_kv_destroy(wr_cuda_kv *kv);
+uint32_t wr_cuda_kv_max_ctx(const wr_cuda_kv *kv);
+
+/* Copy rows [row0, row0+n) of one layer's K (which=0) or V (which=1) between
+ * the paged cache and a [n, n_kv_heads, head_dim] F16 buffer in the
+ * reference's row layout (session.c:647-674).  Used to load a prepared cache
+ * and to compare cache bytes with the reference's. */
+int wr_cuda_kv_write_rows(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t layer,
+                          int which, uint32_t row0, uint32_t n,
+                          const uint16_t *src, int mem);
+int wr_cuda_kv_read_rows(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t layer,
+                         int which, uint32_t row0, uint32_t n, uint16_t *dst,
+                         int mem);
+
+/* ---- the hot path -------------------------------------------------------- */
+
+/* Fused RoPE + KV append for one layer.  Session s contributes n_tokens
+ * consecutive rows at cache rows positions[s] .. positions[s]+n_tokens-1
+ * (its absolute positions).  k_rows, v_rows: F32 [n_sess*n_tokens,
+ * n_kv_heads, head_dim].  With WR_CUDA_APPEND_ROPE, K is rotated with the
+ * reference's RoPE (kernels.c:1356-1412: its polynomial sin/cos, pairing j
+ * with j+head_dim/2, n_rot_pairs as there) and q_rows — F32
+ * [n_sess*n_tokens, n_q_heads, head_dim], may be NULL — is rotated in place.
+ * K and V are stored with the reference's truncating F32->F16
+ * (quant.c:121-136), so cache bytes equal the reference's.
+ * The call does not move any committed length: the host passes seq_lens to
+ * the attention calls and simply does not advance them when a step fails
+ * (wri_session_kv_rollback, session.c:160).  A row past max_ctx is
+ * WR_CUDA_ERR_CTX_FULL before anything is launched (session.c:144). */
+int wr_cuda_kv_append(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv,
+                      uint32_t layer, const uint32_t *positions,
+                      uint32_t n_tokens, const float *k_rows,
+                      const float *v_rows, float *q_rows, uint32_t n_q_heads,
+                      float theta_base, uint32_t n_rot_pairs, uint32_t flags,
+                      int mem);
+
+/* Decode attention, all sessions in one grid.  q, out: F32 [n_sess,
+ * n_q_heads, head_dim] (q already rotated, e.g. by wr_cuda_kv_append).
+ * seq_lens[s] = rows of session s to attend (the row just appended
+ * included).  scale_override <= 0 selects 1/sqrt(head_dim); window > 0
+ * keeps the last `window` keys (kernels.c:1456-1464).  Validation follows
+ * kernels.c:1418-1454.  A session's result does not depend on which other
+ * sessions share the call. */
+int wr_cuda_attn_decode(wr_cuda_ctx *ctx, uint32_t n_sess,
+                        wr_cuda_kv *const *kv, uint32_t layer,
+                        const uint32_t *seq_lens, const float *q, float *out,
+                        uint32_t n_q_heads, float scale_override,
+                        uint32_t window, int mem);
+
+/* The batched decode layer-step in one call: wr_cuda_kv_append with
+ * n_tokens = 1 followed by wr_cuda_attn_decode over seq_lens[s] =
+ * positions[s] + 1 — the per-layer body of wri_batch_decode_step
+ * (src/core/batch.c:152-164 -> session.c:471-496) for all sessions at once.
+ * q: F32 [n_sess, n_q_heads, head_dim], un-rotated on entry (rotated in
+ * place when it is device memory); out: F32 of the same shape.  With host
+ * buffers q, k_rows and v_rows cross the bus once and only out comes back. */
+int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv,
+                        uint32_t layer, const uint32_t *positions, float *q,
+                        const float *k_rows, const float *v_rows, float *out,
+                        uint32_t n_q_heads, float theta_base, uint32_t n_rot_pairs,
+                        uint32_t flags, float scale_override, uint32_t window,
+                        int mem);
+
+/* Causal prefill attention for n new tokens of one session whose rows
+ * [0, p0+n) are already in the cache: query i attends rows [0, p0+i]
+ * (row i of the reference's prefill loop, session.c:599-630).
+ * q: [n, n_q_heads, head_dim] of q_dtype; out: F32 of the same shape. */
+int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t layer,
+                         uint32_t p0, uint32_t n, const void *q, int q_dtype,
+                         float *out, uint32_t n_q_heads, float scale_override,
+                         uint32_t window, int mem);
+
+/* ---- split-KV across devices --------------------------------------------- */
+
+/* Like wr_cuda_attn_decode over this device's shard of each session's keys,
+ * but emits one triple per (session, q head) instead of the normalised row:
+ * triples is F32 [n_sess, n_q_heads, WR_CUDA_TRIPLE_PAD + head_dim] holding
+ * (m, l, 0, 0, o[head_dim]) with m the running max (natural-log domain,
+ * -1e30 for an empty shard), l the denominator and o the unnormalised
+ * accumulator — the state of kernels.c:1480-1516 after the shard's keys.
+ * seq_lens[s] may be 0 (empty shard). */
+int wr_cuda_attn_decode_partial(wr_cuda_ctx *ctx, uint32_t n_sess,
+                                wr_cuda_kv *const *kv, uint32_t layer,
+                                const uint32_t *seq_lens, const float *q,
+                                float *triples, uint32_t n_q_heads,
+                                float scale_override, int mem);
+
+/* Merge n_shards triples per row with the online-softmax rule
+ * (kernels.c:1503-1506 applied across shards): triples is F32 [n_shards,
+ * n_rows, WR_CUDA_TRIPLE_PAD + head_dim], out F32 [n_rows, head_dim]. */
+int wr_cuda_attn_combine(wr_cuda_ctx *ctx, uint32_t n_shards, uint32_t n_rows,
+                         uint32_t head_dim, const float *triples, float *out,
+                         int mem);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

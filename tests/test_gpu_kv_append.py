@@ -1,0 +1,152 @@
+"""GPU parity: fused RoPE + KV append (wr_cuda_kv_append) against the oracle.
+
+Bar: BIT-EXACT.  Cache bytes must equal kv_append_row(wri_op_rope(x))
+(src/core/session.c:139-154, src/core/kernels.c:1356-1412) and the rotated Q
+must equal wri_op_rope(q) bit for bit.
+"""
+import numpy as np
+import pytest
+
+import _gen
+from _cuda_util import port
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import wayruntime_b200 as wr
+    c = wr.Context(0, attn_max_seq=32768)
+    yield c
+    c.close()
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("theta", [1e4, 5e5, 1e6])
+@pytest.mark.parametrize("hq,hkv,hd", [(32, 8, 128), (16, 8, 128), (40, 8, 128), (4, 4, 64), (2, 1, 8)])
+def test_append_single_token_bit_exact(ctx, theta, hq, hkv, hd):
+    P = port()
+    positions = [0, 1, 63, 64, 65, 511, 1000, 4095]
+    kvs = [ctx.kv_create(1, hkv, hd, 4096) for _ in positions]
+    n = len(positions)
+    q = _gen.normal(1, (n, hq, hd))
+    k = _gen.normal(2, (n, hkv, hd)) * np.float32(3.0)
+    v = _gen.normal(3, (n, hkv, hd)) * np.float32(3.0)
+    q_rot = q.copy()
+    ctx.kv_append(kvs, 0, positions, k, v, q_rot, hq, theta=theta)
+    for i, pos in enumerate(positions):
+        _, kr = P.rope(k[i:i + 1], pos, theta)
+        _, qr = P.rope(q[i:i + 1], pos, theta)
+        assert np.array_equal(kvs[i].read_rows(0, 0, pos, 1), P.f32_to_f16(kr)), (pos, "K")
+        assert np.array_equal(kvs[i].read_rows(0, 1, pos, 1), P.f32_to_f16(v[i:i + 1])), (pos, "V")
+        assert np.array_equal(bits(q_rot[i]), bits(qr[0])), (pos, "Q")
+    for kv in kvs:
+        kv.close()
+
+
+def test_append_many_tokens_and_long_positions(ctx):
+    """A prefill-sized append (n_tokens > 1) and positions up to 32767, where
+    the reference's repeated-subtraction range reduction runs thousands of steps."""
+    P = port()
+    hq, hkv, hd, theta = 8, 2, 128, 1e6
+    for p0, n in ((0, 200), (4000, 96), (32768 - 40, 40)):
+        kv = ctx.kv_create(1, hkv, hd, 32768)
+        q = _gen.normal(5, (n, hq, hd))
+        k = _gen.normal(6, (n, hkv, hd))
+        v = _gen.normal(7, (n, hkv, hd))
+        q_rot = q.copy()
+        ctx.kv_append([kv], 0, [p0], k, v, q_rot, hq, theta=theta, n_tokens=n)
+        _, kr = P.rope(k, p0, theta)
+        _, qr = P.rope(q, p0, theta)
+        assert np.array_equal(kv.read_rows(0, 0, p0, n), P.f32_to_f16(kr))
+        assert np.array_equal(kv.read_rows(0, 1, p0, n), P.f32_to_f16(v))
+        assert np.array_equal(bits(q_rot), bits(qr))
+        kv.close()
+
+
+def test_append_truncation_and_specials(ctx):
+    """test/unit_tests.c:105-107 witness plus subnormal flush, overflow and NaN."""
+    P = port()
+    hkv, hd = 1, 8
+    kv = ctx.kv_create(1, hkv, hd, 64)
+    row = np.array([1.0, 1.000732421875, -2.0, 6.0e-5, 5e-8, 1e9, -1e9, np.nan], np.float32)
+    row = row.reshape(1, 1, 8)
+    ctx.kv_append([kv], 0, [0], row, row, rope=False)
+    got_k = kv.read_rows(0, 0, 0, 1)
+    got_v = kv.read_rows(0, 1, 0, 1)
+    want = P.f32_to_f16(row)
+    assert np.array_equal(got_k, want) and np.array_equal(got_v, want)
+    assert list(want.ravel()[:3]) == [0x3C00, 0x3C00, 0xC000]
+    kv.close()
+
+
+def test_append_partial_rotary_and_default_theta(ctx):
+    P = port()
+    hq, hkv, hd = 4, 2, 128
+    kv = ctx.kv_create(1, hkv, hd, 1024)
+    q = _gen.normal(8, (1, hq, hd))
+    k = _gen.normal(9, (1, hkv, hd))
+    v = _gen.normal(10, (1, hkv, hd))
+    for theta, n_rot in ((1e4, 16), (0.5, 0), (1e6, 64), (1e6, 200)):
+        q_rot = q.copy()
+        ctx.kv_append([kv], 0, [777], k, v, q_rot, hq, theta=theta, n_rot_pairs=n_rot)
+        _, kr = P.rope(k, 777, theta, n_rot)
+        _, qr = P.rope(q, 777, theta, n_rot)
+        assert np.array_equal(kv.read_rows(0, 0, 777, 1), P.f32_to_f16(kr)), (theta, n_rot)
+        assert np.array_equal(bits(q_rot), bits(qr)), (theta, n_rot)
+    kv.close()
+
+
+def test_append_refusals(ctx):
+    """session.c:144: a row at max_ctx is CTX_FULL and nothing is written."""
+    import wayruntime_b200 as wr
+    kv = ctx.kv_create(2, 2, 128, 100)
+    row = _gen.normal(11, (1, 2, 128))
+    with pytest.raises(wr.WrCudaError) as e:
+        ctx.kv_append([kv], 0, [100], row, row, rope=False)
+    assert e.value.status == -6
+    with pytest.raises(wr.WrCudaError) as e:
+        ctx.kv_append([kv], 0, [90], np.zeros((11, 2, 128), np.float32),
+                      np.zeros((11, 2, 128), np.float32), rope=False, n_tokens=11)
+    assert e.value.status == -6
+    with pytest.raises(wr.WrCudaError) as e:
+        ctx.kv_append([kv], 2, [0], row, row, rope=False)       # layer out of range
+    assert e.value.status == -4
+    with pytest.raises(wr.WrCudaError) as e:
+        ctx.kv_append([kv, kv], 0, [0, 1], np.zeros((2, 2, 128), np.float32),
+                      np.zeros((2, 2, 128), np.float32), rope=False)   # same session twice
+    assert e.value.status == -4
+    assert not kv.read_rows(0, 0, 0, 100).any()
+    kv.close()
+
+
+def test_session_create_limits(ctx):
+    """session.c:755: max_ctx above the cap is WR_ERR_LIMIT; odd head_dim is INVAL."""
+    import wayruntime_b200 as wr
+    c2 = wr.Context(0)          # default cap 4096
+    with pytest.raises(wr.WrCudaError) as e:
+        c2.kv_create(1, 8, 128, 4097)
+    assert e.value.status == -8
+    c2.kv_create(1, 8, 128, 4096).close()
+    with pytest.raises(wr.WrCudaError) as e:
+        c2.kv_create(1, 8, 127, 64)
+    assert e.value.status == -4
+    with pytest.raises(wr.WrCudaError) as e:
+        c2.kv_create(1, 8, 2048, 64)
+    assert e.value.status == -8
+    c2.close()
+
+
+def test_rows_round_trip_all_layers(ctx):
+    """write_rows/read_rows are inverse on every layer and both layouts."""
+    for hd in (128, 64, 24):
+        kv = ctx.kv_create(3, 3, hd, 200)
+        for layer in range(3):
+            for which in (0, 1):
+                rows = _gen.uniform_u32(100 + layer * 2 + which, (150, 3, hd)).astype(np.uint16)
+                kv.write_rows(layer, which, 25, rows)
+                assert np.array_equal(kv.read_rows(layer, which, 25, 150), rows)
+        kv.close()

@@ -1,0 +1,237 @@
+// wr_internal.cuh — host-side objects and device helpers shared by the
+// translation units of libwr_cuda.so.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <vector>
+
+#include "wr_cuda.h"
+
+// ----------------------------------------------------------------- layout
+//
+// KV page = WR_CUDA_PAGE_TOKENS (64) consecutive tokens of one layer, all KV
+// heads.  Inside a page: [kv_head][K|V] blocks of 64*head_dim F16.
+//
+// head_dim % 64 == 0 ("tiled" blocks): the block is [head_dim/64][64 tok][64
+// dims] with the eight 16-byte chunks of each 128-byte row permuted by
+// chunk ^ (tok & 7).  That is the 128-byte-swizzled K-major operand image the
+// 5th-gen tensor cores read from shared memory, and it also makes ldmatrix
+// rows conflict-free, so one linear bulk copy of a block into shared memory
+// serves both the decode and the prefill kernel with no re-layout.
+//
+// other head_dim ("linear" blocks): [64 tok][pad8(head_dim)] row-major.
+
+constexpr uint32_t kPageTokens = WR_CUDA_PAGE_TOKENS;
+
+__host__ __device__ inline bool wr_tiled(uint32_t hd) { return (hd & 63u) == 0; }
+__host__ __device__ inline uint32_t wr_hd_pad(uint32_t hd) { return (hd + 7u) & ~7u; }
+__host__ __device__ inline uint32_t wr_block_bytes(uint32_t hd)
+{
+    return kPageTokens * wr_hd_pad(hd) * 2u;
+}
+__host__ __device__ inline uint64_t wr_page_bytes(uint32_t n_kv, uint32_t hd)
+{
+    return (uint64_t)n_kv * 2u * wr_block_bytes(hd);
+}
+// Byte offset of element (tok, d) inside one (head, K|V) block.
+__host__ __device__ inline uint32_t wr_elem_off(uint32_t tok, uint32_t d, uint32_t hd)
+{
+    if (wr_tiled(hd)) {
+        uint32_t half = d >> 6, dd = d & 63u;
+        uint32_t chunk = (dd >> 3) ^ (tok & 7u);
+        return half * (kPageTokens * 128u) + tok * 128u + chunk * 16u + (dd & 7u) * 2u;
+    }
+    return (tok * wr_hd_pad(hd) + d) * 2u;
+}
+// Byte offset of the (head, which) block inside a page; which: 0 = K, 1 = V.
+__host__ __device__ inline uint64_t wr_block_off(uint32_t head, uint32_t which, uint32_t hd)
+{
+    return ((uint64_t)head * 2u + which) * wr_block_bytes(hd);
+}
+
+// ------------------------------------------------------------ host objects
+
+struct wr_page_pool {
+    uint64_t page_bytes = 0;
+    std::vector<void *> slabs;       // cudaMalloc'd regions
+    std::vector<void *> free_pages;  // page base pointers
+};
+
+struct wr_cuda_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    std::mutex lock;
+    uint32_t attn_max_seq = WR_CUDA_ATTN_MAX_SEQ;
+    uint64_t launches = 0;
+    std::vector<wr_page_pool> pools;
+    // split-KV scratch: per-chunk partial triples and per-group arrival tickets
+    float *ws = nullptr;
+    size_t ws_bytes = 0;
+    int *tickets = nullptr;
+    size_t ticket_count = 0;
+    int *dev_err = nullptr;          // device-side error flag
+    int *host_err = nullptr;         // pinned mirror
+    // staging for WR_CUDA_MEM_HOST calls
+    void *stage_dev = nullptr;
+    size_t stage_dev_bytes = 0;
+    void *stage_host = nullptr;      // pinned
+    size_t stage_host_bytes = 0;
+    int live_kv = 0;
+    uint32_t attr_flags = 0;         // per-device kernel attributes already set
+};
+
+struct wr_cuda_kv {
+    wr_cuda_ctx *ctx = nullptr;
+    uint32_t n_layers = 0, n_kv = 0, hd = 0, max_ctx = 0, n_pages = 0;
+    std::vector<void *> pages;       // n_layers * n_pages page pointers (host copy)
+    uint64_t *d_pages = nullptr;     // same table on the device
+    size_t pool_index = 0;
+};
+
+// Kernel-parameter block describing the sessions of one batched launch.
+struct wr_batch_desc {
+    const uint64_t *pages[WR_CUDA_BATCH_MAX];   // device page table of (session, layer)
+    uint32_t seq_len[WR_CUDA_BATCH_MAX];
+};
+
+// ------------------------------------------------------------ host helpers
+
+#define WR_CUDA_TRY(expr)                                                   \
+    do {                                                                    \
+        cudaError_t e__ = (expr);                                           \
+        if (e__ != cudaSuccess) {                                           \
+            (void)cudaGetLastError();                                       \
+            return e__ == cudaErrorMemoryAllocation ? WR_CUDA_ERR_NOMEM     \
+                                                    : WR_CUDA_ERR_INTERNAL; \
+        }                                                                   \
+    } while (0)
+
+int wr_ctx_reserve_stage(wr_cuda_ctx *ctx, size_t dev_bytes, size_t host_bytes);
+int wr_ctx_reserve_ws(wr_cuda_ctx *ctx, size_t ws_bytes, size_t tickets);
+int wr_kv_batch_check(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer);
+int wr_append_validate(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
+                       const uint32_t *positions, uint32_t n_tokens, const float *k_rows,
+                       const float *v_rows, const float *q_rows, uint32_t n_q_heads, int mem);
+int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
+                     const uint32_t *positions, uint32_t n_tokens, const float *dk,
+                     const float *dv, float *dq, uint32_t n_q_heads, float theta_base,
+                     uint32_t n_rot_pairs, uint32_t flags);
+
+// ---------------------------------------------------------- device helpers
+
+#ifdef __CUDACC__
+
+// Reference sentinel for "no score yet" / masked keys (src/core/kernels.c:1480).
+#define WR_NEG_SENTINEL (-1e30f)
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: returns false when the phase did not complete within about
+// two seconds of SM clock (the caller records an error and unwinds; nothing
+// in this library spins without a limit).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+{
+    const uint32_t addr = smem_u32(bar);
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (clock64() - t0 > 4000000000LL) return false;
+    }
+}
+__device__ __forceinline__ void fence_barrier_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Linear bulk copy global -> shared through the TMA unit; completion is
+// signalled on `bar` as transaction bytes.  Addresses and size are multiples
+// of 16 bytes.
+__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32_t bytes,
+                                         uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2,
+                                            uint32_t &r3, uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t &r0, uint32_t &r1, uint32_t &r2,
+                                                  uint32_t &r3, uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Split an F32 pair into F16 (hi, lo) pairs with hi + lo ~= x to ~2^-22.
+__device__ __forceinline__ void split_half2(float x, float y, uint32_t &hi, uint32_t &lo)
+{
+    __half2 h = __floats2half2_rn(x, y);
+    float2 hf = __half22float2(h);
+    __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<uint32_t *>(&h);
+    lo = *reinterpret_cast<uint32_t *>(&l);
+}
+
+// The reference's truncating F32 -> F16 (src/core/quant.c:121-136).
+__device__ __forceinline__ uint16_t wr_f32_to_f16_trunc(float f)
+{
+    uint32_t b = __float_as_uint(f);
+    uint32_t sign = (b >> 16) & 0x8000u;
+    int32_t ex = (int32_t)((b >> 23) & 0xFFu) - 112;
+    if (ex <= 0) return (uint16_t)sign;
+    if (ex >= 31) return (uint16_t)(sign | 0x7C00u);
+    return (uint16_t)(sign | ((uint32_t)ex << 10) | ((b >> 13) & 0x3FFu));
+}
+
+#endif  // __CUDACC__
