@@ -254,6 +254,26 @@ def run_gpu_arm(args):
     for i in range(args.warmup):
         step_device(i)
     ctx.sync()
+    # The step is launch-bound from Python (tens of microseconds of work per
+    # step), so one pass over the rotating layers is captured in a CUDA graph
+    # and replayed; leftover steps run eagerly.
+    graph, launch_mode = None, "eager"
+    l_cap = ctx.launch_count
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                for i in range(N_ROT_LAYERS):
+                    step_device(i)
+            launch_mode = f"cuda graph of {N_ROT_LAYERS} steps"
+        except Exception as exc:          # capture unavailable: measure eagerly, say so
+            graph, launch_mode = None, f"eager (graph capture failed: {type(exc).__name__})"
+            torch.cuda.synchronize()
+    launches_per_step = (ctx.launch_count - l_cap) / N_ROT_LAYERS if graph else None
+    torch.cuda.set_stream(stream)
+    if graph is not None:
+        graph.replay()
+    ctx.sync()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -261,12 +281,17 @@ def run_gpu_arm(args):
     l0 = ctx.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
-    for i in range(args.steps):
+    n_replay = args.steps // N_ROT_LAYERS if graph is not None else 0
+    for _ in range(n_replay):
+        graph.replay()
+    for i in range(n_replay * N_ROT_LAYERS, args.steps):
         step_device(i)
     ev1.record(stream)
     ctx.sync()
     barrier()
     launches = ctx.launch_count - l0
+    if graph is not None:
+        launches += int(launches_per_step * n_replay * N_ROT_LAYERS)
     step_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
 
     # ---- decode kernel alone (roofline): one event pair per launch
@@ -342,7 +367,7 @@ def run_gpu_arm(args):
             "e2e": {"value": N_SESS * world * args.steps / e2e_s, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": 1e3 * e2e_s / args.steps},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "launch_mode": launch_mode,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_hd128_kernel",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_src}",
@@ -368,6 +393,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every step from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 20:

@@ -1,0 +1,505 @@
+// attn_decode_hd128.cuh — the decode attention kernel for head_dim 128.
+//
+// Restates wri_op_gqa_attention for seq_q = 1 (src/core/kernels.c:1414-1527):
+// scores = q.k * scale, online softmax with the -1e30 sentinel, o += p * v,
+// out = o / l — for every session of a batch in ONE grid.
+//
+// Organisation
+//   * work item = (session, kv head, q-head subgroup of <= 4*NT heads, chunk
+//     of keys).  The chunk length is a function of that session's length
+//     only, so a session's result does not depend on its batch mates.
+//   * every warp is a self-contained engine: it owns a 16 KB K slot, a 16 KB
+//     V slot and a Q slot in shared memory and refills them itself with TMA
+//     bulk copies (one 16 KB copy per K or V tile: 64 keys of one kv head are
+//     contiguous in the page and already in the swizzled order ldmatrix
+//     wants).  While it computes Q.K on tile t the V of tile t is in flight;
+//     while it computes P.V the K of tile t+1 is in flight — across item
+//     boundaries too.  No CTA-wide barrier exists.
+//   * items come from a global queue (the first one is static); an engine
+//     draws the index of a future item one item ahead and loads the page
+//     pointer of a future tile one tile ahead, so neither latency is exposed.
+//     Which engine runs an item has no effect on the item's result.
+//   * tensor-core tiles are transposed so that nothing is wasted on the tiny
+//     head count: S^T[key, slot] = K[key, :] . Q^T[:, slot] puts 16 keys on the
+//     M side and the q heads on the 8-wide N side, each head twice — slot 2h
+//     carries the F16 high part of the (scaled) F32 query, slot 2h+1 the F16
+//     low part, so scores keep F32-level query precision.  Probabilities are
+//     split the same way (movmatrix transposes them into the B operand) and
+//     O^T[dim, slot] += V^T[dim, key] . P^T[key, slot].  Accumulation is F32.
+//   * chunks of one (session, kv head, subgroup) are merged by the warp that
+//     finishes last (arrival ticket), in chunk order: deterministic.
+//   The kernel is HBM-bound by design: K and V are read exactly once.
+#pragma once
+
+#include "wr_internal.cuh"
+
+namespace wr_decode {
+
+constexpr int kHd = 128;
+constexpr int kTile = 64;                              // keys per tile = tokens per page
+constexpr int kWarps = 6;                              // engines per CTA
+constexpr int kThreads = kWarps * 32;
+constexpr uint32_t kBlockBytes = kTile * kHd * 2;      // one K or V tile of one head
+constexpr int kTripleStride = WR_CUDA_TRIPLE_PAD + kHd;  // m, l, 0, 0, o[128]
+constexpr int kMaxChunks = 16;
+constexpr int kMinChunkTiles = 2;
+
+// Sessions appear here sorted by descending length (longest chunks are drawn
+// first); row[i] is the caller's index of entry i.
+struct params {
+    wr_batch_desc b;
+    uint32_t row[WR_CUDA_BATCH_MAX];
+    uint32_t key_lo[WR_CUDA_BATCH_MAX];
+    uint32_t tile_lo[WR_CUDA_BATCH_MAX];
+    uint32_t n_tiles[WR_CUDA_BATCH_MAX];
+    uint32_t chunk_tiles[WR_CUDA_BATCH_MAX];
+    uint32_t n_chunks[WR_CUDA_BATCH_MAX];      // 0 for a session with no keys (empty shard)
+    uint32_t item_base[WR_CUDA_BATCH_MAX + 1];
+    const float *q;
+    float *out;        // [n_sess, n_q, hd] rows, or triples when emit_triples
+    float *ws;         // per-item partial triples, 8 rows each
+    int *tickets;      // per-group arrival counters, then [n_groups] = queue, [n_groups+1] = exits
+    int *err;
+    uint32_t n_sess, n_q, n_kv, group, qsubs, emit_triples, n_groups;
+    float scale;
+};
+
+struct warp_smem {
+    alignas(128) uint8_t k[kBlockBytes];
+    alignas(128) uint8_t v[kBlockBytes];
+    alignas(128) float q[8][kHd];
+};
+
+struct smem_layout {
+    warp_smem w[kWarps];
+    alignas(8) uint64_t full_k[kWarps];
+    uint64_t full_v[kWarps];
+};
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a)
+{
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ int atom_add_acq_rel(int *addr, int v)
+{
+    int old;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ int atom_add_relaxed(int *addr, int v)
+{
+    int old;
+    asm volatile("atom.add.relaxed.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
+    return old;
+}
+
+// One tile of work, with everything the compute loop needs to know about it.
+struct tile_desc {
+    uint32_t it;          // item index (addresses the partial-triple scratch)
+    uint32_t s, h, qs;    // sorted session slot, kv head, q-head subgroup
+    uint32_t t;           // tile index = page index
+    uint32_t flags;       // bit0 valid, bit1 first tile of item, bit2 last tile of item
+    const char *page;
+};
+
+// Walks this engine's tiles in order, across items.
+struct tile_stream {
+    uint32_t it, s, h, qs, t, t_end;
+    uint32_t idx_next;    // index of the item after the current one (all lanes)
+    int pending;          // lane 0: result of the queue draw issued one item ago
+    bool have;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const params p)
+{
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    smem_layout &sm = *reinterpret_cast<smem_layout *>(smem_raw);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n_items = p.item_base[p.n_sess];
+    const uint32_t n_engines = gridDim.x * kWarps;
+    const uint32_t engine = warp * gridDim.x + blockIdx.x;   // neighbours in item order sit on different SMs
+    warp_smem &ws = sm.w[warp];
+    uint64_t *bar_k = &sm.full_k[warp], *bar_v = &sm.full_v[warp];
+    int *queue = p.tickets + p.n_groups, *exits = queue + 1;
+    constexpr uint32_t kHeadsMax = 4 * NT;
+    const uint32_t g = lane >> 2, t4 = lane & 3;
+
+    if (lane == 0) {
+        mbar_init(bar_k, 1);
+        mbar_init(bar_v, 1);
+        fence_barrier_init();
+    }
+    __syncwarp();
+
+    // A session with no keys (an empty split-KV shard) has no items: its
+    // triples are the neutral element of the merge.
+    if (p.emit_triples && blockIdx.x == 0) {
+        for (uint32_t s = 0; s < p.n_sess; ++s) {
+            if (p.n_chunks[s] != 0) continue;
+            float *base = p.out + (size_t)p.row[s] * p.n_q * kTripleStride;
+            for (uint32_t i = threadIdx.x; i < p.n_q * kTripleStride; i += kThreads)
+                base[i] = (i % kTripleStride == 0) ? WR_NEG_SENTINEL : 0.f;
+        }
+    }
+
+    auto draw = [&]() -> int {       // lane 0: take the next item index from the queue
+        return (int)n_engines + atom_add_relaxed(queue, 1);
+    };
+    tile_stream ts;
+    ts.have = false;
+    ts.it = engine;
+    ts.t = ts.t_end = 0;
+    ts.s = ts.h = ts.qs = 0;
+    ts.pending = 0;
+    {
+        int first = 0;
+        if (lane == 0) {
+            first = draw();
+            ts.pending = draw();
+        }
+        ts.idx_next = (uint32_t)__shfl_sync(0xffffffffu, first, 0);
+    }
+    bool started = false;
+    auto next_tile = [&]() -> tile_desc {
+        tile_desc d;
+        d.flags = 0;
+        d.it = d.s = d.h = d.qs = d.t = 0;
+        d.page = nullptr;
+        if (!ts.have || ts.t >= ts.t_end) {
+            if (started) {
+                ts.it = ts.idx_next;
+                ts.idx_next = (uint32_t)__shfl_sync(0xffffffffu, ts.pending, 0);
+                if (lane == 0) ts.pending = draw();
+            }
+            started = true;
+            if (ts.it >= n_items) {
+                ts.have = false;
+                ts.it = 0xffffffffu;     // stay exhausted
+                return d;
+            }
+            uint32_t s = 0;
+            while (s + 1 < p.n_sess && ts.it >= p.item_base[s + 1]) ++s;
+            const uint32_t local = ts.it - p.item_base[s];
+            const uint32_t nc = p.n_chunks[s];
+            const uint32_t c = local % nc, gq = local / nc;
+            ts.s = s;
+            ts.qs = gq % p.qsubs;
+            ts.h = gq / p.qsubs;
+            ts.t = p.tile_lo[s] + c * p.chunk_tiles[s];
+            ts.t_end = min(ts.t + p.chunk_tiles[s], p.n_tiles[s]);
+            ts.have = true;
+            d.flags |= 2u;
+        }
+        d.it = ts.it;
+        d.s = ts.s;
+        d.h = ts.h;
+        d.qs = ts.qs;
+        d.t = ts.t;
+        d.flags |= 1u;
+        if (ts.t + 1 >= ts.t_end) d.flags |= 4u;
+        d.page = (const char *)p.b.pages[ts.s][ts.t];    // consumed one tile later
+        ++ts.t;
+        return d;
+    };
+    auto issue_k = [&](const tile_desc &d) {   // lane 0 only
+        const char *src = d.page + wr_block_off(d.h, 0, kHd);
+        uint32_t bytes = kBlockBytes;
+        const bool first = (d.flags & 2u) != 0;
+        const uint32_t heads = min(kHeadsMax, p.group - d.qs * kHeadsMax);
+        if (first) bytes += heads * kHd * 4u;
+        mbar_expect_tx(bar_k, bytes);
+        bulk_g2s(ws.k, src, kBlockBytes, bar_k);
+        if (first) {
+            const float *qsrc =
+                p.q + ((size_t)p.row[d.s] * p.n_q + d.h * p.group + d.qs * kHeadsMax) * kHd;
+            bulk_g2s(ws.q, qsrc, heads * kHd * 4u, bar_k);
+        }
+    };
+    auto issue_v = [&](const tile_desc &d) {   // lane 0 only
+        mbar_expect_tx(bar_v, kBlockBytes);
+        bulk_g2s(ws.v, d.page + wr_block_off(d.h, 1, kHd), kBlockBytes, bar_v);
+    };
+
+    tile_desc d0 = next_tile();
+    if (lane == 0 && (d0.flags & 1u)) {
+        issue_k(d0);
+        issue_v(d0);
+    }
+    tile_desc d1 = next_tile();
+    uint32_t uses = 0;
+    const uint32_t kaddr = smem_u32(ws.k), vaddr = smem_u32(ws.v);
+
+    uint32_t qb[NT][kHd / 16][2];       // B operand: Q^T, slot column g
+    float m[NT], l[NT];
+    float oacc[NT][kHd / 16][4];        // O^T: dims on M, slots on N
+
+    while (d0.flags & 1u) {
+        const uint32_t seq_len = p.b.seq_len[d0.s];
+        const uint32_t key_lo = p.key_lo[d0.s];
+        const uint32_t heads_here = min(kHeadsMax, p.group - d0.qs * kHeadsMax);
+
+        // ---------------- K tile (and, on the item's first tile, its Q rows)
+        if (!mbar_wait(bar_k, uses & 1)) {
+            if (lane == 0) atomicExch(p.err, 2);
+            return;
+        }
+        if (d0.flags & 2u) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                m[nt] = WR_NEG_SENTINEL;
+                l[nt] = 0.f;
+#pragma unroll
+                for (int i = 0; i < kHd / 16; ++i)
+                    oacc[nt][i][0] = oacc[nt][i][1] = oacc[nt][i][2] = oacc[nt][i][3] = 0.f;
+                const uint32_t hs = nt * 4 + (g >> 1);
+                const bool live = hs < heads_here;
+                const float *qrow = ws.q[hs];
+#pragma unroll
+                for (int ks = 0; ks < kHd / 16; ++ks) {
+                    float2 x = make_float2(0.f, 0.f), y = make_float2(0.f, 0.f);
+                    if (live) {
+                        x = *reinterpret_cast<const float2 *>(qrow + ks * 16 + 2 * t4);
+                        y = *reinterpret_cast<const float2 *>(qrow + ks * 16 + 8 + 2 * t4);
+                    }
+                    uint32_t xh, xl, yh, yl;
+                    split_half2(x.x * p.scale, x.y * p.scale, xh, xl);
+                    split_half2(y.x * p.scale, y.y * p.scale, yh, yl);
+                    qb[nt][ks][0] = (g & 1) ? xl : xh;
+                    qb[nt][ks][1] = (g & 1) ? yl : yh;
+                }
+            }
+        }
+
+        // S^T = K . Q^T : four 16-key M tiles, eight 16-dim K steps
+        float sacc[NT][4][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt)
+                sacc[nt][mt][0] = sacc[nt][mt][1] = sacc[nt][mt][2] = sacc[nt][mt][3] = 0.f;
+        {
+            const uint32_t mi = lane >> 3;
+            const uint32_t krow0 = (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                const uint32_t krow = mt * 16 + krow0;
+                const uint32_t rowaddr = kaddr + krow * 128;
+                const uint32_t sw = krow & 7;
+#pragma unroll
+                for (int ks = 0; ks < kHd / 16; ++ks) {
+                    const uint32_t c16 = ks * 2 + (mi >> 1);
+                    uint32_t a[4];
+                    ldmatrix_x4(a[0], a[1], a[2], a[3],
+                                rowaddr + (c16 >> 3) * 8192 + (((c16 & 7) ^ sw) * 16));
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                        mma_16816(sacc[nt][mt], a, qb[nt][ks][0], qb[nt][ks][1]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && (d1.flags & 1u)) issue_k(d1);    // K slot is free: fetch the next K tile
+
+        // ---------------- online softmax for this thread's head slot(s)
+        const uint32_t key0 = d0.t * kTile;
+        const bool tail = key0 + kTile > seq_len;
+        const bool need_mask = tail || key0 < key_lo;
+        uint32_t pb[NT][4][2];              // B operand: P^T per 16-key step
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            float sc[4][2];
+            float tmax = WR_NEG_SENTINEL;
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                sc[mt][0] = sacc[nt][mt][0] + sacc[nt][mt][1];    // key mt*16+g   (high + low part)
+                sc[mt][1] = sacc[nt][mt][2] + sacc[nt][mt][3];    // key mt*16+g+8
+                if (need_mask) {
+                    const uint32_t ka = key0 + mt * 16 + g, kb2 = ka + 8;
+                    if (!(ka < seq_len && ka >= key_lo)) sc[mt][0] = WR_NEG_SENTINEL;
+                    if (!(kb2 < seq_len && kb2 >= key_lo)) sc[mt][1] = WR_NEG_SENTINEL;
+                }
+                tmax = fmaxf(tmax, fmaxf(sc[mt][0], sc[mt][1]));
+            }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+            const float m_new = fmaxf(m[nt], tmax);
+            const float a = (m[nt] == WR_NEG_SENTINEL) ? 0.f : __expf(m[nt] - m_new);
+            float psum = 0.f;
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                const float p0 = (sc[mt][0] == WR_NEG_SENTINEL) ? 0.f : __expf(sc[mt][0] - m_new);
+                const float p1 = (sc[mt][1] == WR_NEG_SENTINEL) ? 0.f : __expf(sc[mt][1] - m_new);
+                psum += p0 + p1;
+                // (high, low) pair of p sits where S^T had (slot 2h, slot 2h+1);
+                // the 8x8 transpose turns it into the B fragment of P^T.
+                const __half p0h = __float2half_rn(p0), p1h = __float2half_rn(p1);
+                __half2 h0 = __halves2half2(p0h, __float2half_rn(p0 - __half2float(p0h)));
+                __half2 h1 = __halves2half2(p1h, __float2half_rn(p1 - __half2float(p1h)));
+                pb[nt][mt][0] = movmatrix_trans(*reinterpret_cast<uint32_t *>(&h0));
+                pb[nt][mt][1] = movmatrix_trans(*reinterpret_cast<uint32_t *>(&h1));
+            }
+            l[nt] = l[nt] * a + psum;
+            m[nt] = m_new;
+#pragma unroll
+            for (int i = 0; i < kHd / 16; ++i) {
+                oacc[nt][i][0] *= a; oacc[nt][i][1] *= a; oacc[nt][i][2] *= a; oacc[nt][i][3] *= a;
+            }
+        }
+
+        // ---------------- V tile
+        if (!mbar_wait(bar_v, uses & 1)) {
+            if (lane == 0) atomicExch(p.err, 3);
+            return;
+        }
+        ++uses;
+        if (tail) {
+            // Rows past the session's length were never written for this
+            // position (or belong to a rolled-back step): clear them so that
+            // 0 * garbage cannot make a NaN.
+            const uint32_t first_bad = seq_len - key0;
+            for (uint32_t i = first_bad * 16 + lane; i < kTile * 16; i += 32) {
+                const uint32_t krow = i >> 4, ch = i & 15;
+                *reinterpret_cast<uint4 *>(ws.v + (ch >> 3) * 8192 + krow * 128 + (ch & 7) * 16) =
+                    make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async();   // these generic writes precede the next bulk copy into the slot
+            __syncwarp();
+        }
+        // O^T += V^T . P^T : eight 16-dim M tiles, four 16-key K steps
+        {
+            const uint32_t mi = lane >> 3;
+            const uint32_t krow0 = (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const uint32_t krow = kk * 16 + krow0;
+                const uint32_t rowaddr = vaddr + krow * 128;
+                const uint32_t sw = krow & 7;
+#pragma unroll
+                for (int md = 0; md < kHd / 16; ++md) {
+                    const uint32_t c16 = md * 2 + (mi & 1);
+                    uint32_t a[4];
+                    ldmatrix_x4_trans(a[0], a[1], a[2], a[3],
+                                      rowaddr + (c16 >> 3) * 8192 + (((c16 & 7) ^ sw) * 16));
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                        mma_16816(oacc[nt][md], a, pb[nt][kk][0], pb[nt][kk][1]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && (d1.flags & 1u)) issue_v(d1);    // V slot is free: fetch the next V tile
+
+        if (d0.flags & 4u) {
+            // ---------------- item done: emit its row(s) or its partial triple
+            const uint32_t nc = p.n_chunks[d0.s];
+            const bool direct = (nc == 1);
+            const size_t row0 = (size_t)p.row[d0.s] * p.n_q + d0.h * p.group + d0.qs * kHeadsMax;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                float lt = l[nt];
+                lt += __shfl_xor_sync(0xffffffffu, lt, 4);
+                lt += __shfl_xor_sync(0xffffffffu, lt, 8);
+                lt += __shfl_xor_sync(0xffffffffu, lt, 16);
+                const uint32_t hs = nt * 4 + t4;            // this thread's head slot
+                if (hs < heads_here) {
+                    if (direct && !p.emit_triples) {
+                        const float inv = (lt > 0.f) ? 1.0f / lt : 0.f;
+                        float *o = p.out + (row0 + hs) * kHd;
+#pragma unroll
+                        for (int md = 0; md < kHd / 16; ++md) {
+                            o[md * 16 + g] = (oacc[nt][md][0] + oacc[nt][md][1]) * inv;
+                            o[md * 16 + g + 8] = (oacc[nt][md][2] + oacc[nt][md][3]) * inv;
+                        }
+                    } else {
+                        float *tr = direct ? p.out + (row0 + hs) * kTripleStride
+                                           : p.ws + ((size_t)d0.it * 8 + hs) * kTripleStride;
+#pragma unroll
+                        for (int md = 0; md < kHd / 16; ++md) {
+                            tr[WR_CUDA_TRIPLE_PAD + md * 16 + g] = oacc[nt][md][0] + oacc[nt][md][1];
+                            tr[WR_CUDA_TRIPLE_PAD + md * 16 + g + 8] = oacc[nt][md][2] + oacc[nt][md][3];
+                        }
+                        if (g == 0) {
+                            tr[0] = m[nt]; tr[1] = lt; tr[2] = 0.f; tr[3] = 0.f;
+                        }
+                    }
+                }
+            }
+
+            if (!direct) {
+                // Arrival ticket: the warp that completes the group merges it.
+                // __syncwarp orders every lane's partial stores before lane
+                // 0's release; the acquire side re-reads through L2.
+                __syncwarp();
+                const uint32_t gidx = (d0.s * p.n_kv + d0.h) * p.qsubs + d0.qs;
+                int last = 0;
+                if (lane == 0) last = (atom_add_acq_rel(&p.tickets[gidx], 1) == (int)nc - 1);
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __syncwarp();
+                    const uint32_t c_here = (d0.it - p.item_base[d0.s]) % nc;
+                    const size_t first_item = (size_t)d0.it - c_here;
+                    for (uint32_t hs = 0; hs < heads_here; ++hs) {
+                        // lane c holds chunk c's (m, l); chunks merge in index order
+                        float mc = WR_NEG_SENTINEL, lc = 0.f;
+                        if (lane < nc) {
+                            const float *tr = p.ws + ((first_item + lane) * 8 + hs) * kTripleStride;
+                            mc = __ldcg(tr);
+                            lc = __ldcg(tr + 1);
+                        }
+                        float4 ov[kMaxChunks];
+#pragma unroll
+                        for (int j = 0; j < kMaxChunks; ++j)
+                            ov[j] = ((uint32_t)j < nc)
+                                        ? __ldcg(reinterpret_cast<const float4 *>(
+                                              p.ws + ((first_item + j) * 8 + hs) * kTripleStride +
+                                              WR_CUDA_TRIPLE_PAD) + lane)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                        float mstar = mc;
+#pragma unroll
+                        for (int off = 16; off > 0; off >>= 1)
+                            mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, off));
+                        const float wgt = (mc == WR_NEG_SENTINEL) ? 0.f : __expf(mc - mstar);
+                        const float wl = wgt * lc;
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                        float L = 0.f;
+#pragma unroll
+                        for (int j = 0; j < kMaxChunks; ++j) {
+                            const float wj = __shfl_sync(0xffffffffu, wgt, j);
+                            L += __shfl_sync(0xffffffffu, wl, j);
+                            acc.x += wj * ov[j].x; acc.y += wj * ov[j].y;
+                            acc.z += wj * ov[j].z; acc.w += wj * ov[j].w;
+                        }
+                        if (p.emit_triples) {
+                            float *tr = p.out + (row0 + hs) * kTripleStride;
+                            reinterpret_cast<float4 *>(tr + WR_CUDA_TRIPLE_PAD)[lane] = acc;
+                            if (lane == 0) {
+                                tr[0] = mstar; tr[1] = L; tr[2] = 0.f; tr[3] = 0.f;
+                            }
+                        } else {
+                            const float inv = (L > 0.f) ? 1.0f / L : 0.f;
+                            acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+                            reinterpret_cast<float4 *>(p.out + (row0 + hs) * kHd)[lane] = acc;
+                        }
+                    }
+                    if (lane == 0) p.tickets[gidx] = 0;   // ready for the next launch
+                }
+            }
+        }
+        d0 = d1;
+        d1 = next_tile();
+    }
+
+    // The last engine to leave rewinds the queue for the next launch.
+    if (lane == 0) {
+        if (atom_add_acq_rel(exits, 1) == (int)n_engines - 1) {
+            *queue = 0;
+            *exits = 0;
+        }
+    }
+}
+
+}  // namespace wr_decode

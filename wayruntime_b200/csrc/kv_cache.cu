@@ -84,6 +84,9 @@ extern "C" int wr_cuda_ctx_sync(wr_cuda_ctx *ctx)
     if (*ctx->host_err != 0) {
         *ctx->host_err = 0;
         WR_CUDA_TRY(cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
+        // A kernel that gave up left its arrival tickets and work queue mid-count.
+        if (ctx->tickets)
+            WR_CUDA_TRY(cudaMemsetAsync(ctx->tickets, 0, ctx->ticket_count * sizeof(int), ctx->stream));
         WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
         return WR_CUDA_ERR_INTERNAL;
     }
