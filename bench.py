@@ -294,18 +294,35 @@ def run_gpu_arm(args):
         launches += int(launches_per_step * n_replay * N_ROT_LAYERS)
     step_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
 
-    # ---- decode kernel alone (roofline): one event pair per launch
-    dec_ms = []
-    for i in range(args.steps):
-        layer = i % N_ROT_LAYERS
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream)
-        ctx.attn_decode(batch, layer, len_arr, q_work, out, HQ)
-        b.record(stream)
-        dec_ms.append((a, b))
+    # ---- decode kernel alone (roofline): K launches back to back between two
+    # events on the launching stream, rotating layers; average per launch
+    def decode_only(i):
+        ctx.attn_decode(batch, i % N_ROT_LAYERS, len_arr, q_work, out, HQ)
+
+    dgraph = None
+    if graph is not None:
+        try:
+            dgraph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(dgraph, stream=stream, capture_error_mode="thread_local"):
+                for i in range(N_ROT_LAYERS):
+                    decode_only(i)
+        except Exception:
+            dgraph = None
+            torch.cuda.synchronize()
+    torch.cuda.set_stream(stream)
+    for i in range(N_ROT_LAYERS):
+        decode_only(i)
     ctx.sync()
-    dec_ms = [a.elapsed_time(b) for a, b in dec_ms]
-    dec_avg_ms = float(np.mean(dec_ms))
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    n_rep = args.steps // N_ROT_LAYERS if dgraph is not None else 0
+    for _ in range(n_rep):
+        dgraph.replay()
+    for i in range(n_rep * N_ROT_LAYERS, args.steps):
+        decode_only(i)
+    b.record(stream)
+    ctx.sync()
+    dec_avg_ms = a.elapsed_time(b) / args.steps
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the C-ABI with pinned host buffers

@@ -193,6 +193,9 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
             const uint32_t nc = (span + ct - 1) / ct;          // 0 for an empty shard
             p.b.pages[i] = kv[s]->d_pages + (size_t)layer * kv[s]->n_pages;
             p.b.seq_len[i] = len;
+            p.page_base[i] = kv[s]->contig[layer]
+                                 ? (const char *)kv[s]->pages[(size_t)layer * kv[s]->n_pages]
+                                 : nullptr;
             p.row[i] = s;
             p.key_lo[i] = key_lo;
             p.tile_lo[i] = tile_lo;
@@ -203,6 +206,8 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
             items += n_kv * qsubs * nc;
         }
         for (uint32_t s = n_sess; s <= WR_CUDA_BATCH_MAX; ++s) p.item_base[s] = items;
+        for (uint32_t i = n_sess; i < WR_CUDA_BATCH_MAX; ++i) p.page_base[i] = nullptr;
+        p.page_bytes = wr_page_bytes(n_kv, hd);
         p.n_groups = n_sess * n_kv * qsubs;
         int rc = wr_ctx_reserve_ws(ctx, (size_t)std::max(items, 1u) * 8 * kTripleStride * sizeof(float),
                                    (size_t)p.n_groups + 2);

@@ -55,6 +55,8 @@ struct params {
     uint32_t chunk_tiles[WR_CUDA_BATCH_MAX];
     uint32_t n_chunks[WR_CUDA_BATCH_MAX];      // 0 for a session with no keys (empty shard)
     uint32_t item_base[WR_CUDA_BATCH_MAX + 1];
+    const char *page_base[WR_CUDA_BATCH_MAX];  // non-null: page t = page_base + t * page_bytes
+    uint64_t page_bytes;
     const float *q;
     float *out;        // [n_sess, n_q, hd] rows, or triples when emit_triples
     float *ws;         // per-item partial triples, 8 rows each
@@ -126,6 +128,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
     int *queue = p.tickets + p.n_groups, *exits = queue + 1;
     constexpr uint32_t kHeadsMax = 4 * NT;
     const uint32_t g = lane >> 2, t4 = lane & 3;
+    const uint64_t stream_policy = l2_policy_evict_first();
 
     if (lane == 0) {
         mbar_init(bar_k, 1);
@@ -145,23 +148,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         }
     }
 
+    // The first two items of an engine are fixed (engine, engine + n_engines);
+    // later ones come from the queue, drawn one item before they are needed.
     auto draw = [&]() -> int {       // lane 0: take the next item index from the queue
-        return (int)n_engines + atom_add_relaxed(queue, 1);
+        return 2 * (int)n_engines + atom_add_relaxed(queue, 1);
     };
     tile_stream ts;
     ts.have = false;
     ts.it = engine;
     ts.t = ts.t_end = 0;
     ts.s = ts.h = ts.qs = 0;
+    ts.idx_next = engine + n_engines;
     ts.pending = 0;
-    {
-        int first = 0;
-        if (lane == 0) {
-            first = draw();
-            ts.pending = draw();
-        }
-        ts.idx_next = (uint32_t)__shfl_sync(0xffffffffu, first, 0);
-    }
+    if (lane == 0) ts.pending = draw();
     bool started = false;
     auto next_tile = [&]() -> tile_desc {
         tile_desc d;
@@ -200,7 +199,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         d.t = ts.t;
         d.flags |= 1u;
         if (ts.t + 1 >= ts.t_end) d.flags |= 4u;
-        d.page = (const char *)p.b.pages[ts.s][ts.t];    // consumed one tile later
+        // consumed one tile later, so a table lookup is off the critical path
+        d.page = p.page_base[ts.s] ? p.page_base[ts.s] + (uint64_t)ts.t * p.page_bytes
+                                   : (const char *)p.b.pages[ts.s][ts.t];
         ++ts.t;
         return d;
     };
@@ -211,7 +212,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         const uint32_t heads = min(kHeadsMax, p.group - d.qs * kHeadsMax);
         if (first) bytes += heads * kHd * 4u;
         mbar_expect_tx(bar_k, bytes);
-        bulk_g2s(ws.k, src, kBlockBytes, bar_k);
+        bulk_g2s_hint(ws.k, src, kBlockBytes, bar_k, stream_policy);
         if (first) {
             const float *qsrc =
                 p.q + ((size_t)p.row[d.s] * p.n_q + d.h * p.group + d.qs * kHeadsMax) * kHd;
@@ -220,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
     };
     auto issue_v = [&](const tile_desc &d) {   // lane 0 only
         mbar_expect_tx(bar_v, kBlockBytes);
-        bulk_g2s(ws.v, d.page + wr_block_off(d.h, 1, kHd), kBlockBytes, bar_v);
+        bulk_g2s_hint(ws.v, d.page + wr_block_off(d.h, 1, kHd), kBlockBytes, bar_v, stream_policy);
     };
 
     tile_desc d0 = next_tile();
@@ -442,14 +443,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
                     __syncwarp();
                     const uint32_t c_here = (d0.it - p.item_base[d0.s]) % nc;
                     const size_t first_item = (size_t)d0.it - c_here;
-                    for (uint32_t hs = 0; hs < heads_here; ++hs) {
-                        // lane c holds chunk c's (m, l); chunks merge in index order
-                        float mc = WR_NEG_SENTINEL, lc = 0.f;
-                        if (lane < nc) {
+                    // One load round for every head's (m, l): lane c holds chunk c.
+                    float mc[kHeadsMax], lc[kHeadsMax];
+#pragma unroll
+                    for (uint32_t hs = 0; hs < kHeadsMax; ++hs) {
+                        mc[hs] = WR_NEG_SENTINEL;
+                        lc[hs] = 0.f;
+                        if (lane < nc && hs < heads_here) {
                             const float *tr = p.ws + ((first_item + lane) * 8 + hs) * kTripleStride;
-                            mc = __ldcg(tr);
-                            lc = __ldcg(tr + 1);
+                            mc[hs] = __ldcg(tr);
+                            lc[hs] = __ldcg(tr + 1);
                         }
+                    }
+#pragma unroll
+                    for (uint32_t hs = 0; hs < kHeadsMax; ++hs) {
+                        if (hs >= heads_here) break;
+                        // all chunk rows of this head in flight at once, merged in chunk order
                         float4 ov[kMaxChunks];
 #pragma unroll
                         for (int j = 0; j < kMaxChunks; ++j)
@@ -458,12 +467,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
                                               p.ws + ((first_item + j) * 8 + hs) * kTripleStride +
                                               WR_CUDA_TRIPLE_PAD) + lane)
                                         : make_float4(0.f, 0.f, 0.f, 0.f);
-                        float mstar = mc;
+                        float mstar = mc[hs];
 #pragma unroll
                         for (int off = 16; off > 0; off >>= 1)
                             mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, off));
-                        const float wgt = (mc == WR_NEG_SENTINEL) ? 0.f : __expf(mc - mstar);
-                        const float wl = wgt * lc;
+                        const float wgt = (mc[hs] == WR_NEG_SENTINEL) ? 0.f : __expf(mc[hs] - mstar);
+                        const float wl = wgt * lc[hs];
                         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                         float L = 0.f;
 #pragma unroll

@@ -235,6 +235,15 @@ extern "C" int wr_cuda_kv_create(wr_cuda_ctx *ctx, uint32_t n_layers, uint32_t n
         delete kv;
         return e == cudaErrorMemoryAllocation ? WR_CUDA_ERR_NOMEM : WR_CUDA_ERR_INTERNAL;
     }
+    // A layer whose pages came out of the pool back to back needs no table
+    // lookup on the device: page i sits at base + i * page_bytes.
+    kv->contig.assign(n_layers, 1);
+    const uint64_t pb = wr_page_bytes(n_kv_heads, head_dim);
+    for (uint32_t L = 0; L < n_layers; ++L)
+        for (uint32_t i = 1; i < kv->n_pages; ++i)
+            if ((char *)kv->pages[(size_t)L * kv->n_pages + i] !=
+                (char *)kv->pages[(size_t)L * kv->n_pages + i - 1] + pb)
+                kv->contig[L] = 0;
     ctx->live_kv++;
     *out = kv;
     return WR_CUDA_OK;
@@ -367,52 +376,67 @@ struct append_params {
     uint32_t rope;
 };
 
-// One thread per (token, pair j).  The pair's cos/sin depend only on
-// (position, j), so they are computed once and reused for every KV head, the
-// V copy and every Q head of that token.
-__global__ void __launch_bounds__(128) rope_kv_append_kernel(const append_params p)
-{
-    const uint32_t half = p.hd / 2u;
-    const uint64_t total = (uint64_t)p.n_sess * p.n_tokens * half;
-    const float ln_theta = wrmath::log_ref(p.theta);
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
-         i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint32_t j = (uint32_t)(i % half);
-        const uint64_t tok_idx = i / half;                       // s * n_tokens + t
-        const uint32_t s = (uint32_t)(tok_idx / p.n_tokens);
-        const uint32_t t = (uint32_t)(tok_idx % p.n_tokens);
-        const uint32_t row = p.b.seq_len[s] + t;                 // absolute position = cache row
-        const bool rot = p.rope && j < p.n_rot;
-        float sn = 0.0f, cs = 1.0f;
-        if (rot) wrmath::rope_angle(row, j, p.hd, ln_theta, sn, cs);
+// A pair's cos/sin depend only on (position, j): they are computed once per
+// token and reused for every KV head and every Q head of that token.
+//
+// One CTA per token.  Phase 1: thread j < hd/2 evaluates the pair's angle
+// (the reference's range reduction is a serial float loop, so this is the
+// latency of the kernel).  Phase 2: every thread takes (head, pair) work
+// items across K, V and Q — independent loads and stores.
+constexpr int kAppendThreads = 256;
 
-        char *page = (char *)p.b.pages[s][row / kPageTokens];
-        const uint32_t tk = row % kPageTokens;
-        const uint32_t off0 = wr_elem_off(tk, j, p.hd);
-        const uint32_t off1 = wr_elem_off(tk, j + half, p.hd);
-        const float *krow = p.k_rows + tok_idx * p.n_kv * p.hd;
-        const float *vrow = p.v_rows + tok_idx * p.n_kv * p.hd;
-        for (uint32_t h = 0; h < p.n_kv; ++h) {
-            float x0 = krow[h * p.hd + j], x1 = krow[h * p.hd + j + half];
-            float y0 = x0, y1 = x1;
-            if (rot) {   // kernels.c:1406-1407, products rounded separately
-                y0 = wrmath::sub(wrmath::mul(x0, cs), wrmath::mul(x1, sn));
-                y1 = wrmath::add(wrmath::mul(x0, sn), wrmath::mul(x1, cs));
-            }
-            char *kb = page + wr_block_off(h, 0, p.hd);
-            *(uint16_t *)(kb + off0) = wr_f32_to_f16_trunc(y0);
-            *(uint16_t *)(kb + off1) = wr_f32_to_f16_trunc(y1);
-            char *vb = page + wr_block_off(h, 1, p.hd);
-            *(uint16_t *)(vb + off0) = wr_f32_to_f16_trunc(vrow[h * p.hd + j]);
-            *(uint16_t *)(vb + off1) = wr_f32_to_f16_trunc(vrow[h * p.hd + j + half]);
+__global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const append_params p)
+{
+    extern __shared__ float trig[];                              // cs[half], sn[half]
+    const uint32_t half = p.hd / 2u;
+    const uint32_t tok_idx = blockIdx.x;                         // s * n_tokens + t
+    const uint32_t s = tok_idx / p.n_tokens, t = tok_idx % p.n_tokens;
+    const uint32_t row = p.b.seq_len[s] + t;                     // absolute position = cache row
+    float *cs_tab = trig, *sn_tab = trig + half;
+    if (p.rope) {
+        const float ln_theta = wrmath::log_ref(p.theta);
+        for (uint32_t j = threadIdx.x; j < p.n_rot; j += blockDim.x) {
+            float sn, cs;
+            wrmath::rope_angle(row, j, p.hd, ln_theta, sn, cs);
+            cs_tab[j] = cs;
+            sn_tab[j] = sn;
         }
-        if (p.q_rows && rot) {
-            float *qrow = p.q_rows + tok_idx * p.n_q * p.hd;
-            for (uint32_t h = 0; h < p.n_q; ++h) {
-                float x0 = qrow[h * p.hd + j], x1 = qrow[h * p.hd + j + half];
-                qrow[h * p.hd + j] = wrmath::sub(wrmath::mul(x0, cs), wrmath::mul(x1, sn));
-                qrow[h * p.hd + j + half] = wrmath::add(wrmath::mul(x0, sn), wrmath::mul(x1, cs));
-            }
+    }
+    char *page = (char *)p.b.pages[s][row / kPageTokens];
+    const uint32_t tk = row % kPageTokens;
+    __syncthreads();
+
+    const float *__restrict__ krow = p.k_rows + (size_t)tok_idx * p.n_kv * p.hd;
+    const float *__restrict__ vrow = p.v_rows + (size_t)tok_idx * p.n_kv * p.hd;
+    const uint32_t kv_work = p.n_kv * half;
+    for (uint32_t i = threadIdx.x; i < kv_work; i += blockDim.x) {
+        const uint32_t h = i / half, j = i % half;
+        const bool rot = p.rope && j < p.n_rot;
+        const float x0 = krow[h * p.hd + j], x1 = krow[h * p.hd + j + half];
+        const float v0 = vrow[h * p.hd + j], v1 = vrow[h * p.hd + j + half];
+        float y0 = x0, y1 = x1;
+        if (rot) {   // kernels.c:1406-1407, products rounded separately
+            const float cs = cs_tab[j], sn = sn_tab[j];
+            y0 = wrmath::sub(wrmath::mul(x0, cs), wrmath::mul(x1, sn));
+            y1 = wrmath::add(wrmath::mul(x0, sn), wrmath::mul(x1, cs));
+        }
+        const uint32_t off0 = wr_elem_off(tk, j, p.hd), off1 = wr_elem_off(tk, j + half, p.hd);
+        char *kb = page + wr_block_off(h, 0, p.hd);
+        char *vb = page + wr_block_off(h, 1, p.hd);
+        *(uint16_t *)(kb + off0) = wr_f32_to_f16_trunc(y0);
+        *(uint16_t *)(kb + off1) = wr_f32_to_f16_trunc(y1);
+        *(uint16_t *)(vb + off0) = wr_f32_to_f16_trunc(v0);
+        *(uint16_t *)(vb + off1) = wr_f32_to_f16_trunc(v1);
+    }
+    if (p.q_rows && p.rope) {
+        float *qrow = p.q_rows + (size_t)tok_idx * p.n_q * p.hd;
+        const uint32_t q_work = p.n_q * p.n_rot;
+        for (uint32_t i = threadIdx.x; i < q_work; i += blockDim.x) {
+            const uint32_t h = i / p.n_rot, j = i % p.n_rot;
+            const float cs = cs_tab[j], sn = sn_tab[j];
+            const float x0 = qrow[h * p.hd + j], x1 = qrow[h * p.hd + j + half];
+            qrow[h * p.hd + j] = wrmath::sub(wrmath::mul(x0, cs), wrmath::mul(x1, sn));
+            qrow[h * p.hd + j + half] = wrmath::add(wrmath::mul(x0, sn), wrmath::mul(x1, cs));
         }
     }
 }
@@ -455,10 +479,7 @@ int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
     p.n_rot = (n_rot_pairs >= 1 && n_rot_pairs < half) ? n_rot_pairs : half;  // kernels.c:1381-1383
     p.theta = (theta_base < 1.0f) ? 10000.0f : theta_base;                    // kernels.c:1374
     p.rope = (flags & WR_CUDA_APPEND_ROPE) ? 1u : 0u;
-    const uint64_t work = (uint64_t)n_sess * n_tokens * half;
-    const uint32_t blocks =
-        (uint32_t)std::min<uint64_t>((work + 127) / 128, (uint64_t)ctx->sm_count * 32);
-    rope_kv_append_kernel<<<blocks, 128, 0, ctx->stream>>>(p);
+    rope_kv_append_kernel<<<n_sess * n_tokens, kAppendThreads, hd * sizeof(float), ctx->stream>>>(p);
     ctx->launches++;
     WR_CUDA_TRY(cudaGetLastError());
     return WR_CUDA_OK;

@@ -12,6 +12,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "rope_reduce.h"
+
 namespace wrmath {
 
 __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
@@ -68,12 +70,10 @@ __device__ inline float sqrt_ref(float x)
 
 // src/core/mathx.c:124-127: the reduction is a float loop whose rounding
 // accumulates, so it is run as written (fmodf would not give the same bits).
-__device__ inline float reduce_pi(float x)
-{
-    while (x > kPi) x = sub(x, kTwoPi);
-    while (x < -kPi) x = add(x, kTwoPi);
-    return x;
-}
+//
+// wr_reduce_pi (rope_reduce.h) returns the bits of that loop without running
+// its thousands of dependent subtractions.
+__device__ inline float reduce_pi(float x) { return wr_reduce_pi(x); }
 
 // src/core/mathx.c:124-147 after reduction; both series share x2.
 __device__ inline void sincos_ref(float angle, float &sn, float &cs)

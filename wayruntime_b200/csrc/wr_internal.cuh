@@ -90,6 +90,7 @@ struct wr_cuda_kv {
     uint32_t n_layers = 0, n_kv = 0, hd = 0, max_ctx = 0, n_pages = 0;
     std::vector<void *> pages;       // n_layers * n_pages page pointers (host copy)
     uint64_t *d_pages = nullptr;     // same table on the device
+    std::vector<uint8_t> contig;     // per layer: pages are consecutive in memory
     size_t pool_index = 0;
 };
 
@@ -185,6 +186,25 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Same copy with an L2 eviction policy: streamed-once data (K/V tiles of a
+// decode step) is marked evict-first so that it does not push the small
+// re-used data (partials, page tables, queries) out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void *dst_smem, const void *src, uint32_t bytes,
+                                              uint64_t *bar, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
 
