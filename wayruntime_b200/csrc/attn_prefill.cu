@@ -1,8 +1,512 @@
-// attn_prefill.cu — causal prefill attention (placeholder until the kernel lands).
+// attn_prefill.cu — causal prefill attention on the 5th-generation tensor cores.
+//
+// The reference has no batched causal op: its prefill runs one single-token
+// attention per new token (src/core/session.c:599-630), token i seeing cache
+// rows [0, p0+i] through wri_op_gqa_attention (src/core/kernels.c:1414-1527).
+// This kernel computes the same rows all at once as a dense contraction.
+//
+// One CTA = one (q head, 128-token tile).  Data flow:
+//   * TMA warp: the Q tile through a 2-D tensor map (cp.async.bulk.tensor,
+//     128-byte swizzle, out-of-range rows zero-filled), then K|V tiles of 64
+//     keys straight from the paged cache with linear bulk copies — the page
+//     layout already is the swizzled operand image the tensor core reads;
+//   * MMA warp (one thread): S = Q.K^T as tcgen05.mma M128 N64 K16 x8 into
+//     TMEM, later O += P.V as M128 N128 K16 x4 (V is the MN-major operand);
+//     completion is signalled with tcgen05.commit on mbarriers;
+//   * four softmax warps, one thread per query row: tcgen05.ld the 64 scores,
+//     mask (causal / window), exponentiate against a running reference max,
+//     write P as F16 into shared memory in operand order.  O stays in TMEM;
+//     it is rescaled only when the row max has grown by more than 8 (exact:
+//     the final division by l uses the same reference max), and read once at
+//     the end, normalised and stored as F32.
+// Every wait has a time limit; on expiry the kernel records an error, still
+// frees its TMEM and returns.
+#include <cuda.h>
+
+#include <algorithm>
+
 #include "wr_internal.cuh"
 
-extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *, wr_cuda_kv *, uint32_t, uint32_t, uint32_t,
-                                    const void *, int, float *, uint32_t, float, uint32_t, int)
+namespace {
+
+constexpr int kHd = 128;
+constexpr int kBM = 128;                 // query rows per CTA
+constexpr int kBN = 64;                  // keys per tile = page tokens
+constexpr int kStages = 3;
+constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = kSoftmaxThreads + 64;   // + TMA warp + MMA warp
+constexpr uint32_t kQHalfBytes = kBM * 128;      // 64 dims of 128 rows
+constexpr uint32_t kKVBlock = kBN * kHd * 2;     // 16 KB: one K or V tile
+constexpr uint32_t kPBytes = kBM * kBN * 2;      // 16 KB
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kTmemS = 0, kTmemO = 128;
+constexpr float kRescaleThreshold = 8.0f;        // in units of the natural-log score
+
+struct prefill_params {
+    const uint64_t *pages;      // page table of (session, layer)
+    float *out;                 // [n, n_q, hd] F32
+    int *err;
+    uint32_t n, p0, n_q, group, window, n_qtiles;
+    float scale;
+};
+
+struct smem_layout {
+    alignas(1024) uint8_t q[2 * kQHalfBytes];            // 32 KB
+    alignas(1024) uint8_t kv[kStages][2 * kKVBlock];     // K then V per stage
+    alignas(1024) uint8_t p[2][kPBytes];
+    alignas(8) uint64_t bar_q;
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t s_full;
+    uint64_t p_ready[2];
+    uint64_t o_done;
+    uint32_t tmem_base;
+    int failed;
+};
+
+// ---- tcgen05 / TMA wrappers ------------------------------------------------
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
 {
-    return WR_CUDA_ERR_UNSUPPORTED;
+    // start address [0,14) (>>4), leading byte offset [16,30) (>>4), stride byte
+    // offset [32,46) (>>4), descriptor version 1 at [46,48), 128-byte swizzle (2) at [61,64)
+    const uint64_t lo = (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16);
+    const uint64_t hi = (uint64_t)(sbo_bytes >> 4) | (1ull << 14) | (2ull << 29);
+    return lo | (hi << 32);
+}
+// F16 x F16 -> F32 instruction descriptor: c_format F32 (bit 4), N>>3 at [17,23), M>>4 at [24,29),
+// bit 16 = B operand is MN-major.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t m, uint32_t n, bool b_mn_major)
+{
+    return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32])
+{
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+          "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+          "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+          "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+          "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+          "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// Tiled 2-D tensor copy global -> shared (no multicast).  The inner coordinate
+// x is in elements; x * 2 bytes is a multiple of 16 for every caller.
+__device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *map, int x, int y,
+                                            uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// ---- the kernel ------------------------------------------------------------
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefill_params p)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    smem_layout &sm = *reinterpret_cast<smem_layout *>(smem_raw);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // Heaviest tiles first: the last query tile of the prompt has the most keys.
+    const uint32_t qt = p.n_qtiles - 1 - blockIdx.x / p.n_q;
+    const uint32_t qh = blockIdx.x % p.n_q;
+    const uint32_t kvh = qh / p.group;
+    const uint32_t tok0 = qt * kBM;
+    const uint32_t rows_here = min((uint32_t)kBM, p.n - tok0);
+    // keys visible to this tile: [key_first, key_end)
+    const uint32_t key_end = p.p0 + tok0 + rows_here;
+    uint32_t key_first = 0;
+    if (p.window > 0 && p.p0 + tok0 + 1 > p.window) key_first = p.p0 + tok0 + 1 - p.window;
+    const uint32_t t_first = key_first / kBN;
+    const uint32_t n_kt = (key_end + kBN - 1) / kBN - t_first;     // >= 1
+
+    if (tid == 0) {
+        mbar_init(&sm.bar_q, 1);
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&sm.full[i], 1);
+            mbar_init(&sm.empty[i], 1);
+        }
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.p_ready[0], kSoftmaxThreads);
+        mbar_init(&sm.p_ready[1], kSoftmaxThreads);
+        mbar_init(&sm.o_done, 1);
+        sm.failed = 0;
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA warp
+        if (lane == 0) {
+            mbar_expect_tx(&sm.bar_q, 2 * kQHalfBytes);
+            tma_load_2d(sm.q, &q_map, (int)(qh * kHd), (int)tok0, &sm.bar_q);
+            tma_load_2d(sm.q + kQHalfBytes, &q_map, (int)(qh * kHd + 64), (int)tok0, &sm.bar_q);
+            for (uint32_t i = 0; i < n_kt; ++i) {
+                const uint32_t st = i % kStages;
+                if (i >= kStages && !mbar_wait(&sm.empty[st], ((i / kStages) - 1) & 1)) {
+                    atomicExch(p.err, 11);
+                    sm.failed = 1;
+                    break;
+                }
+                const char *src = (const char *)p.pages[t_first + i] + wr_block_off(kvh, 0, kHd);
+                mbar_expect_tx(&sm.full[st], 2 * kKVBlock);
+                bulk_g2s(sm.kv[st], src, 2 * kKVBlock, &sm.full[st]);     // K and V are adjacent
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA warp
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
+            const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
+            const uint32_t q_addr = smem_u32(sm.q);
+            bool ok = mbar_wait(&sm.bar_q, 0);
+            auto issue_s = [&](uint32_t i) {
+                const uint32_t k_addr = smem_u32(sm.kv[i % kStages]);
+#pragma unroll
+                for (int kk = 0; kk < kHd / 16; ++kk) {
+                    const uint32_t half = kk >> 2, off = (kk & 3) * 32;
+                    umma_f16(tmem + kTmemS,
+                             umma_desc(q_addr + half * kQHalfBytes + off, 16, 1024),
+                             umma_desc(k_addr + half * (kBN * 128) + off, 16, 1024), idesc_s, kk > 0);
+                }
+                umma_commit(&sm.s_full);
+            };
+            if (ok) ok = mbar_wait(&sm.full[0], 0);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (uint32_t i = 0; ok && i < n_kt; ++i) {
+                // softmax of tile i has read S and written P[i&1]
+                ok = mbar_wait(&sm.p_ready[i & 1], (i >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                if (i + 1 < n_kt) {
+                    ok = mbar_wait(&sm.full[(i + 1) % kStages], ((i + 1) / kStages) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(i + 1);                       // S of the next tile first: softmax can start
+                }
+                const uint32_t v_addr = smem_u32(sm.kv[i % kStages]) + kKVBlock;
+                const uint32_t p_addr = smem_u32(sm.p[i & 1]);
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk)
+                    umma_f16(tmem + kTmemO, umma_desc(p_addr + kk * 32, 16, 1024),
+                             umma_desc(v_addr + kk * 2048, 8192, 1024), idesc_o, (i > 0) || (kk > 0));
+                umma_commit(&sm.empty[i % kStages]);      // K/V stage may be refilled
+                umma_commit(&sm.o_done);                  // O holds tiles 0..i
+            }
+            if (!ok) {
+                atomicExch(p.err, 12);
+                sm.failed = 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------- softmax: thread = row
+        const uint32_t row = tid;                           // 0..127 = TMEM lane
+        const uint32_t lane_base = (warp * 32u) << 16;      // this warp's TMEM lanes
+        const uint32_t qpos = p.p0 + tok0 + row;            // absolute position of this query
+        uint32_t lo_key = 0;
+        if (p.window > 0 && qpos + 1 > p.window) lo_key = qpos + 1 - p.window;
+        const float sc = p.scale;
+        float m_ref = WR_NEG_SENTINEL, l = 0.f;
+        bool ok = true;
+        for (uint32_t i = 0; i < n_kt; ++i) {
+            ok = mbar_wait(&sm.s_full, i & 1);
+            if (!ok) break;
+            tc_fence_after();
+            float s[kBN];
+            {
+                float a[32], b[32];
+                tmem_ld32(tmem + lane_base + kTmemS, a);
+                tmem_ld32(tmem + lane_base + kTmemS + 32, b);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    s[j] = a[j] * sc;
+                    s[32 + j] = b[j] * sc;
+                }
+            }
+            const uint32_t key0 = (t_first + i) * kBN;
+            // tiles that no row's causal or window limit cuts through need no masking
+            const bool edge = (key0 + kBN - 1 > p.p0 + tok0) || (p.window > 0);
+            float tmax = WR_NEG_SENTINEL;
+            if (edge) {
+#pragma unroll
+                for (int j = 0; j < kBN; ++j) {
+                    const uint32_t key = key0 + j;
+                    if (key > qpos || key < lo_key) s[j] = WR_NEG_SENTINEL;
+                    tmax = fmaxf(tmax, s[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < kBN; ++j) tmax = fmaxf(tmax, s[j]);
+            }
+            // Rescale the accumulator only when the reference max must move.
+            if (tmax > m_ref + kRescaleThreshold || (m_ref == WR_NEG_SENTINEL && tmax > WR_NEG_SENTINEL)) {
+                if (m_ref != WR_NEG_SENTINEL) {
+                    const float a = __expf(m_ref - tmax);
+                    l *= a;
+                    // O must hold every earlier tile before it is touched
+                    ok = mbar_wait(&sm.o_done, (i - 1) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < kHd; c += 32) {
+                        float o[32];
+                        tmem_ld32(tmem + lane_base + kTmemO + c, o);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) o[j] *= a;
+                        tmem_st32(tmem + lane_base + kTmemO + c, o);
+                    }
+                }
+                m_ref = tmax;
+            }
+            // P = exp(s - m_ref) as F16 in operand order: row `row`, 8 chunks of 8 keys
+            uint8_t *prow = sm.p[i & 1] + row * 128;
+            float psum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float s0 = s[c * 8 + 2 * e], s1 = s[c * 8 + 2 * e + 1];
+                    const float p0 = (s0 == WR_NEG_SENTINEL) ? 0.f : __expf(s0 - m_ref);
+                    const float p1 = (s1 == WR_NEG_SENTINEL) ? 0.f : __expf(s1 - m_ref);
+                    const __half2 h = __floats2half2_rn(p0, p1);
+                    // the denominator sums what the tensor core will multiply
+                    const float2 hf = __half22float2(h);
+                    psum += hf.x + hf.y;
+                    w[e] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l += psum;
+            if (i == n_kt - 1 && (key_end % kBN) != 0) {
+                // Cache rows past the last key were never written for this
+                // prompt (or belong to a rolled-back step): clear them in the
+                // staged V tile so that 0 * garbage cannot make a NaN.
+                ok = mbar_wait(&sm.full[i % kStages], (i / kStages) & 1);
+                if (!ok) break;
+                if (row < kBN && key0 + row >= key_end) {
+                    uint8_t *vrow = sm.kv[i % kStages] + kKVBlock + row * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        *reinterpret_cast<uint4 *>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4 *>(vrow + 8192 + c * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                }
+            }
+            fence_proxy_async();          // P (generic writes) is read by the tensor core
+            tc_fence_before();
+            mbar_arrive(&sm.p_ready[i & 1]);
+        }
+        if (ok) {
+            ok = mbar_wait(&sm.o_done, (n_kt - 1) & 1);
+            if (ok) {
+                tc_fence_after();
+                const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+                float *orow = p.out + ((size_t)(tok0 + row) * p.n_q + qh) * kHd;
+#pragma unroll 1
+                for (int c = 0; c < kHd; c += 32) {
+                    float o[32];
+                    tmem_ld32(tmem + lane_base + kTmemO + c, o);
+                    if (row < rows_here) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4 *>(orow + c + j) =
+                                make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            atomicExch(p.err, 13);
+            sm.failed = 1;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// F32 -> F16 (round to nearest) copy of Q for callers that hold F32 queries.
+__global__ void q_to_f16_kernel(const float *__restrict__ src, __half *__restrict__ dst, size_t n)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = __float2half_rn(src[i]);
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+encode_tiled_fn get_encode_tiled()
+{
+    static encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (encode_tiled_fn)sym;
+        else
+            (void)cudaGetLastError();
+    }
+    return fn;
+}
+
+}  // namespace
+
+extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t layer, uint32_t p0,
+                                    uint32_t n, const void *q, int q_dtype, float *out,
+                                    uint32_t n_q_heads, float scale_override, uint32_t window, int mem)
+{
+    if (!ctx || !kv || kv->ctx != ctx || !q || !out) return WR_CUDA_ERR_INVAL;
+    if (layer >= kv->n_layers) return WR_CUDA_ERR_INVAL;
+    if (q_dtype != WR_CUDA_F32 && q_dtype != WR_CUDA_F16) return WR_CUDA_ERR_INVAL;
+    if (mem != WR_CUDA_MEM_HOST && mem != WR_CUDA_MEM_DEVICE) return WR_CUDA_ERR_INVAL;
+    if (n == 0) return WR_CUDA_OK;
+    if (n_q_heads == 0 || n_q_heads % kv->n_kv != 0) return WR_CUDA_ERR_INVAL;   // kernels.c:1429-1432
+    if (kv->hd != kHd) return WR_CUDA_ERR_UNSUPPORTED;       // tensor-core tiles are built for head_dim 128
+    std::lock_guard<std::mutex> g(ctx->lock);
+    if ((uint64_t)p0 + n > ctx->attn_max_seq) return WR_CUDA_ERR_LIMIT;           // kernels.c:1444
+    if ((uint64_t)p0 + n > kv->max_ctx) return WR_CUDA_ERR_INVAL;                 // capacity, kernels.c:1449-1454
+    encode_tiled_fn encode = get_encode_tiled();
+    if (!encode) return WR_CUDA_ERR_INTERNAL;
+    WR_CUDA_TRY(cudaSetDevice(ctx->device));
+
+    const size_t elems = (size_t)n * n_q_heads * kHd;
+    const size_t q_in_bytes = elems * (q_dtype == WR_CUDA_F32 ? 4 : 2);
+    const size_t q16_bytes = (elems * 2 + 255) & ~(size_t)255;
+    const size_t out_bytes = elems * 4;
+    // staging layout: [q as F16][q as given (host callers / F32)][out (host callers)]
+    size_t need = 0;
+    const bool convert = (q_dtype == WR_CUDA_F32);
+    const bool host = (mem == WR_CUDA_MEM_HOST);
+    if (convert) need += q16_bytes;
+    if (host) need += ((q_in_bytes + 255) & ~(size_t)255) + out_bytes;
+    if (need) {
+        int rc = wr_ctx_reserve_stage(ctx, need, 0);
+        if (rc != WR_CUDA_OK) return rc;
+    }
+    char *stage = (char *)ctx->stage_dev;
+    size_t off = 0;
+    __half *q16 = nullptr;
+    if (convert) {
+        q16 = (__half *)(stage + off);
+        off += q16_bytes;
+    }
+    const void *dq = q;
+    float *dout = out;
+    if (host) {
+        dq = stage + off;
+        off += (q_in_bytes + 255) & ~(size_t)255;
+        dout = (float *)(stage + off);
+        WR_CUDA_TRY(cudaMemcpyAsync((void *)dq, q, q_in_bytes, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    if (convert) {
+        const uint32_t blocks = (uint32_t)std::min<size_t>((elems + 255) / 256, (size_t)ctx->sm_count * 16);
+        q_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>((const float *)dq, q16, elems);
+        ctx->launches++;
+        WR_CUDA_TRY(cudaGetLastError());
+    } else {
+        q16 = (__half *)dq;
+    }
+    if (((uintptr_t)q16 & 15u) || ((uintptr_t)dout & 15u)) return WR_CUDA_ERR_INVAL;
+
+    CUtensorMap q_map;
+    const cuuint64_t dims[2] = {(cuuint64_t)n_q_heads * kHd, (cuuint64_t)n};
+    const cuuint64_t strides[1] = {(cuuint64_t)n_q_heads * kHd * 2};
+    const cuuint32_t box[2] = {64, kBM};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)q16, dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return WR_CUDA_ERR_INTERNAL;
+
+    prefill_params p;
+    p.pages = kv->d_pages + (size_t)layer * kv->n_pages;
+    p.out = dout;
+    p.err = ctx->dev_err;
+    p.n = n;
+    p.p0 = p0;
+    p.n_q = n_q_heads;
+    p.group = n_q_heads / kv->n_kv;
+    p.window = window;
+    p.n_qtiles = (n + kBM - 1) / kBM;
+    p.scale = (scale_override > 0.0f) ? scale_override : 1.0f / sqrtf((float)kHd);   // kernels.c:1457-1459
+    if (!(ctx->attr_flags & 2u)) {
+        WR_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_hd128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)sizeof(smem_layout)));
+        ctx->attr_flags |= 2u;
+    }
+    attn_prefill_hd128_kernel<<<p.n_qtiles * n_q_heads, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, p);
+    ctx->launches++;
+    WR_CUDA_TRY(cudaGetLastError());
+    if (host) {
+        WR_CUDA_TRY(cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    }
+    return WR_CUDA_OK;
 }
