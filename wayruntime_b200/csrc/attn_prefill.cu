@@ -5,20 +5,23 @@
 // rows [0, p0+i] through wri_op_gqa_attention (src/core/kernels.c:1414-1527).
 // This kernel computes the same rows all at once as a dense contraction.
 //
-// One CTA = one (q head, 128-token tile).  Data flow:
-//   * TMA warp: the Q tile through a 2-D tensor map (cp.async.bulk.tensor,
+// One CTA = one 128-token query tile of TWO q heads of the same GQA group (a
+// lone head when the group size is odd), so every K|V tile staged in shared
+// memory feeds both.  Data flow:
+//   * TMA warp: the two Q tiles through a 2-D tensor map (cp.async.bulk.tensor,
 //     128-byte swizzle, out-of-range rows zero-filled), then K|V tiles of 64
 //     keys straight from the paged cache with linear bulk copies — the page
 //     layout already is the swizzled operand image the tensor core reads;
-//   * MMA warp (one thread): S = Q.K^T as tcgen05.mma M128 N64 K16 x8 into
-//     TMEM, later O += P.V as M128 N128 K16 x4 (V is the MN-major operand);
-//     completion is signalled with tcgen05.commit on mbarriers;
-//   * four softmax warps, one thread per query row: tcgen05.ld the 64 scores,
-//     mask (causal / window), exponentiate against a running reference max,
-//     write P as F16 into shared memory in operand order.  O stays in TMEM;
-//     it is rescaled only when the row max has grown by more than 8 (exact:
-//     the final division by l uses the same reference max), and read once at
-//     the end, normalised and stored as F32.
+//   * MMA warp (one thread): per head, S = Q.K^T as tcgen05.mma M128 N64 K16 x8
+//     into TMEM and O += P.V as M128 N128 K16 x4 (V is the MN-major operand);
+//     completion is signalled with tcgen05.commit on mbarriers.  The two heads
+//     alternate, so the tensor core works for one while the other is in softmax;
+//   * two softmax warpgroups (one per head), one thread per query row:
+//     tcgen05.ld the 64 scores, mask (causal / window), exponentiate against a
+//     running reference max, write P as F16 into shared memory in operand
+//     order.  O stays in TMEM; it is rescaled only when the row max has grown
+//     by more than 2^8 (exact: the final division by l uses the same reference
+//     max), and read once at the end, normalised and stored as F32.
 // Every wait has a time limit; on expiry the kernel records an error, still
 // frees its TMEM and returns.
 #include <cuda.h>
@@ -30,38 +33,40 @@
 namespace {
 
 constexpr int kHd = 128;
-constexpr int kBM = 128;                 // query rows per CTA
+constexpr int kBM = 128;                 // query rows per head per CTA
 constexpr int kBN = 64;                  // keys per tile = page tokens
 constexpr int kStages = 3;
-constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = kSoftmaxThreads + 64;   // + TMA warp + MMA warp
+constexpr int kGroupThreads = 128;       // one softmax warpgroup
+constexpr int kThreads = 2 * kGroupThreads + 64;     // + TMA warp + MMA warp
 constexpr uint32_t kQHalfBytes = kBM * 128;      // 64 dims of 128 rows
+constexpr uint32_t kQBytes = 2 * kQHalfBytes;    // 32 KB per head
 constexpr uint32_t kKVBlock = kBN * kHd * 2;     // 16 KB: one K or V tile
 constexpr uint32_t kPBytes = kBM * kBN * 2;      // 16 KB
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kTmemS = 0, kTmemO = 128;
-constexpr float kRescaleThreshold = 8.0f;        // in units of the natural-log score
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemS = 0;                   // S of head h at columns 64*h
+constexpr uint32_t kTmemO = 128;                 // O of head h at columns 128 + 128*h
+constexpr float kRescaleLog2 = 8.0f;             // move the reference max when it is 2^8 behind
+constexpr float kLog2e = 1.4426950408889634f;
 
 struct prefill_params {
     const uint64_t *pages;      // page table of (session, layer)
     float *out;                 // [n, n_q, hd] F32
     int *err;
-    uint32_t n, p0, n_q, group, window, n_qtiles;
-    float scale;
+    uint32_t n, p0, n_q, n_kv, group, n_pairs, window, n_qtiles;
+    float scale_log2;           // score scale * log2(e)
 };
 
 struct smem_layout {
-    alignas(1024) uint8_t q[2 * kQHalfBytes];            // 32 KB
+    alignas(1024) uint8_t q[2][kQBytes];                 // per head
     alignas(1024) uint8_t kv[kStages][2 * kKVBlock];     // K then V per stage
-    alignas(1024) uint8_t p[2][kPBytes];
+    alignas(1024) uint8_t p[2][2][kPBytes];              // [head][tile parity]
     alignas(8) uint64_t bar_q;
     uint64_t full[kStages];
     uint64_t empty[kStages];
-    uint64_t s_full;
-    uint64_t p_ready[2];
-    uint64_t o_done;
+    uint64_t s_full[2];
+    uint64_t p_ready[2][2];
+    uint64_t o_done[2];
     uint32_t tmem_base;
-    int failed;
 };
 
 // ---- tcgen05 / TMA wrappers ------------------------------------------------
@@ -97,9 +102,12 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar)
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32])
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 32 consecutive F32 columns of this thread's TMEM lane (no wait).
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, float *v)
 {
-    uint32_t r[32];
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -110,29 +118,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32])
           "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
           "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32])
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float *v)
 {
+    const uint32_t *r = reinterpret_cast<const uint32_t *>(v);
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
         "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
-          "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
-          "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
-          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
-          "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
-          "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
-          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
-          "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 // Tiled 2-D tensor copy global -> shared (no multicast).  The inner coordinate
 // x is in elements; x * 2 bytes is a multiple of 16 for every caller.
@@ -156,9 +160,12 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // Heaviest tiles first: the last query tile of the prompt has the most keys.
-    const uint32_t qt = p.n_qtiles - 1 - blockIdx.x / p.n_q;
-    const uint32_t qh = blockIdx.x % p.n_q;
-    const uint32_t kvh = qh / p.group;
+    const uint32_t per_tile = p.n_kv * p.n_pairs;
+    const uint32_t qt = p.n_qtiles - 1 - blockIdx.x / per_tile;
+    const uint32_t kvh = (blockIdx.x % per_tile) / p.n_pairs;
+    const uint32_t pair = blockIdx.x % p.n_pairs;
+    const uint32_t head0 = kvh * p.group + 2 * pair;
+    const uint32_t n_heads = min(2u, p.group - 2 * pair);          // 1 for the odd head of a group
     const uint32_t tok0 = qt * kBM;
     const uint32_t rows_here = min((uint32_t)kBM, p.n - tok0);
     // keys visible to this tile: [key_first, key_end)
@@ -174,11 +181,12 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             mbar_init(&sm.full[i], 1);
             mbar_init(&sm.empty[i], 1);
         }
-        mbar_init(&sm.s_full, 1);
-        mbar_init(&sm.p_ready[0], kSoftmaxThreads);
-        mbar_init(&sm.p_ready[1], kSoftmaxThreads);
-        mbar_init(&sm.o_done, 1);
-        sm.failed = 0;
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(&sm.s_full[h], 1);
+            mbar_init(&sm.p_ready[h][0], kGroupThreads);
+            mbar_init(&sm.p_ready[h][1], kGroupThreads);
+            mbar_init(&sm.o_done[h], 1);
+        }
         fence_barrier_init();
     }
     if (warp == 0) {
@@ -191,17 +199,19 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------ TMA warp
         if (lane == 0) {
-            mbar_expect_tx(&sm.bar_q, 2 * kQHalfBytes);
-            tma_load_2d(sm.q, &q_map, (int)(qh * kHd), (int)tok0, &sm.bar_q);
-            tma_load_2d(sm.q + kQHalfBytes, &q_map, (int)(qh * kHd + 64), (int)tok0, &sm.bar_q);
+            mbar_expect_tx(&sm.bar_q, n_heads * kQBytes);
+            for (uint32_t h = 0; h < n_heads; ++h) {
+                tma_load_2d(sm.q[h], &q_map, (int)((head0 + h) * kHd), (int)tok0, &sm.bar_q);
+                tma_load_2d(sm.q[h] + kQHalfBytes, &q_map, (int)((head0 + h) * kHd + 64), (int)tok0,
+                            &sm.bar_q);
+            }
             for (uint32_t i = 0; i < n_kt; ++i) {
                 const uint32_t st = i % kStages;
                 if (i >= kStages && !mbar_wait(&sm.empty[st], ((i / kStages) - 1) & 1)) {
                     atomicExch(p.err, 11);
-                    sm.failed = 1;
                     break;
                 }
                 const char *src = (const char *)p.pages[t_first + i] + wr_block_off(kvh, 0, kHd);
@@ -209,79 +219,75 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 bulk_g2s(sm.kv[st], src, 2 * kKVBlock, &sm.full[st]);     // K and V are adjacent
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------ MMA warp
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
             const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
-            const uint32_t q_addr = smem_u32(sm.q);
             bool ok = mbar_wait(&sm.bar_q, 0);
-            auto issue_s = [&](uint32_t i) {
+            auto issue_s = [&](uint32_t h, uint32_t i) {
+                const uint32_t q_addr = smem_u32(sm.q[h]);
                 const uint32_t k_addr = smem_u32(sm.kv[i % kStages]);
 #pragma unroll
                 for (int kk = 0; kk < kHd / 16; ++kk) {
                     const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-                    umma_f16(tmem + kTmemS,
+                    umma_f16(tmem + kTmemS + 64 * h,
                              umma_desc(q_addr + half * kQHalfBytes + off, 16, 1024),
                              umma_desc(k_addr + half * (kBN * 128) + off, 16, 1024), idesc_s, kk > 0);
                 }
-                umma_commit(&sm.s_full);
+                umma_commit(&sm.s_full[h]);
             };
             if (ok) ok = mbar_wait(&sm.full[0], 0);
             if (ok) {
                 tc_fence_after();
-                issue_s(0);
+                for (uint32_t h = 0; h < n_heads; ++h) issue_s(h, 0);
             }
             for (uint32_t i = 0; ok && i < n_kt; ++i) {
-                // softmax of tile i has read S and written P[i&1]
-                ok = mbar_wait(&sm.p_ready[i & 1], (i >> 1) & 1);
-                if (!ok) break;
-                tc_fence_after();
-                if (i + 1 < n_kt) {
-                    ok = mbar_wait(&sm.full[(i + 1) % kStages], ((i + 1) / kStages) & 1);
+                for (uint32_t h = 0; ok && h < n_heads; ++h) {
+                    // softmax of (head h, tile i) has consumed S and written P
+                    ok = mbar_wait(&sm.p_ready[h][i & 1], (i >> 1) & 1);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_s(i + 1);                       // S of the next tile first: softmax can start
-                }
-                const uint32_t v_addr = smem_u32(sm.kv[i % kStages]) + kKVBlock;
-                const uint32_t p_addr = smem_u32(sm.p[i & 1]);
+                    if (i + 1 < n_kt) {
+                        ok = mbar_wait(&sm.full[(i + 1) % kStages], ((i + 1) / kStages) & 1);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_s(h, i + 1);            // next scores first: that softmax can start
+                    }
+                    const uint32_t v_addr = smem_u32(sm.kv[i % kStages]) + kKVBlock;
+                    const uint32_t p_addr = smem_u32(sm.p[h][i & 1]);
 #pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk)
-                    umma_f16(tmem + kTmemO, umma_desc(p_addr + kk * 32, 16, 1024),
-                             umma_desc(v_addr + kk * 2048, 8192, 1024), idesc_o, (i > 0) || (kk > 0));
-                umma_commit(&sm.empty[i % kStages]);      // K/V stage may be refilled
-                umma_commit(&sm.o_done);                  // O holds tiles 0..i
+                    for (int kk = 0; kk < kBN / 16; ++kk)
+                        umma_f16(tmem + kTmemO + 128 * h, umma_desc(p_addr + kk * 32, 16, 1024),
+                                 umma_desc(v_addr + kk * 2048, 8192, 1024), idesc_o, (i > 0) || (kk > 0));
+                    umma_commit(&sm.o_done[h]);                             // O_h holds tiles 0..i
+                    if (h + 1 == n_heads) umma_commit(&sm.empty[i % kStages]);  // stage may be refilled
+                }
             }
-            if (!ok) {
-                atomicExch(p.err, 12);
-                sm.failed = 1;
-            }
+            if (!ok) atomicExch(p.err, 12);
         }
-    } else {
-        // ------------------------------------------------- softmax: thread = row
-        const uint32_t row = tid;                           // 0..127 = TMEM lane
-        const uint32_t lane_base = (warp * 32u) << 16;      // this warp's TMEM lanes
+    } else if (warp < 4 * n_heads) {
+        // ----------------------------- softmax warpgroup h: one thread per query row
+        const uint32_t h = warp >> 2;
+        const uint32_t row = tid & (kGroupThreads - 1);     // TMEM lane
+        const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
+        const uint32_t s_addr = tmem + lane_base + kTmemS + 64 * h;
+        const uint32_t o_addr = tmem + lane_base + kTmemO + 128 * h;
         const uint32_t qpos = p.p0 + tok0 + row;            // absolute position of this query
         uint32_t lo_key = 0;
         if (p.window > 0 && qpos + 1 > p.window) lo_key = qpos + 1 - p.window;
-        const float sc = p.scale;
-        float m_ref = WR_NEG_SENTINEL, l = 0.f;
+        const float c2 = p.scale_log2;
+        float m_ref = WR_NEG_SENTINEL;                      // reference max, log2 domain
+        float l = 0.f;
         bool ok = true;
         for (uint32_t i = 0; i < n_kt; ++i) {
-            ok = mbar_wait(&sm.s_full, i & 1);
+            ok = mbar_wait(&sm.s_full[h], i & 1);
             if (!ok) break;
             tc_fence_after();
             float s[kBN];
-            {
-                float a[32], b[32];
-                tmem_ld32(tmem + lane_base + kTmemS, a);
-                tmem_ld32(tmem + lane_base + kTmemS + 32, b);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    s[j] = a[j] * sc;
-                    s[32 + j] = b[j] * sc;
-                }
-            }
+            tmem_ld32_nowait(s_addr, s);
+            tmem_ld32_nowait(s_addr + 32, s + 32);
+            tmem_wait_ld();
             const uint32_t key0 = (t_first + i) * kBN;
             // tiles that no row's causal or window limit cuts through need no masking
             const bool edge = (key0 + kBN - 1 > p.p0 + tok0) || (p.window > 0);
@@ -297,47 +303,51 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
 #pragma unroll
                 for (int j = 0; j < kBN; ++j) tmax = fmaxf(tmax, s[j]);
             }
-            // Rescale the accumulator only when the reference max must move.
-            if (tmax > m_ref + kRescaleThreshold || (m_ref == WR_NEG_SENTINEL && tmax > WR_NEG_SENTINEL)) {
-                if (m_ref != WR_NEG_SENTINEL) {
-                    const float a = __expf(m_ref - tmax);
+            if (tmax > WR_NEG_SENTINEL) {
+                const float tm2 = tmax * c2;
+                // Move the reference max (and rescale O) only when it is far behind.
+                if (m_ref == WR_NEG_SENTINEL) {
+                    m_ref = tm2;
+                } else if (tm2 > m_ref + kRescaleLog2) {
+                    const float a = ex2_approx(m_ref - tm2);
                     l *= a;
-                    // O must hold every earlier tile before it is touched
-                    ok = mbar_wait(&sm.o_done, (i - 1) & 1);
+                    ok = mbar_wait(&sm.o_done[h], (i - 1) & 1);    // O must hold every earlier tile
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < kHd; c += 32) {
                         float o[32];
-                        tmem_ld32(tmem + lane_base + kTmemO + c, o);
+                        tmem_ld32_nowait(o_addr + c, o);
+                        tmem_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) o[j] *= a;
-                        tmem_st32(tmem + lane_base + kTmemO + c, o);
+                        tmem_st32(o_addr + c, o);
                     }
+                    tmem_wait_st();
+                    m_ref = tm2;
                 }
-                m_ref = tmax;
             }
-            // P = exp(s - m_ref) as F16 in operand order: row `row`, 8 chunks of 8 keys
-            uint8_t *prow = sm.p[i & 1] + row * 128;
+            // P = 2^(s*c2 - m_ref) as F16 in operand order: row `row`, 8 chunks of 8 keys
+            uint8_t *prow = sm.p[h][i & 1] + row * 128;
+            // (no visible key yet for this row: every score is the sentinel and must give 0)
+            const float neg_m = (m_ref == WR_NEG_SENTINEL) ? 0.f : -m_ref;
             float psum = 0.f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float s0 = s[c * 8 + 2 * e], s1 = s[c * 8 + 2 * e + 1];
-                    const float p0 = (s0 == WR_NEG_SENTINEL) ? 0.f : __expf(s0 - m_ref);
-                    const float p1 = (s1 == WR_NEG_SENTINEL) ? 0.f : __expf(s1 - m_ref);
-                    const __half2 h = __floats2half2_rn(p0, p1);
-                    // the denominator sums what the tensor core will multiply
-                    const float2 hf = __half22float2(h);
-                    psum += hf.x + hf.y;
-                    w[e] = *reinterpret_cast<const uint32_t *>(&h);
+                    // a masked score is -1e30: the fused multiply-add stays hugely negative, 2^x gives 0
+                    const float p0 = ex2_approx(fmaf(s[c * 8 + 2 * e], c2, neg_m));
+                    const float p1 = ex2_approx(fmaf(s[c * 8 + 2 * e + 1], c2, neg_m));
+                    psum += p0 + p1;
+                    const __half2 hh = __floats2half2_rn(p0, p1);
+                    w[e] = *reinterpret_cast<const uint32_t *>(&hh);
                 }
                 *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             l += psum;
-            if (i == n_kt - 1 && (key_end % kBN) != 0) {
+            if (i == n_kt - 1 && (key_end % kBN) != 0 && h == 0) {
                 // Cache rows past the last key were never written for this
                 // prompt (or belong to a rolled-back step): clear them in the
                 // staged V tile so that 0 * garbage cannot make a NaN.
@@ -354,18 +364,19 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             }
             fence_proxy_async();          // P (generic writes) is read by the tensor core
             tc_fence_before();
-            mbar_arrive(&sm.p_ready[i & 1]);
+            mbar_arrive(&sm.p_ready[h][i & 1]);
         }
         if (ok) {
-            ok = mbar_wait(&sm.o_done, (n_kt - 1) & 1);
+            ok = mbar_wait(&sm.o_done[h], (n_kt - 1) & 1);
             if (ok) {
                 tc_fence_after();
                 const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-                float *orow = p.out + ((size_t)(tok0 + row) * p.n_q + qh) * kHd;
+                float *orow = p.out + ((size_t)(tok0 + row) * p.n_q + head0 + h) * kHd;
 #pragma unroll 1
                 for (int c = 0; c < kHd; c += 32) {
                     float o[32];
-                    tmem_ld32(tmem + lane_base + kTmemO + c, o);
+                    tmem_ld32_nowait(o_addr + c, o);
+                    tmem_wait_ld();
                     if (row < rows_here) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
@@ -375,10 +386,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 }
             }
         }
-        if (!ok) {
-            atomicExch(p.err, 13);
-            sm.failed = 1;
-        }
+        if (!ok) atomicExch(p.err, 13);
     }
 
     tc_fence_before();
@@ -440,7 +448,7 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
     const size_t q_in_bytes = elems * (q_dtype == WR_CUDA_F32 ? 4 : 2);
     const size_t q16_bytes = (elems * 2 + 255) & ~(size_t)255;
     const size_t out_bytes = elems * 4;
-    // staging layout: [q as F16][q as given (host callers / F32)][out (host callers)]
+    // staging layout: [q as F16][q as given (host callers)][out (host callers)]
     size_t need = 0;
     const bool convert = (q_dtype == WR_CUDA_F32);
     const bool host = (mem == WR_CUDA_MEM_HOST);
@@ -492,16 +500,20 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
     p.n = n;
     p.p0 = p0;
     p.n_q = n_q_heads;
+    p.n_kv = kv->n_kv;
     p.group = n_q_heads / kv->n_kv;
+    p.n_pairs = (p.group + 1) / 2;
     p.window = window;
     p.n_qtiles = (n + kBM - 1) / kBM;
-    p.scale = (scale_override > 0.0f) ? scale_override : 1.0f / sqrtf((float)kHd);   // kernels.c:1457-1459
+    const float scale = (scale_override > 0.0f) ? scale_override : 1.0f / sqrtf((float)kHd);   // kernels.c:1457-1459
+    p.scale_log2 = scale * kLog2e;
     if (!(ctx->attr_flags & 2u)) {
         WR_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_hd128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)sizeof(smem_layout)));
         ctx->attr_flags |= 2u;
     }
-    attn_prefill_hd128_kernel<<<p.n_qtiles * n_q_heads, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, p);
+    const uint32_t grid = p.n_qtiles * p.n_kv * p.n_pairs;
+    attn_prefill_hd128_kernel<<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, p);
     ctx->launches++;
     WR_CUDA_TRY(cudaGetLastError());
     if (host) {
