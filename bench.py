@@ -183,6 +183,49 @@ def workload_config(n_gpus):
             "no collective", "l2_defeat": f"rotating {N_ROT_LAYERS} layer caches, each > L2"}
 
 
+# ------------------------------------------------- prefill (BASELINE config 3)
+
+PF_N, PF_HQ, PF_HKV = 2048, 32, 8
+
+
+def measure_prefill(ctx, stream, torch, reps):
+    """Causal prefill attention of one 2048-token prompt (32Q/8KV, hd 128, F16
+    Q/K/V ~N(0,1)), `reps` launches back to back between two events on the
+    launching stream.  flops = 4*Hq*hd*S(S+1)/2 (Q.K^T and P.V, causal half)."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 3)
+    kv = ctx.kv_create(1, PF_HKV, HD, PF_N)
+    for which in (0, 1):
+        rows = torch.randn((PF_N, PF_HKV, HD), generator=gen, device="cuda").to(torch.float16)
+        kv.write_rows(0, which, 0, rows.view(torch.int16))
+    q = torch.randn((PF_N, PF_HQ, HD), generator=gen, device="cuda").to(torch.float16)
+    out = torch.empty((PF_N, PF_HQ, HD), device="cuda", dtype=torch.float32)
+    for _ in range(3):
+        ctx.attn_prefill(kv, 0, 0, PF_N, q, out, PF_HQ)
+    ctx.sync()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(reps):
+        ctx.attn_prefill(kv, 0, 0, PF_N, q, out, PF_HQ)
+    b.record(stream)
+    ctx.sync()
+    ms = a.elapsed_time(b) / reps
+    flops = 4.0 * PF_HQ * HD * PF_N * (PF_N + 1) / 2
+    tflops = flops / (ms * 1e-3) / 1e12
+    peak, src = 1590.0, "fallback"
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak, src = float(json.load(f)["bf16_tflops"]), "measured"
+    finite = bool(torch.isfinite(out).all().item())
+    kv.close()
+    return {"workload": "c3_causal_prefill: 1 session, 2048 tokens, 32Q/8KV heads, hd128, F16 Q/K/V",
+            "kernel": "attn_prefill_hd128_kernel", "bound": "tensor", "achieved": tflops,
+            "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak, "peak_source": f"of {src} (burst)",
+            "frac_of_2250_spec": tflops / 2250.0, "algorithmic_flops_per_launch": flops,
+            "avg_launch_ms": ms, "launches": reps, "traffic": None, "output_finite": finite}
+
+
 # ----------------------------------------------------------------- GPU arm
 
 def run_gpu_arm(args):
@@ -202,6 +245,14 @@ def run_gpu_arm(args):
 
     ctx = wr.Context(local)
     stream = torch.cuda.ExternalStream(ctx.stream, device=local)
+    if args.only == "prefill":
+        # profiling aid: just the prefill kernel, a few launches, one short JSON line
+        torch.cuda.set_stream(stream)
+        res = measure_prefill(ctx, stream, torch, max(1, args.steps))
+        if rank == 0:
+            print(json.dumps({"only": "prefill", "roofline_prefill": res}))
+        ctx.close()
+        return
     lens = session_lengths(rank)
     positions = [n - 1 for n in lens]
 
@@ -349,6 +400,8 @@ def run_gpu_arm(args):
     h2d = 2 * kv_row_bytes + q_bytes
     d2h = q_bytes
 
+    prefill = measure_prefill(ctx, stream, torch, max(10, min(args.steps, 50))) if rank == 0 else None
+
     # ---- parity spot check + CPU baseline on rank 0 (bounded sample)
     cpu = None
     max_err = None
@@ -385,6 +438,7 @@ def run_gpu_arm(args):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": 1e3 * e2e_s / args.steps},
             "gpu_launches": int(launches), "launch_mode": launch_mode,
+            "roofline_prefill": prefill,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_hd128_kernel",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_src}",
@@ -412,6 +466,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step from Python instead of replaying a CUDA graph")
+    ap.add_argument("--only", default="all", choices=["all", "prefill"],
+                    help="'prefill': run only the prefill-kernel measurement (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 20:

@@ -35,7 +35,7 @@ namespace {
 constexpr int kHd = 128;
 constexpr int kBM = 128;                 // query rows per head per CTA
 constexpr int kBN = 64;                  // keys per tile = page tokens
-constexpr int kStages = 3;
+constexpr int kStages = 3;               // per ring (K and V tiles are staged separately)
 constexpr int kGroupThreads = 128;       // one softmax warpgroup
 constexpr int kThreads = 2 * kGroupThreads + 64;     // + TMA warp + MMA warp
 constexpr uint32_t kQHalfBytes = kBM * 128;      // 64 dims of 128 rows
@@ -43,8 +43,8 @@ constexpr uint32_t kQBytes = 2 * kQHalfBytes;    // 32 KB per head
 constexpr uint32_t kKVBlock = kBN * kHd * 2;     // 16 KB: one K or V tile
 constexpr uint32_t kPBytes = kBM * kBN * 2;      // 16 KB
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0;                   // S of head h at columns 64*h
-constexpr uint32_t kTmemO = 128;                 // O of head h at columns 128 + 128*h
+constexpr uint32_t kTmemS = 0;                   // S of (head h, tile parity b) at columns 64*(2h+b)
+constexpr uint32_t kTmemO = 256;                 // O of head h at columns 256 + 128*h
 constexpr float kRescaleLog2 = 8.0f;             // move the reference max when it is 2^8 behind
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -58,12 +58,15 @@ struct prefill_params {
 
 struct smem_layout {
     alignas(1024) uint8_t q[2][kQBytes];                 // per head
-    alignas(1024) uint8_t kv[kStages][2 * kKVBlock];     // K then V per stage
+    alignas(1024) uint8_t k[kStages][kKVBlock];          // K ring (freed after the scores)
+    alignas(1024) uint8_t v[kStages][kKVBlock];          // V ring (freed after P.V)
     alignas(1024) uint8_t p[2][2][kPBytes];              // [head][tile parity]
     alignas(8) uint64_t bar_q;
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
-    uint64_t s_full[2];
+    uint64_t full_k[kStages];
+    uint64_t empty_k[kStages];
+    uint64_t full_v[kStages];
+    uint64_t empty_v[kStages];
+    uint64_t s_full[2][2];                               // [head][tile parity]
     uint64_t p_ready[2][2];
     uint64_t o_done[2];
     uint32_t tmem_base;
@@ -178,11 +181,14 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
     if (tid == 0) {
         mbar_init(&sm.bar_q, 1);
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(&sm.full[i], 1);
-            mbar_init(&sm.empty[i], 1);
+            mbar_init(&sm.full_k[i], 1);
+            mbar_init(&sm.empty_k[i], 1);
+            mbar_init(&sm.full_v[i], 1);
+            mbar_init(&sm.empty_v[i], 1);
         }
         for (int h = 0; h < 2; ++h) {
-            mbar_init(&sm.s_full[h], 1);
+            mbar_init(&sm.s_full[h][0], 1);
+            mbar_init(&sm.s_full[h][1], 1);
             mbar_init(&sm.p_ready[h][0], kGroupThreads);
             mbar_init(&sm.p_ready[h][1], kGroupThreads);
             mbar_init(&sm.o_done[h], 1);
@@ -208,15 +214,22 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 tma_load_2d(sm.q[h] + kQHalfBytes, &q_map, (int)((head0 + h) * kHd + 64), (int)tok0,
                             &sm.bar_q);
             }
+        }
+        if (lane < 2) {
+            // lane 0 streams the K tiles, lane 1 the V tiles: separate rings,
+            // because a K tile is free again long before its V tile is.
+            uint8_t (*ring)[kKVBlock] = lane == 0 ? sm.k : sm.v;
+            uint64_t *full = lane == 0 ? sm.full_k : sm.full_v;
+            uint64_t *empty = lane == 0 ? sm.empty_k : sm.empty_v;
             for (uint32_t i = 0; i < n_kt; ++i) {
                 const uint32_t st = i % kStages;
-                if (i >= kStages && !mbar_wait(&sm.empty[st], ((i / kStages) - 1) & 1)) {
+                if (i >= kStages && !mbar_wait(&empty[st], ((i / kStages) - 1) & 1)) {
                     atomicExch(p.err, 11);
                     break;
                 }
-                const char *src = (const char *)p.pages[t_first + i] + wr_block_off(kvh, 0, kHd);
-                mbar_expect_tx(&sm.full[st], 2 * kKVBlock);
-                bulk_g2s(sm.kv[st], src, 2 * kKVBlock, &sm.full[st]);     // K and V are adjacent
+                const char *src = (const char *)p.pages[t_first + i] + wr_block_off(kvh, lane, kHd);
+                mbar_expect_tx(&full[st], kKVBlock);
+                bulk_g2s(ring[st], src, kKVBlock, &full[st]);
             }
         }
     } else if (warp == 9) {
@@ -225,43 +238,61 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
             const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
             bool ok = mbar_wait(&sm.bar_q, 0);
+            // This one thread feeds the tensor core, so its instruction count
+            // per tile matters: descriptors are built once and an operand is
+            // selected by adding its byte offset (>>4) to the address field.
+            const uint64_t q_desc[2] = {umma_desc(smem_u32(sm.q[0]), 16, 1024),
+                                        umma_desc(smem_u32(sm.q[1]), 16, 1024)};
+            const uint64_t k_desc0 = umma_desc(smem_u32(sm.k[0]), 16, 1024);
+            const uint64_t v_desc0 = umma_desc(smem_u32(sm.v[0]), 8192, 1024);
+            const uint64_t p_desc0 = umma_desc(smem_u32(sm.p[0][0]), 16, 1024);
             auto issue_s = [&](uint32_t h, uint32_t i) {
-                const uint32_t q_addr = smem_u32(sm.q[h]);
-                const uint32_t k_addr = smem_u32(sm.kv[i % kStages]);
+                const uint64_t qd = q_desc[h];
+                const uint64_t kd = k_desc0 + (uint64_t)((i % kStages) * (kKVBlock >> 4));
+                const uint32_t d = tmem + kTmemS + 64 * (2 * h + (i & 1));
 #pragma unroll
                 for (int kk = 0; kk < kHd / 16; ++kk) {
                     const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-                    umma_f16(tmem + kTmemS + 64 * h,
-                             umma_desc(q_addr + half * kQHalfBytes + off, 16, 1024),
-                             umma_desc(k_addr + half * (kBN * 128) + off, 16, 1024), idesc_s, kk > 0);
+                    umma_f16(d, qd + ((half * kQHalfBytes + off) >> 4),
+                             kd + ((half * (kBN * 128) + off) >> 4), idesc_s, kk > 0);
                 }
-                umma_commit(&sm.s_full[h]);
+                umma_commit(&sm.s_full[h][i & 1]);
             };
-            if (ok) ok = mbar_wait(&sm.full[0], 0);
-            if (ok) {
+            // Scores run two tiles ahead of the softmax that consumes them (S is
+            // double-buffered in TMEM), so a softmax does not wait for its S.
+            for (uint32_t i = 0; ok && i < min(2u, n_kt); ++i) {
+                ok = mbar_wait(&sm.full_k[i], 0);
+                if (!ok) break;
                 tc_fence_after();
-                for (uint32_t h = 0; h < n_heads; ++h) issue_s(h, 0);
+                for (uint32_t h = 0; h < n_heads; ++h) issue_s(h, i);
+                umma_commit(&sm.empty_k[i]);                     // K tile i may be refilled
             }
             for (uint32_t i = 0; ok && i < n_kt; ++i) {
                 for (uint32_t h = 0; ok && h < n_heads; ++h) {
-                    // softmax of (head h, tile i) has consumed S and written P
+                    // softmax of (head h, tile i) has consumed S[i&1] and written P[i&1]
                     ok = mbar_wait(&sm.p_ready[h][i & 1], (i >> 1) & 1);
+                    if (ok && h == 0) ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1);
                     if (!ok) break;
                     tc_fence_after();
-                    if (i + 1 < n_kt) {
-                        ok = mbar_wait(&sm.full[(i + 1) % kStages], ((i + 1) / kStages) & 1);
-                        if (!ok) break;
-                        tc_fence_after();
-                        issue_s(h, i + 1);            // next scores first: that softmax can start
-                    }
-                    const uint32_t v_addr = smem_u32(sm.kv[i % kStages]) + kKVBlock;
-                    const uint32_t p_addr = smem_u32(sm.p[h][i & 1]);
+                    const uint64_t vd = v_desc0 + (uint64_t)((i % kStages) * (kKVBlock >> 4));
+                    const uint64_t pd = p_desc0 + (uint64_t)((2 * h + (i & 1)) * (kPBytes >> 4));
+                    const uint32_t d = tmem + kTmemO + 128 * h;
 #pragma unroll
                     for (int kk = 0; kk < kBN / 16; ++kk)
-                        umma_f16(tmem + kTmemO + 128 * h, umma_desc(p_addr + kk * 32, 16, 1024),
-                                 umma_desc(v_addr + kk * 2048, 8192, 1024), idesc_o, (i > 0) || (kk > 0));
-                    umma_commit(&sm.o_done[h]);                             // O_h holds tiles 0..i
-                    if (h + 1 == n_heads) umma_commit(&sm.empty[i % kStages]);  // stage may be refilled
+                        umma_f16(d, pd + ((kk * 32) >> 4), vd + ((kk * 2048) >> 4), idesc_o,
+                                 (i > 0) || (kk > 0));
+                    umma_commit(&sm.o_done[h]);                  // O_h holds tiles 0..i
+                    if (h + 1 == n_heads) umma_commit(&sm.empty_v[i % kStages]);   // V tile i may be refilled
+                    if (i + 2 < n_kt) {
+                        if (h == 0) ok = mbar_wait(&sm.full_k[(i + 2) % kStages], ((i + 2) / kStages) & 1);
+                        if (!ok) break;
+                        tc_fence_after();
+                        // into the S buffer this softmax just released; being issued after
+                        // P.V of tile i, its completion also tells the softmax of tile i+2
+                        // that P[i&1] is free again
+                        issue_s(h, i + 2);
+                        if (h + 1 == n_heads) umma_commit(&sm.empty_k[(i + 2) % kStages]);
+                    }
                 }
             }
             if (!ok) atomicExch(p.err, 12);
@@ -271,7 +302,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
         const uint32_t h = warp >> 2;
         const uint32_t row = tid & (kGroupThreads - 1);     // TMEM lane
         const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
-        const uint32_t s_addr = tmem + lane_base + kTmemS + 64 * h;
+        const uint32_t s_base = tmem + lane_base + kTmemS + 128 * h;
         const uint32_t o_addr = tmem + lane_base + kTmemO + 128 * h;
         const uint32_t qpos = p.p0 + tok0 + row;            // absolute position of this query
         uint32_t lo_key = 0;
@@ -281,9 +312,10 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
         float l = 0.f;
         bool ok = true;
         for (uint32_t i = 0; i < n_kt; ++i) {
-            ok = mbar_wait(&sm.s_full[h], i & 1);
+            ok = mbar_wait(&sm.s_full[h][i & 1], (i >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
+            const uint32_t s_addr = s_base + 64 * (i & 1);
             float s[kBN];
             tmem_ld32_nowait(s_addr, s);
             tmem_ld32_nowait(s_addr + 32, s + 32);
@@ -291,18 +323,23 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             const uint32_t key0 = (t_first + i) * kBN;
             // tiles that no row's causal or window limit cuts through need no masking
             const bool edge = (key0 + kBN - 1 > p.p0 + tok0) || (p.window > 0);
-            float tmax = WR_NEG_SENTINEL;
             if (edge) {
 #pragma unroll
                 for (int j = 0; j < kBN; ++j) {
                     const uint32_t key = key0 + j;
                     if (key > qpos || key < lo_key) s[j] = WR_NEG_SENTINEL;
-                    tmax = fmaxf(tmax, s[j]);
                 }
-            } else {
-#pragma unroll
-                for (int j = 0; j < kBN; ++j) tmax = fmaxf(tmax, s[j]);
             }
+            // four independent max chains instead of one 64-deep dependency
+            float mx[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+            for (int j = 4; j < kBN; j += 4) {
+                mx[0] = fmaxf(mx[0], s[j]);
+                mx[1] = fmaxf(mx[1], s[j + 1]);
+                mx[2] = fmaxf(mx[2], s[j + 2]);
+                mx[3] = fmaxf(mx[3], s[j + 3]);
+            }
+            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             if (tmax > WR_NEG_SENTINEL) {
                 const float tm2 = tmax * c2;
                 // Move the reference max (and rescale O) only when it is far behind.
@@ -328,10 +365,11 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 }
             }
             // P = 2^(s*c2 - m_ref) as F16 in operand order: row `row`, 8 chunks of 8 keys
+            // (P[i&1] is free: the scores of this tile were issued after the P.V of tile i-2)
             uint8_t *prow = sm.p[h][i & 1] + row * 128;
             // (no visible key yet for this row: every score is the sentinel and must give 0)
             const float neg_m = (m_ref == WR_NEG_SENTINEL) ? 0.f : -m_ref;
-            float psum = 0.f;
+            float psum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t w[4];
@@ -340,21 +378,21 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                     // a masked score is -1e30: the fused multiply-add stays hugely negative, 2^x gives 0
                     const float p0 = ex2_approx(fmaf(s[c * 8 + 2 * e], c2, neg_m));
                     const float p1 = ex2_approx(fmaf(s[c * 8 + 2 * e + 1], c2, neg_m));
-                    psum += p0 + p1;
+                    psum[e] += p0 + p1;
                     const __half2 hh = __floats2half2_rn(p0, p1);
                     w[e] = *reinterpret_cast<const uint32_t *>(&hh);
                 }
                 *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            l += psum;
+            l += (psum[0] + psum[1]) + (psum[2] + psum[3]);
             if (i == n_kt - 1 && (key_end % kBN) != 0 && h == 0) {
                 // Cache rows past the last key were never written for this
                 // prompt (or belong to a rolled-back step): clear them in the
                 // staged V tile so that 0 * garbage cannot make a NaN.
-                ok = mbar_wait(&sm.full[i % kStages], (i / kStages) & 1);
+                ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1);
                 if (!ok) break;
                 if (row < kBN && key0 + row >= key_end) {
-                    uint8_t *vrow = sm.kv[i % kStages] + kKVBlock + row * 128;
+                    uint8_t *vrow = sm.v[i % kStages] + row * 128;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         *reinterpret_cast<uint4 *>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
@@ -367,7 +405,11 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             mbar_arrive(&sm.p_ready[h][i & 1]);
         }
         if (ok) {
-            ok = mbar_wait(&sm.o_done[h], (n_kt - 1) & 1);
+            // A parity wait may be at most one completion behind.  This group can
+            // be two tiles ahead of the tensor core here (only tile n_kt-3 is
+            // known to be done), so step through the last two completions.
+            if (n_kt >= 2) ok = mbar_wait(&sm.o_done[h], (n_kt - 2) & 1);
+            if (ok) ok = mbar_wait(&sm.o_done[h], (n_kt - 1) & 1);
             if (ok) {
                 tc_fence_after();
                 const float inv = (l > 0.f) ? 1.0f / l : 0.f;
