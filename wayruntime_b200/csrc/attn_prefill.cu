@@ -12,10 +12,10 @@
 //     128-byte swizzle, out-of-range rows zero-filled), then K|V tiles of 64
 //     keys straight from the paged cache with linear bulk copies — the page
 //     layout already is the swizzled operand image the tensor core reads;
-//   * MMA warp (one thread): per head, S = Q.K^T as tcgen05.mma M128 N64 K16 x8
-//     into TMEM and O += P.V as M128 N128 K16 x4 (V is the MN-major operand);
-//     completion is signalled with tcgen05.commit on mbarriers.  The two heads
-//     alternate, so the tensor core works for one while the other is in softmax;
+//   * two MMA warps (one issuing thread per head): S = Q.K^T as tcgen05.mma
+//     M128 N64 K16 x8 into TMEM, two tiles ahead of the softmax (S is
+//     double-buffered), and O += P.V as M128 N128 K16 x4 (V is the MN-major
+//     operand); completion is signalled with tcgen05.commit on mbarriers;
 //   * two softmax warpgroups (one per head), one thread per query row:
 //     tcgen05.ld the 64 scores, mask (causal / window), exponentiate against a
 //     running reference max, write P as F16 into shared memory in operand
@@ -37,7 +37,7 @@ constexpr int kBM = 128;                 // query rows per head per CTA
 constexpr int kBN = 64;                  // keys per tile = page tokens
 constexpr int kStages = 3;               // per ring (K and V tiles are staged separately)
 constexpr int kGroupThreads = 128;       // one softmax warpgroup
-constexpr int kThreads = 2 * kGroupThreads + 64;     // + TMA warp + MMA warp
+constexpr int kThreads = 2 * kGroupThreads + 96;     // + TMA warp + one MMA warp per head
 constexpr uint32_t kQHalfBytes = kBM * 128;      // 64 dims of 128 rows
 constexpr uint32_t kQBytes = 2 * kQHalfBytes;    // 32 KB per head
 constexpr uint32_t kKVBlock = kBN * kHd * 2;     // 16 KB: one K or V tile
@@ -182,9 +182,9 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
         mbar_init(&sm.bar_q, 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sm.full_k[i], 1);
-            mbar_init(&sm.empty_k[i], 1);
+            mbar_init(&sm.empty_k[i], n_heads);      // one tcgen05.commit per head
             mbar_init(&sm.full_v[i], 1);
-            mbar_init(&sm.empty_v[i], 1);
+            mbar_init(&sm.empty_v[i], n_heads);
         }
         for (int h = 0; h < 2; ++h) {
             mbar_init(&sm.s_full[h][0], 1);
@@ -232,22 +232,23 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 bulk_g2s(ring[st], src, kKVBlock, &full[st]);
             }
         }
-    } else if (warp == 9) {
-        // ------------------------------------------------------------ MMA warp
-        if (lane == 0) {
+    } else if (warp >= 9) {
+        // ------------------------------------- MMA warps: one issuing thread per head
+        // (while one of them waits on a barrier the other keeps the tensor core fed)
+        const uint32_t h = warp - 9;
+        if (lane == 0 && h < n_heads) {
             const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
             const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
             bool ok = mbar_wait(&sm.bar_q, 0);
             // This one thread feeds the tensor core, so its instruction count
             // per tile matters: descriptors are built once and an operand is
             // selected by adding its byte offset (>>4) to the address field.
-            const uint64_t q_desc[2] = {umma_desc(smem_u32(sm.q[0]), 16, 1024),
-                                        umma_desc(smem_u32(sm.q[1]), 16, 1024)};
+            const uint64_t qd = umma_desc(smem_u32(sm.q[h]), 16, 1024);
             const uint64_t k_desc0 = umma_desc(smem_u32(sm.k[0]), 16, 1024);
             const uint64_t v_desc0 = umma_desc(smem_u32(sm.v[0]), 8192, 1024);
             const uint64_t p_desc0 = umma_desc(smem_u32(sm.p[0][0]), 16, 1024);
             auto issue_s = [&](uint32_t h, uint32_t i) {
-                const uint64_t qd = q_desc[h];
+
                 const uint64_t kd = k_desc0 + (uint64_t)((i % kStages) * (kKVBlock >> 4));
                 const uint32_t d = tmem + kTmemS + 64 * (2 * h + (i & 1));
 #pragma unroll
@@ -264,35 +265,32 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 ok = mbar_wait(&sm.full_k[i], 0);
                 if (!ok) break;
                 tc_fence_after();
-                for (uint32_t h = 0; h < n_heads; ++h) issue_s(h, i);
-                umma_commit(&sm.empty_k[i]);                     // K tile i may be refilled
+                issue_s(h, i);
+                umma_commit(&sm.empty_k[i]);                     // this head is done with K tile i
             }
             for (uint32_t i = 0; ok && i < n_kt; ++i) {
-                for (uint32_t h = 0; ok && h < n_heads; ++h) {
-                    // softmax of (head h, tile i) has consumed S[i&1] and written P[i&1]
-                    ok = mbar_wait(&sm.p_ready[h][i & 1], (i >> 1) & 1);
-                    if (ok && h == 0) ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1);
+                // softmax of (head h, tile i) has consumed S[i&1] and written P[i&1]
+                ok = mbar_wait(&sm.p_ready[h][i & 1], (i >> 1) & 1);
+                if (ok) ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t vd = v_desc0 + (uint64_t)((i % kStages) * (kKVBlock >> 4));
+                const uint64_t pd = p_desc0 + (uint64_t)((2 * h + (i & 1)) * (kPBytes >> 4));
+                const uint32_t d = tmem + kTmemO + 128 * h;
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk)
+                    umma_f16(d, pd + ((kk * 32) >> 4), vd + ((kk * 2048) >> 4), idesc_o, (i > 0) || (kk > 0));
+                umma_commit(&sm.o_done[h]);                      // O_h holds tiles 0..i
+                umma_commit(&sm.empty_v[i % kStages]);           // this head is done with V tile i
+                if (i + 2 < n_kt) {
+                    ok = mbar_wait(&sm.full_k[(i + 2) % kStages], ((i + 2) / kStages) & 1);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t vd = v_desc0 + (uint64_t)((i % kStages) * (kKVBlock >> 4));
-                    const uint64_t pd = p_desc0 + (uint64_t)((2 * h + (i & 1)) * (kPBytes >> 4));
-                    const uint32_t d = tmem + kTmemO + 128 * h;
-#pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk)
-                        umma_f16(d, pd + ((kk * 32) >> 4), vd + ((kk * 2048) >> 4), idesc_o,
-                                 (i > 0) || (kk > 0));
-                    umma_commit(&sm.o_done[h]);                  // O_h holds tiles 0..i
-                    if (h + 1 == n_heads) umma_commit(&sm.empty_v[i % kStages]);   // V tile i may be refilled
-                    if (i + 2 < n_kt) {
-                        if (h == 0) ok = mbar_wait(&sm.full_k[(i + 2) % kStages], ((i + 2) / kStages) & 1);
-                        if (!ok) break;
-                        tc_fence_after();
-                        // into the S buffer this softmax just released; being issued after
-                        // P.V of tile i, its completion also tells the softmax of tile i+2
-                        // that P[i&1] is free again
-                        issue_s(h, i + 2);
-                        if (h + 1 == n_heads) umma_commit(&sm.empty_k[(i + 2) % kStages]);
-                    }
+                    // into the S buffer this softmax just released; being issued after
+                    // P.V of tile i, its completion also tells the softmax of tile i+2
+                    // that P[i&1] is free again
+                    issue_s(h, i + 2);
+                    umma_commit(&sm.empty_k[(i + 2) % kStages]);
                 }
             }
             if (!ok) atomicExch(p.err, 12);

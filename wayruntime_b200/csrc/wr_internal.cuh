@@ -155,8 +155,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
     const uint32_t addr = smem_u32(bar);
-    const long long t0 = clock64();
-    for (;;) {
+    long long t0 = 0;                       // the clock is read only once a poll has failed
+    for (bool first = true;; first = false) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -166,7 +166,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if (clock64() - t0 > 4000000000LL) return false;
+        if (first) t0 = clock64();
+        else if (clock64() - t0 > 4000000000LL) return false;
     }
 }
 __device__ __forceinline__ void fence_barrier_init()
