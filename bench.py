@@ -226,6 +226,79 @@ def measure_prefill(ctx, stream, torch, reps):
             "avg_launch_ms": ms, "launches": reps, "traffic": None, "output_finite": finite}
 
 
+# ------------------------------- long-context split-KV decode (BASELINE config 4)
+
+LC_CTX = 32768
+
+
+def measure_split_kv(ctx, stream, torch, rank, world, reps):
+    """16 sessions x 32768 cached keys (8 KV heads, hd 128, ~2.1 GB of K/V per
+    layer), the KEY SEQUENCE sharded contiguously over the ranks.  One step =
+    per-rank partial attention -> one NCCL all-gather of the (m, l, o) triples
+    -> local merge.  Timed with events on the launching stream, max over ranks."""
+    from wayruntime_b200 import splitkv
+    ctx.set_attn_max_seq(LC_CTX)
+    lo, hi = splitkv.shard_range(LC_CTX, rank, world)
+    n_local = hi - lo
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 77 + rank)
+    kvs = [ctx.kv_create(1, HKV, HD, max(n_local, 1)) for _ in range(N_SESS)]
+    for kv in kvs:
+        for which in (0, 1):
+            rows = torch.randn((n_local, HKV, HD), generator=gen, device="cuda").to(torch.float16)
+            kv.write_rows(0, which, 0, rows.view(torch.int16))
+    q = torch.randn((N_SESS, HQ, HD), generator=gen, device="cuda", dtype=torch.float32)
+    if world > 1:
+        import torch.distributed as dist
+        dist.broadcast(q, src=0)
+    out = torch.empty_like(q)
+    rows_n = N_SESS * HQ
+    triples = torch.empty((rows_n, 4 + HD), dtype=torch.float32, device="cuda")
+    gathered = torch.empty((world, rows_n, 4 + HD), dtype=torch.float32, device="cuda")
+    batch = wr_batch(kvs)
+    lens = [n_local] * N_SESS
+
+    def step():
+        splitkv.decode_split_kv(ctx, batch, 0, lens, q, out, HQ, triples=triples, gathered=gathered)
+
+    for _ in range(3):
+        step()
+    ctx.sync()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(reps):
+        step()
+    b.record(stream)
+    ctx.sync()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / reps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    finite = bool(torch.isfinite(out).all().item())
+    for kv in kvs:
+        kv.close()
+    total_bytes = N_SESS * LC_CTX * HKV * HD * 2 * 2
+    peak, src = measured_peaks()
+    per_gpu = total_bytes / world / (ms * 1e-3) / 1e9
+    return {"workload": f"c4_long_context_split_kv: 16 sessions x {LC_CTX} keys, 32Q/8KV, hd128, "
+                        f"key sequence sharded over {world} GPU(s)",
+            "ms_per_step": ms, "tokens_per_s": N_SESS / (ms * 1e-3),
+            "kv_bytes_total": total_bytes, "hbm_gbs_per_gpu": per_gpu, "frac_per_gpu": per_gpu / peak,
+            "peak_source": f"of {src}", "allgather_bytes_per_rank": rows_n * (4 + HD) * 4,
+            "collective": "none" if world == 1 else "one NCCL all-gather of triples per step",
+            "output_finite": finite}
+
+
+def wr_batch(kvs):
+    import wayruntime_b200 as wr
+    return wr.Batch(kvs)
+
+
 # ----------------------------------------------------------------- GPU arm
 
 def run_gpu_arm(args):
@@ -401,6 +474,12 @@ def run_gpu_arm(args):
     d2h = q_bytes
 
     prefill = measure_prefill(ctx, stream, torch, max(10, min(args.steps, 50))) if rank == 0 else None
+    try:
+        split_kv = measure_split_kv(ctx, stream, torch, rank, world, 10)
+    except Exception as exc:                       # reported, never fatal for the headline line
+        split_kv = {"error": f"{type(exc).__name__}: {exc}"}
+        if world > 1:
+            raise
 
     # ---- parity spot check + CPU baseline on rank 0 (bounded sample)
     cpu = None
@@ -438,7 +517,7 @@ def run_gpu_arm(args):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": 1e3 * e2e_s / args.steps},
             "gpu_launches": int(launches), "launch_mode": launch_mode,
-            "roofline_prefill": prefill,
+            "roofline_prefill": prefill, "split_kv": split_kv,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_hd128_kernel",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_src}",

@@ -1,0 +1,75 @@
+"""Long-context decode with the KV sequence sharded across devices.
+
+Each rank holds a contiguous range of every session's keys in its own paged
+cache, runs the split-KV decode kernel over that range
+(``wr_cuda_attn_decode_partial``) and emits one (m, l, o) triple per (session,
+q head).  One all-gather of those triples (130-odd floats per row and rank)
+and a local merge (``wr_cuda_attn_combine``) give every rank the full result.
+The merge is the reference's online-softmax update (src/core/kernels.c:1503-1506)
+applied across shards instead of across 64-key tiles.
+
+``torch.distributed`` is the transport: NCCL over NVLink for CUDA tensors, gloo
+for the CPU tests of the plumbing.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+TRIPLE_PAD = 4
+NEG_SENTINEL = np.float32(-1e30)
+
+
+def shard_range(n_keys: int, rank: int, world: int) -> tuple[int, int]:
+    """Keys [lo, hi) of an n_keys-long sequence that rank `rank` of `world` holds:
+    contiguous ranges of ceil(n_keys / world), the last ones possibly empty."""
+    per = (n_keys + world - 1) // world
+    lo = min(rank * per, n_keys)
+    return lo, min(lo + per, n_keys)
+
+
+def gather_triples(local, group=None):
+    """All-gather [rows, TRIPLE_PAD + hd] triples -> [world, rows, TRIPLE_PAD + hd]."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    out = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    # (the concatenated 2-D form of the output is the one every backend accepts)
+    dist.all_gather_into_tensor(out.view(world * local.shape[0], *local.shape[1:]),
+                                local.contiguous(), group=group)
+    return out
+
+
+def merge_triples_reference(triples: np.ndarray) -> np.ndarray:
+    """numpy statement of the merge: triples [G, rows, TRIPLE_PAD + hd] -> [rows, hd]."""
+    m = triples[:, :, 0]
+    l = triples[:, :, 1]
+    o = triples[:, :, TRIPLE_PAD:]
+    mstar = m.max(axis=0)
+    w = np.where(m == NEG_SENTINEL, np.float32(0), np.exp(m - mstar[None, :])).astype(np.float32)
+    num = (w[:, :, None] * o).sum(axis=0)
+    den = (w * l).sum(axis=0)
+    safe = np.where(den > 0, den, np.float32(1))
+    return np.where(den[:, None] > 0, num / safe[:, None], np.float32(0)).astype(np.float32)
+
+
+def decode_split_kv(ctx, kvs, layer, local_lens, q, out, n_q_heads, scale=0.0, group=None,
+                    triples=None, gathered=None):
+    """One decode step over key-sharded caches.  q, out: CUDA float32 tensors
+    [n_sess, n_q_heads, hd]; local_lens: keys of each session held by this rank.
+    Everything is enqueued on the context's stream (set it current for NCCL)."""
+    import torch
+    import torch.distributed as dist
+    n_sess, _, hd = q.shape
+    rows = n_sess * n_q_heads
+    if triples is None:
+        triples = torch.empty((rows, TRIPLE_PAD + hd), dtype=torch.float32, device=q.device)
+    ctx.attn_decode_partial(kvs, layer, local_lens, q, triples, n_q_heads, scale=scale)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        gathered = triples
+    else:
+        if gathered is None:
+            gathered = torch.empty((world, rows, TRIPLE_PAD + hd), dtype=torch.float32, device=q.device)
+        dist.all_gather_into_tensor(gathered.view(world * rows, TRIPLE_PAD + hd), triples, group=group)
+    ctx.attn_combine(world, rows, hd, gathered, out)
+    return out
