@@ -157,6 +157,27 @@ int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv
                         uint32_t flags, float scale_override, uint32_t window,
                         int mem);
 
+/* Decode attention that never allocates.  (No counterpart in the reference:
+ * its attention op mallocs a scratch row on every call, kernels.c:1471.)
+ * Same arguments, checks and result as wr_cuda_attn_decode with device
+ * buffers, but the split-KV scratch lives in a fixed array inside the library
+ * image instead of buffers the context grows on demand.  It is meant for
+ * callers that may not allocate at step time — a serving loop whose device
+ * memory is fully committed to the KV pool, a thread that must not enter the
+ * CUDA allocator.  head_dim 128 only; q and out are device memory; a call
+ * needing more than WR_CUDA_STATIC_MAX_ITEMS work items (sessions x kv heads
+ * x key chunks) or WR_CUDA_STATIC_MAX_GROUPS groups is WR_CUDA_ERR_LIMIT.
+ * The first call on a device resolves the array's address: make it before
+ * opening a stream capture.  All calls share the one array per device, so
+ * calls that overlap on the GPU race; issue them one after another. */
+#define WR_CUDA_STATIC_MAX_ITEMS  2048
+#define WR_CUDA_STATIC_MAX_GROUPS 1024
+int wr_cuda_attn_decode_static(wr_cuda_ctx *ctx, uint32_t n_sess,
+                               wr_cuda_kv *const *kv, uint32_t layer,
+                               const uint32_t *seq_lens, const float *q,
+                               float *out, uint32_t n_q_heads,
+                               float scale_override, uint32_t window);
+
 /* Causal prefill attention for n new tokens of one session whose rows
  * [0, p0+n) are already in the cache: query i attends rows [0, p0+i]
  * (row i of the reference's prefill loop, session.c:599-630).

@@ -33,6 +33,7 @@ EXPORTS = [
     "wr_cuda_kv_create", "wr_cuda_kv_destroy", "wr_cuda_kv_max_ctx", "wr_cuda_kv_write_rows",
     "wr_cuda_kv_read_rows", "wr_cuda_kv_append", "wr_cuda_attn_decode", "wr_cuda_attn_prefill",
     "wr_cuda_attn_decode_partial", "wr_cuda_attn_combine", "wr_cuda_decode_step",
+    "wr_cuda_attn_decode_static",
 ]
 
 
@@ -83,6 +84,8 @@ def load_library():
         "wr_cuda_attn_combine": (i32, [vp, u32, u32, u32, vp, vp, i32]),
         "wr_cuda_decode_step": (i32, [vp, u32, C.POINTER(vp), u32, C.POINTER(u32), vp, vp, vp, vp,
                                       u32, f32, u32, u32, f32, u32, i32]),
+        "wr_cuda_attn_decode_static": (i32, [vp, u32, C.POINTER(vp), u32, C.POINTER(u32), vp, vp,
+                                             u32, f32, u32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -210,6 +213,19 @@ class Context:
         rc = self._lib.wr_cuda_attn_decode(self._h, len(kvs), self._handles(kvs), layer, lens, qp,
                                            op, n_q_heads, scale, window, mem)
         _check(rc, "wr_cuda_attn_decode")
+
+    def attn_decode_static(self, kvs, layer, seq_lens, q, out, n_q_heads, scale=0.0, window=0):
+        """wr_cuda_attn_decode_static: the decode kernel over the library's fixed
+        scratch array, for callers that may not allocate.  q and out must be
+        device buffers; oversize calls raise WR_ERR_LIMIT."""
+        qp, qm, _q = _buf(q)
+        op, om, _o = _buf(out)
+        if qm != MEM_DEVICE or om != MEM_DEVICE:
+            raise ValueError("wr_cuda_attn_decode_static takes device buffers only")
+        rc = self._lib.wr_cuda_attn_decode_static(self._h, len(kvs), self._handles(kvs), layer,
+                                                  self._u32s(seq_lens), qp, op, n_q_heads, scale,
+                                                  window)
+        _check(rc, "wr_cuda_attn_decode_static")
 
     def attn_decode_partial(self, kvs, layer, seq_lens, q, triples, n_q_heads, scale=0.0):
         qp, qm, _q = _buf(q)
