@@ -1,0 +1,639 @@
+/*
+ * wr_b200_session.c — the session / batch objects of wayruntime with the
+ * attention hot path on a B200.
+ *
+ * Drop-in for the reference's src/core/session.c and src/core/batch.c: it
+ * defines the same 15 external symbols (wr_session_create, wr_session_destroy,
+ * wr_session_pos, wr_session_max_context, wr_session_status, wr_prefill,
+ * wr_step, wr_batch_step, wri_session_decode_body, wri_session_kv_rollback,
+ * wri_session_prefill, wri_session_step, wri_batch_decode_step,
+ * wri_self_test_llm_step, wri_self_test_batch_step), so that linking these
+ * objects before the reference archive leaves session.o and batch.o unused.
+ * It is compiled against the reference's own headers (include/, src/) at
+ * integration time; nothing of the reference is copied here.
+ *
+ * What stays on the host, through the reference's own ops and therefore with
+ * the reference's own numerics: embedding, RMSNorm, the Q/K/V/O and FFN
+ * matmuls, per-head QK-norm, residual adds, the LM head.  What moves to the
+ * GPU: RoPE on Q and K, the F16 KV append and the attention itself
+ * (src/core/session.c:471-496), through libwr_cuda.so.
+ *
+ * Execution order is layer-lockstep over a set of rows: the n sessions of a
+ * batched step, or the n tokens of a prefill.  Rows interact only through
+ * attention, and every host op runs per row with M = 1 exactly as the
+ * reference's decode body does, so per-row host arithmetic is unchanged.
+ *
+ * Not supported (refused with WR_ERR_UNSUPPORTED at session create, never
+ * mis-run): Gemma-class models (sandwich norms, per-layer head_dim, shared-KV
+ * layers, per-layer-input embeddings, sliding-window layers).
+ *
+ * Environment: WR_CUDA_DEVICE selects the device (default 0);
+ * WR_B200_PREFILL=decode makes wr_prefill run token by token through the
+ * decode kernel (F32-exact queries) instead of the tensor-core prefill kernel
+ * (F16 queries and probabilities).
+ */
+#include <inttypes.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "core/internal.h"
+#include "core/tensor.h"
+#include "wr_cuda.h"
+
+/* ------------------------------------------------------------- device side */
+
+static wr_cuda_ctx *g_cuda;            /* one per process, like the engine */
+static int          g_cuda_rc;
+static volatile int g_cuda_guard;
+
+static wr_cuda_ctx *cuda_ctx(int *rc_out)
+{
+    while (__atomic_exchange_n(&g_cuda_guard, 1, __ATOMIC_ACQUIRE)) { }
+    if (!g_cuda && g_cuda_rc == 0) {
+        const char *dev = getenv("WR_CUDA_DEVICE");
+        int d = dev ? atoi(dev) : 0;
+        g_cuda_rc = wr_cuda_ctx_create(d, &g_cuda);
+        if (g_cuda_rc == 0)
+            g_cuda_rc = wr_cuda_ctx_set_attn_max_seq(g_cuda, WR_ATTN_MAX_SEQ);
+        if (g_cuda_rc != 0)
+            wri_log_msg(0, "b200 session: no usable sm_100 device (rc=%d); there is no CPU "
+                           "fallback for attention", g_cuda_rc);
+    }
+    wr_cuda_ctx *c = g_cuda;
+    if (rc_out) *rc_out = g_cuda_rc;
+    __atomic_store_n(&g_cuda_guard, 0, __ATOMIC_RELEASE);
+    return c;
+}
+
+/* ------------------------------------------------------------------ session */
+
+typedef struct b200_session {
+    struct wr_session pub;     /* first member: generate.c reads s->model through it */
+    wr_cuda_kv *kv;
+    float      *host;          /* one aligned block holding the scratch tensors */
+} b200_session;
+
+static b200_session *priv(wr_session *s) { return (b200_session *)s; }
+
+static void f32_tensor(wr_tensor *t, float *data, uint32_t ndim, uint32_t d0, uint32_t d1, uint32_t d2)
+{
+    memset(t, 0, sizeof(*t));
+    uint64_t n = d0;
+    if (ndim >= 2) n *= d1;
+    if (ndim >= 3) n *= d2;
+    t->data = data;
+    t->size_bytes = n * 4u;
+    t->ndim = (uint8_t)ndim;
+    t->dtype = WR_DTYPE_F32;
+    t->flags = WR_TENSOR_ARENA;
+    t->shape[0] = d0;
+    if (ndim >= 2) t->shape[1] = d1;
+    if (ndim >= 3) t->shape[2] = d2;
+}
+
+static uint32_t max_ffn(const wr_model *m)
+{
+    uint32_t f = m->ffn_dim;
+    for (uint32_t L = 0; L < m->n_layers; L++)
+        if (m->ffn_dim_per_layer[L] > f) f = m->ffn_dim_per_layer[L];
+    return f;
+}
+
+static size_t pad16(size_t n) { return (n + 15u) & ~(size_t)15u; }
+
+wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_session **out)
+{
+    if (!out) return WR_ERR_INVAL;
+    *out = NULL;
+    if (!m) return WR_ERR_INVAL;
+    if (!m->weights_committed || !m->lock) return WR_ERR_STATE;
+    if (m->n_layers == 0) return WR_ERR_INVAL;
+    if (m->n_layers > WR_MAX_LAYERS) return WR_ERR_LIMIT;
+    if (m->n_kv_heads == 0 || m->n_q_heads == 0 || m->head_dim == 0 || m->hidden_dim == 0 ||
+        m->vocab_size == 0 || m->max_context == 0)
+        return WR_ERR_INVAL;
+    if (m->is_gemma || m->kv_shared_layers || m->has_swa || m->pl_emb_dim) return WR_ERR_UNSUPPORTED;
+
+    uint32_t max_ctx = m->max_context;
+    if (params && params->max_context) {
+        if (params->max_context > m->max_context) return WR_ERR_INVAL;
+        max_ctx = params->max_context;
+    }
+    if (max_ctx > WR_ATTN_MAX_SEQ) return WR_ERR_LIMIT;
+
+    int crc = 0;
+    wr_cuda_ctx *cuda = cuda_ctx(&crc);
+    if (!cuda) return (crc < 0) ? (wr_status)crc : WR_ERR_UNSUPPORTED;
+
+    b200_session *bs = calloc(1, sizeof(*bs));
+    if (!bs) return WR_ERR_NOMEM;
+    wr_session *s = &bs->pub;
+    s->model = m;
+    s->max_context = max_ctx;
+    s->last_status = WR_OK;
+    s->lock = wr_mutex_create();
+    if (!s->lock) { free(bs); return WR_ERR_NOMEM; }
+
+    const uint32_t hid = m->hidden_dim, hd = m->head_dim, ffn = max_ffn(m);
+    const size_t nq = (size_t)m->n_q_heads * hd, nkv = (size_t)m->n_kv_heads * hd;
+    const size_t total = pad16(hid) * 3 + pad16(nq) * 2 + pad16(nkv) * 2 + pad16(ffn) * 2 +
+                         pad16(m->vocab_size);
+    bs->host = aligned_alloc(64, total * sizeof(float));
+    if (!bs->host) { wr_mutex_destroy(s->lock); free(bs); return WR_ERR_NOMEM; }
+    memset(bs->host, 0, total * sizeof(float));
+    float *p = bs->host;
+    f32_tensor(&s->residual, p, 1, hid, 0, 0);                 p += pad16(hid);
+    f32_tensor(&s->normed, p, 1, hid, 0, 0);                   p += pad16(hid);
+    f32_tensor(&s->ffn_proj, p, 1, hid, 0, 0);                 p += pad16(hid);
+    f32_tensor(&s->q, p, 3, 1, m->n_q_heads, hd);              p += pad16(nq);
+    f32_tensor(&s->attn, p, 3, 1, m->n_q_heads, hd);           p += pad16(nq);
+    f32_tensor(&s->k_row, p, 3, 1, m->n_kv_heads, hd);         p += pad16(nkv);
+    f32_tensor(&s->v_row, p, 3, 1, m->n_kv_heads, hd);         p += pad16(nkv);
+    f32_tensor(&s->ffn_gate, p, 1, ffn, 0, 0);                 p += pad16(ffn);
+    f32_tensor(&s->ffn_up, p, 1, ffn, 0, 0);                   p += pad16(ffn);
+    f32_tensor(&s->logits, p, 1, m->vocab_size, 0, 0);
+
+    int rc = wr_cuda_kv_create(cuda, m->n_layers, m->n_kv_heads, hd, max_ctx, &bs->kv);
+    if (rc != 0) {
+        wri_log_msg(0, "b200 session: device KV allocation failed (rc=%d)", rc);
+        free(bs->host);
+        wr_mutex_destroy(s->lock);
+        free(bs);
+        return (wr_status)rc;
+    }
+    wr_mutex_lock(m->lock);
+    m->session_refs++;
+    wr_mutex_unlock(m->lock);
+    *out = s;
+    return WR_OK;
+}
+
+void wr_session_destroy(wr_session *s)
+{
+    if (!s) return;
+    b200_session *bs = priv(s);
+    wr_model *m = s->model;
+    if (m && m->lock) {
+        wr_mutex_lock(m->lock);
+        if (m->session_refs > 0) m->session_refs--;
+        wr_mutex_unlock(m->lock);
+    }
+    if (bs->kv) wr_cuda_kv_destroy(bs->kv);
+    free(bs->host);
+    if (s->lock) wr_mutex_destroy(s->lock);
+    free(bs);
+}
+
+/* The committed KV length is s->pos, passed to every device call; a failed
+ * step never advanced it, so there is nothing to undo (the reference resets
+ * per-layer cursors here, src/core/session.c:160-168). */
+void wri_session_kv_rollback(wr_session *s) { (void)s; }
+
+uint32_t wr_session_pos(const wr_session *s)
+{
+    return s ? __atomic_load_n(&s->pos, __ATOMIC_ACQUIRE) : 0;
+}
+uint32_t wr_session_max_context(const wr_session *s) { return s ? s->max_context : 0; }
+wr_status wr_session_status(const wr_session *s)
+{
+    return s ? __atomic_load_n(&s->last_status, __ATOMIC_ACQUIRE) : WR_ERR_INVAL;
+}
+
+/* --------------------------------------------------------- forward over rows */
+
+typedef struct row_buffers {
+    uint32_t rows;
+    float *resid;   /* [rows][hidden]  */
+    float *q;       /* [rows][n_q*hd]  */
+    float *k, *v;   /* [rows][n_kv*hd] */
+    float *attn;    /* [rows][n_q*hd]  */
+    float *normed, *proj, *gate, *up;   /* one row each */
+    void  *block;
+} row_buffers;
+
+static int rows_alloc(row_buffers *rb, const wr_model *m, uint32_t rows)
+{
+    const size_t hid = m->hidden_dim, nq = (size_t)m->n_q_heads * m->head_dim,
+                 nkv = (size_t)m->n_kv_heads * m->head_dim, ffn = max_ffn(m);
+    const size_t total = rows * (pad16(hid) + 2 * pad16(nq) + 2 * pad16(nkv)) + 2 * pad16(hid) +
+                         2 * pad16(ffn);
+    memset(rb, 0, sizeof(*rb));
+    rb->block = aligned_alloc(64, total * sizeof(float));
+    if (!rb->block) return WR_ERR_NOMEM;
+    float *p = rb->block;
+    rb->rows = rows;
+    rb->resid = p;  p += rows * pad16(hid);
+    rb->q = p;      p += rows * pad16(nq);
+    rb->attn = p;   p += rows * pad16(nq);
+    rb->k = p;      p += rows * pad16(nkv);
+    rb->v = p;      p += rows * pad16(nkv);
+    rb->normed = p; p += pad16(hid);
+    rb->proj = p;   p += pad16(hid);
+    rb->gate = p;   p += pad16(ffn);
+    rb->up = p;
+    return WR_OK;
+}
+
+static wr_status fail(const char *what, uint32_t layer, int rc)
+{
+    wri_log_msg(0, "b200 session: %s failed at layer %u (rc=%d)", what, layer, rc);
+    return (rc < 0) ? (wr_status)rc : WR_ERR_INTERNAL;
+}
+
+enum { ATTN_DECODE = 0, ATTN_PREFILL = 1 };
+
+/* Layer stack (minus the LM head) for `rows` rows.
+ *   ATTN_DECODE : row r is the new token of session kvs[r] at position pos[r];
+ *   ATTN_PREFILL: rows are consecutive tokens of session kvs[0] from pos[0].
+ * On success rb->resid holds the pre-final-norm hidden rows. */
+static wr_status forward_rows(const wr_model *m, row_buffers *rb, const uint32_t *tokens,
+                              wr_cuda_kv *const *kvs, const uint32_t *pos, int mode)
+{
+    const uint32_t R = rb->rows, hid = m->hidden_dim, hd = m->head_dim;
+    const uint32_t nq = m->n_q_heads * hd, nkv = m->n_kv_heads * hd;
+    const size_t s_hid = pad16(hid), s_q = pad16(nq), s_kv = pad16(nkv);
+    const float eps = m->rms_eps;
+    const float theta = (m->rope_freq_base > 0.0f) ? m->rope_freq_base : 10000.0f;
+    int crc = 0;
+    wr_cuda_ctx *cuda = cuda_ctx(&crc);
+    if (!cuda) return (crc < 0) ? (wr_status)crc : WR_ERR_UNSUPPORTED;
+    /* the device calls want dense [rows, heads, hd] blocks */
+    if (s_q != nq || s_kv != nkv) return WR_ERR_UNSUPPORTED;
+    wr_tensor t_res, t_norm, t_q, t_k, t_v, t_a, t_proj, t_gate, t_up;
+    int rc;
+
+    for (uint32_t r = 0; r < R; r++) {
+        f32_tensor(&t_res, rb->resid + r * s_hid, 1, hid, 0, 0);
+        rc = wri_op_embed(&m->embed_table, tokens[r], &t_res);
+        if (rc != WR_OK) return fail("embed", 0, rc);
+    }
+    for (uint32_t L = 0; L < m->n_layers; L++) {
+        const uint32_t ffn = m->ffn_dim_per_layer[L] ? m->ffn_dim_per_layer[L] : m->ffn_dim;
+        for (uint32_t r = 0; r < R; r++) {           /* norm, projections, QK-norm: per row, M = 1 */
+            f32_tensor(&t_res, rb->resid + r * s_hid, 1, hid, 0, 0);
+            f32_tensor(&t_norm, rb->normed, 1, hid, 0, 0);
+            rc = wri_op_rmsnorm(&t_res, &m->attn_norm[L], &t_norm, eps);
+            if (rc != WR_OK) return fail("attn norm", L, rc);
+            f32_tensor(&t_norm, rb->normed, 2, 1, hid, 0);
+            f32_tensor(&t_q, rb->q + r * s_q, 2, 1, nq, 0);
+            f32_tensor(&t_k, rb->k + r * s_kv, 2, 1, nkv, 0);
+            f32_tensor(&t_v, rb->v + r * s_kv, 2, 1, nkv, 0);
+            rc = wri_op_matmul(&t_norm, &m->wq[L], &t_q);
+            if (rc != WR_OK) return fail("wq matmul", L, rc);
+            rc = wri_op_matmul(&t_norm, &m->wk[L], &t_k);
+            if (rc != WR_OK) return fail("wk matmul", L, rc);
+            rc = wri_op_matmul(&t_norm, &m->wv[L], &t_v);
+            if (rc != WR_OK) return fail("wv matmul", L, rc);
+            if (m->has_qk_norm && m->q_norm[L].data && m->k_norm[L].data) {
+                f32_tensor(&t_q, rb->q + r * s_q, 2, m->n_q_heads, hd, 0);
+                rc = wri_op_rmsnorm(&t_q, &m->q_norm[L], &t_q, eps);
+                if (rc != WR_OK) return fail("q norm", L, rc);
+                f32_tensor(&t_k, rb->k + r * s_kv, 2, m->n_kv_heads, hd, 0);
+                rc = wri_op_rmsnorm(&t_k, &m->k_norm[L], &t_k, eps);
+                if (rc != WR_OK) return fail("k norm", L, rc);
+            }
+        }
+        /* RoPE(Q, K) + KV append + attention: one device call for all rows */
+        const float scale = (m->attn_scale > 0.0f) ? m->attn_scale : 0.0f;
+        if (mode == ATTN_DECODE) {
+            rc = wr_cuda_decode_step(cuda, R, kvs, L, pos, rb->q, rb->k, rb->v, rb->attn, m->n_q_heads,
+                                     theta, m->n_rot_pairs, WR_CUDA_APPEND_ROPE, scale, 0,
+                                     WR_CUDA_MEM_HOST);
+            if (rc != 0) return fail("cuda decode step", L, rc);
+        } else {
+            rc = wr_cuda_kv_append(cuda, 1, kvs, L, pos, R, rb->k, rb->v, rb->q, m->n_q_heads, theta,
+                                   m->n_rot_pairs, WR_CUDA_APPEND_ROPE, WR_CUDA_MEM_HOST);
+            if (rc != 0) return fail("cuda kv append", L, rc);
+            rc = wr_cuda_attn_prefill(cuda, kvs[0], L, pos[0], R, rb->q, WR_CUDA_F32, rb->attn,
+                                      m->n_q_heads, scale, 0, WR_CUDA_MEM_HOST);
+            if (rc != 0) return fail("cuda prefill attention", L, rc);
+        }
+        WRI_CTR_ADD(WR_CTR_ATTENTION_CALLS, R);   /* one launch, R attention calls (kernels.c:1423) */
+
+        for (uint32_t r = 0; r < R; r++) {           /* output projection, FFN: per row */
+            f32_tensor(&t_res, rb->resid + r * s_hid, 1, hid, 0, 0);
+            f32_tensor(&t_a, rb->attn + r * s_q, 2, 1, nq, 0);
+            f32_tensor(&t_proj, rb->proj, 2, 1, hid, 0);
+            rc = wri_op_matmul(&t_a, &m->wo[L], &t_proj);
+            if (rc != WR_OK) return fail("wo matmul", L, rc);
+            f32_tensor(&t_proj, rb->proj, 1, hid, 0, 0);
+            rc = wri_op_add(&t_res, &t_proj, &t_res);
+            if (rc != WR_OK) return fail("attn residual", L, rc);
+
+            f32_tensor(&t_norm, rb->normed, 1, hid, 0, 0);
+            rc = wri_op_rmsnorm(&t_res, &m->ffn_norm[L], &t_norm, eps);
+            if (rc != WR_OK) return fail("ffn norm", L, rc);
+            f32_tensor(&t_norm, rb->normed, 2, 1, hid, 0);
+            f32_tensor(&t_gate, rb->gate, 2, 1, ffn, 0);
+            f32_tensor(&t_up, rb->up, 2, 1, ffn, 0);
+            rc = wri_op_matmul(&t_norm, &m->w_gate[L], &t_gate);
+            if (rc != WR_OK) return fail("gate matmul", L, rc);
+            rc = wri_op_matmul(&t_norm, &m->w_up[L], &t_up);
+            if (rc != WR_OK) return fail("up matmul", L, rc);
+            f32_tensor(&t_gate, rb->gate, 1, ffn, 0, 0);
+            f32_tensor(&t_up, rb->up, 1, ffn, 0, 0);
+            rc = wri_op_fused_silu_mul(&t_gate, &t_up, &t_gate);
+            if (rc != WR_OK) return fail("swiglu", L, rc);
+            f32_tensor(&t_gate, rb->gate, 2, 1, ffn, 0);
+            f32_tensor(&t_proj, rb->proj, 2, 1, hid, 0);
+            rc = wri_op_matmul(&t_gate, &m->w_down[L], &t_proj);
+            if (rc != WR_OK) return fail("down matmul", L, rc);
+            f32_tensor(&t_proj, rb->proj, 1, hid, 0, 0);
+            rc = wri_op_add(&t_res, &t_proj, &t_res);
+            if (rc != WR_OK) return fail("ffn residual", L, rc);
+        }
+    }
+    return WR_OK;
+}
+
+/* Final RMSNorm into s->normed, then logits <- normed x lm_head (src/core/session.c:554). */
+static wr_status finish_row(wr_session *s, const float *resid_row, int compute_logits)
+{
+    const wr_model *m = s->model;
+    wr_tensor t_res;
+    f32_tensor(&t_res, (float *)resid_row, 1, m->hidden_dim, 0, 0);
+    int rc = wri_op_rmsnorm(&t_res, &m->final_norm, &s->normed, m->rms_eps);
+    if (rc != WR_OK) return fail("final norm", m->n_layers, rc);
+    memcpy(s->residual.data, resid_row, (size_t)m->hidden_dim * 4u);
+    if (!compute_logits) return WR_OK;
+    wr_tensor lmv, nv, lv;
+    rc = wri_tensor_view_2d(&m->lm_head, m->hidden_dim, m->vocab_size, &lmv);
+    if (rc != WR_OK) return fail("lm-head view", m->n_layers, rc);
+    f32_tensor(&nv, (float *)s->normed.data, 2, 1, m->hidden_dim, 0);
+    f32_tensor(&lv, (float *)s->logits.data, 2, 1, m->vocab_size, 0);
+    rc = wri_op_matmul(&nv, &lmv, &lv);
+    if (rc != WR_OK) return fail("lm-head matmul", m->n_layers, rc);
+    return WR_OK;
+}
+
+/* One token of one session, without the LM head; pos is not advanced.
+ * Kept as an external symbol because the reference exports it. */
+wr_status wri_session_decode_body(wr_session *s, uint32_t token)
+{
+    row_buffers rb;
+    int rc = rows_alloc(&rb, s->model, 1);
+    if (rc != WR_OK) return (wr_status)rc;
+    wr_cuda_kv *kv = priv(s)->kv;
+    uint32_t pos = s->pos;
+    wr_status st = forward_rows(s->model, &rb, &token, &kv, &pos, ATTN_DECODE);
+    if (st == WR_OK) st = finish_row(s, rb.resid, 0);
+    free(rb.block);
+    return st;
+}
+
+wr_status wri_session_step(wr_session *s, uint32_t token, int compute_logits)
+{
+    if (!s) return WR_ERR_INVAL;
+    wr_mutex_lock(s->lock);
+    wr_status st;
+    if (s->pos >= s->max_context) {
+        st = WR_ERR_CTX_FULL;                       /* consumed nothing */
+    } else {
+        row_buffers rb;
+        st = (wr_status)rows_alloc(&rb, s->model, 1);
+        if (st == WR_OK) {
+            wr_cuda_kv *kv = priv(s)->kv;
+            uint32_t pos = s->pos;
+            st = forward_rows(s->model, &rb, &token, &kv, &pos, ATTN_DECODE);
+            if (st == WR_OK) st = finish_row(s, rb.resid, compute_logits);
+            free(rb.block);
+        }
+        if (st == WR_OK) __atomic_store_n(&s->pos, s->pos + 1, __ATOMIC_RELEASE);
+    }
+    __atomic_store_n(&s->last_status, st, __ATOMIC_RELEASE);
+    wr_mutex_unlock(s->lock);
+    return st;
+}
+
+int wri_session_prefill(wr_session *s, const uint32_t *ids, uint32_t n)
+{
+    if (!s) return WR_ERR_INVAL;
+    if (n == 0) return 0;
+    if (!ids) return WR_ERR_INVAL;
+    wr_mutex_lock(s->lock);
+    wr_status st = WR_OK;
+    /* All-or-nothing (src/core/session.c:608-626): position and cache are
+     * untouched unless every token goes through. */
+    if ((uint64_t)s->pos + n > s->max_context) {
+        st = WR_ERR_CTX_FULL;
+    } else {
+        const char *mode = getenv("WR_B200_PREFILL");
+        const int by_token = (mode && strcmp(mode, "decode") == 0) || s->model->head_dim != 128;
+        wr_cuda_kv *kv = priv(s)->kv;
+        if (by_token) {
+            row_buffers rb;
+            st = (wr_status)rows_alloc(&rb, s->model, 1);
+            uint32_t pos = s->pos;
+            for (uint32_t i = 0; st == WR_OK && i < n; i++, pos++)
+                st = forward_rows(s->model, &rb, &ids[i], &kv, &pos, ATTN_DECODE);
+            if (st == WR_OK) st = finish_row(s, rb.resid, 0);
+            if (rb.block) free(rb.block);
+        } else {
+            row_buffers rb;
+            st = (wr_status)rows_alloc(&rb, s->model, n);
+            if (st == WR_OK) {
+                uint32_t pos = s->pos;
+                st = forward_rows(s->model, &rb, ids, &kv, &pos, ATTN_PREFILL);
+                if (st == WR_OK)
+                    st = finish_row(s, rb.resid + (size_t)(n - 1) * pad16(s->model->hidden_dim), 0);
+                free(rb.block);
+            }
+        }
+        if (st == WR_OK) __atomic_store_n(&s->pos, s->pos + n, __ATOMIC_RELEASE);
+    }
+    __atomic_store_n(&s->last_status, st, __ATOMIC_RELEASE);
+    wr_mutex_unlock(s->lock);
+    return (st == WR_OK) ? (int)n : (int)st;
+}
+
+int wr_prefill(wr_session *s, const uint32_t *ids, uint32_t n) { return wri_session_prefill(s, ids, n); }
+
+const float *wr_step(wr_session *s, uint32_t token)
+{
+    if (!s) return NULL;
+    if (wri_session_step(s, token, 1) != WR_OK) return NULL;
+    return (const float *)s->logits.data;
+}
+
+/* -------------------------------------------------------------------- batch */
+
+int wri_batch_decode_step(wr_session *const *sessions, const uint32_t *tokens, uint32_t n)
+{
+    if (!sessions || !tokens) return WR_ERR_INVAL;
+    if (n == 0 || n > WR_BATCH_MAX) return WR_ERR_LIMIT;
+    wr_model *m = sessions[0] ? sessions[0]->model : NULL;
+    if (!m || !m->weights_committed) return WR_ERR_STATE;
+    for (uint32_t i = 0; i < n; i++) {
+        if (!sessions[i] || sessions[i]->model != m) return WR_ERR_INVAL;
+        for (uint32_t j = 0; j < i; j++)
+            if (sessions[i] == sessions[j]) return WR_ERR_INVAL;
+    }
+    /* lock in ascending address order (src/core/batch.c:106-120) */
+    wr_session *order[WR_BATCH_MAX];
+    for (uint32_t i = 0; i < n; i++) order[i] = sessions[i];
+    for (uint32_t i = 1; i < n; i++)
+        for (uint32_t j = i; j > 0 && (uintptr_t)order[j - 1] > (uintptr_t)order[j]; j--) {
+            wr_session *t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
+        }
+    for (uint32_t i = 0; i < n; i++) wr_mutex_lock(order[i]->lock);
+
+    wr_status st = WR_OK;
+    for (uint32_t i = 0; i < n && st == WR_OK; i++)
+        if (sessions[i]->pos >= sessions[i]->max_context) st = WR_ERR_CTX_FULL;
+    if (st == WR_OK) {
+        row_buffers rb;
+        st = (wr_status)rows_alloc(&rb, m, n);
+        if (st == WR_OK) {
+            wr_cuda_kv *kvs[WR_BATCH_MAX];
+            uint32_t pos[WR_BATCH_MAX];
+            for (uint32_t i = 0; i < n; i++) { kvs[i] = priv(sessions[i])->kv; pos[i] = sessions[i]->pos; }
+            st = forward_rows(m, &rb, tokens, kvs, pos, ATTN_DECODE);    /* all sessions, one grid per layer */
+            for (uint32_t i = 0; i < n && st == WR_OK; i++)
+                st = finish_row(sessions[i], rb.resid + (size_t)i * pad16(m->hidden_dim), 1);
+            free(rb.block);
+        }
+    }
+    if (st == WR_OK)
+        for (uint32_t i = 0; i < n; i++)
+            __atomic_store_n(&sessions[i]->pos, sessions[i]->pos + 1, __ATOMIC_RELEASE);
+    for (uint32_t i = 0; i < n; i++) __atomic_store_n(&sessions[i]->last_status, st, __ATOMIC_RELEASE);
+    for (uint32_t i = n; i > 0; i--) wr_mutex_unlock(order[i - 1]->lock);
+    return (st == WR_OK) ? (int)n : (int)st;
+}
+
+int wr_batch_step(wr_session *const *sessions, const uint32_t *tokens, uint32_t n, const float **logits_out)
+{
+    int rc = wri_batch_decode_step(sessions, tokens, n);
+    if (rc < 0) return rc;
+    if (logits_out)
+        for (uint32_t i = 0; i < n; i++) logits_out[i] = (const float *)sessions[i]->logits.data;
+    return rc;
+}
+
+/* --------------------------------------------------------------- self-tests
+ *
+ * Same contracts as the reference's fixtures (src/core/session.c:888-999,
+ * src/core/batch.c:257-390) on a small synthetic model with patterned weights:
+ * cursor accounting, refusal without consumption, CTX_FULL, and batched
+ * logits byte-equal to serial ones.  They need a B200 (return -2 without). */
+
+static int fx_alloc(wr_tensor *t, uint32_t ndim, uint32_t d0, uint32_t d1, uint16_t flags, uint32_t salt,
+                    float constant)
+{
+    uint32_t shape[2] = { d0, d1 };
+    if (wri_tensor_init(t, WR_DTYPE_F32, ndim, shape, flags, NULL) != WR_OK) return -1;
+    uint64_t n = (uint64_t)d0 * (ndim > 1 ? d1 : 1);
+    float *p = t->data;
+    for (uint64_t i = 0; i < n; i++)
+        p[i] = salt ? (float)((int32_t)((i * 37u + salt * 11u) % 41u) - 20) * 0.01f : constant;
+    return 0;
+}
+
+static int fx_model(wr_model *m, uint32_t layers)
+{
+    memset(m, 0, sizeof(*m));
+    m->n_layers = layers; m->n_q_heads = 4; m->n_kv_heads = 2; m->head_dim = 8;
+    m->hidden_dim = 32; m->ffn_dim = 64; m->vocab_size = 64; m->max_context = 16;
+    m->train_context = 16; m->rms_eps = 1e-5f; m->rope_freq_base = 10000.0f;
+    m->weights_committed = 1;
+    m->lock = wr_mutex_create();
+    if (!m->lock) return -1;
+    int bad = 0;
+    bad |= fx_alloc(&m->embed_table, 2, 64, 32, 0, 3, 0);
+    bad |= fx_alloc(&m->final_norm, 1, 32, 0, 0, 0, 1.0f);
+    bad |= fx_alloc(&m->lm_head, 2, 64, 32, WR_TENSOR_GGML_WEIGHT, 5, 0);
+    for (uint32_t L = 0; L < layers; L++) {
+        bad |= fx_alloc(&m->attn_norm[L], 1, 32, 0, 0, 0, 1.0f);
+        bad |= fx_alloc(&m->ffn_norm[L], 1, 32, 0, 0, 0, 1.0f);
+        bad |= fx_alloc(&m->wq[L], 2, 32, 32, WR_TENSOR_GGML_WEIGHT, 7 + L, 0);
+        bad |= fx_alloc(&m->wk[L], 2, 16, 32, WR_TENSOR_GGML_WEIGHT, 9 + L, 0);
+        bad |= fx_alloc(&m->wv[L], 2, 16, 32, WR_TENSOR_GGML_WEIGHT, 11 + L, 0);
+        bad |= fx_alloc(&m->wo[L], 2, 32, 32, WR_TENSOR_GGML_WEIGHT, 13 + L, 0);
+        bad |= fx_alloc(&m->w_gate[L], 2, 64, 32, WR_TENSOR_GGML_WEIGHT, 15 + L, 0);
+        bad |= fx_alloc(&m->w_up[L], 2, 64, 32, WR_TENSOR_GGML_WEIGHT, 17 + L, 0);
+        bad |= fx_alloc(&m->w_down[L], 2, 32, 64, WR_TENSOR_GGML_WEIGHT, 19 + L, 0);
+    }
+    return bad;
+}
+
+static void fx_model_free(wr_model *m)
+{
+    wri_tensor_free(&m->embed_table);
+    wri_tensor_free(&m->final_norm);
+    wri_tensor_free(&m->lm_head);
+    for (uint32_t L = 0; L < m->n_layers; L++) {
+        wri_tensor_free(&m->attn_norm[L]); wri_tensor_free(&m->ffn_norm[L]);
+        wri_tensor_free(&m->wq[L]); wri_tensor_free(&m->wk[L]); wri_tensor_free(&m->wv[L]);
+        wri_tensor_free(&m->wo[L]); wri_tensor_free(&m->w_gate[L]); wri_tensor_free(&m->w_up[L]);
+        wri_tensor_free(&m->w_down[L]);
+    }
+    if (m->lock) wr_mutex_destroy(m->lock);
+}
+
+int wri_self_test_llm_step(void)
+{
+    int crc = 0;
+    if (!cuda_ctx(&crc)) return -2;
+    wr_model *m = calloc(1, sizeof(*m));
+    if (!m) return -1;
+    int ret = -1;
+    wr_session *s = NULL;
+    if (fx_model(m, 2) != 0) goto out;
+    if (wr_session_create(m, NULL, &s) != WR_OK) goto out;
+    if (wr_session_pos(s) != 0 || wr_session_max_context(s) != 16) goto out;
+    if (!wr_step(s, 3) || wr_session_pos(s) != 1) goto out;                 /* cursor 0 -> 1 */
+    if (wr_step(s, 64) != NULL || wr_session_pos(s) != 1) goto out;         /* out-of-vocab: nothing consumed */
+    if (wr_session_status(s) != WR_ERR_INVAL) goto out;
+    uint32_t ids[14];
+    for (uint32_t i = 0; i < 14; i++) ids[i] = (i * 5u + 1u) % 64u;
+    if (wr_prefill(s, ids, 14) != 14 || wr_session_pos(s) != 15) goto out;
+    if (wr_prefill(s, ids, 2) != WR_ERR_CTX_FULL || wr_session_pos(s) != 15) goto out;  /* all-or-nothing */
+    if (!wr_step(s, 7) || wr_session_pos(s) != 16) goto out;                /* now full */
+    if (wr_step(s, 7) != NULL || wr_session_status(s) != WR_ERR_CTX_FULL) goto out;
+    if (wr_session_pos(s) != 16) goto out;                                   /* CTX_FULL consumed nothing */
+    ret = 0;
+out:
+    if (s) wr_session_destroy(s);
+    fx_model_free(m);
+    free(m);
+    return ret;
+}
+
+int wri_self_test_batch_step(void)
+{
+    enum { N = 3, STEPS = 4 };
+    int crc = 0;
+    if (!cuda_ctx(&crc)) return -2;
+    wr_model *m = calloc(1, sizeof(*m));
+    if (!m) return -1;
+    int ret = -1;
+    wr_session *ser[N] = { 0 }, *bat[N] = { 0 };
+    float *keep = NULL;
+    if (fx_model(m, 1) != 0) goto out;
+    keep = malloc(sizeof(float) * N * STEPS * 64);
+    if (!keep) goto out;
+    for (int i = 0; i < N; i++)
+        if (wr_session_create(m, NULL, &ser[i]) != WR_OK || wr_session_create(m, NULL, &bat[i]) != WR_OK)
+            goto out;
+    for (int t = 0; t < STEPS; t++)
+        for (int i = 0; i < N; i++) {
+            const float *lg = wr_step(ser[i], (uint32_t)((i * 7 + t * 3 + 1) % 64));
+            if (!lg) goto out;
+            memcpy(keep + ((size_t)t * N + i) * 64, lg, 64 * sizeof(float));
+        }
+    for (int t = 0; t < STEPS; t++) {
+        uint32_t toks[N];
+        const float *lg[N];
+        for (int i = 0; i < N; i++) toks[i] = (uint32_t)((i * 7 + t * 3 + 1) % 64);
+        if (wr_batch_step((wr_session *const *)bat, toks, N, lg) != N) goto out;
+        for (int i = 0; i < N; i++)
+            if (memcmp(lg[i], keep + ((size_t)t * N + i) * 64, 64 * sizeof(float)) != 0) goto out;   /* byte-equal */
+    }
+    ret = 0;
+out:
+    for (int i = 0; i < N; i++) { if (ser[i]) wr_session_destroy(ser[i]); if (bat[i]) wr_session_destroy(bat[i]); }
+    free(keep);
+    fx_model_free(m);
+    free(m);
+    return ret;
+}
