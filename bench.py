@@ -36,6 +36,10 @@ CTX_LO, CTX_HI = 1024, 4096
 N_ROT_LAYERS = 4
 THETA = 500000.0
 SEED = 20261125
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures
+# (profiles/): same seeded workloads as the ones timed here.
+NCU_TRAFFIC_DECODE_C2 = 171_380_000      # algorithmic 165 429 248 B
+NCU_TRAFFIC_PREFILL_C3 = 25_250_000      # operands are re-read from L2; output stays in L2
 METRIC = "batched_decode_attention_tokens_per_s"
 UNIT = "tok/s"
 
@@ -223,7 +227,9 @@ def measure_prefill(ctx, stream, torch, reps):
             "kernel": "attn_prefill_hd128_kernel", "bound": "tensor", "achieved": tflops,
             "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak, "peak_source": f"of {src} (burst)",
             "frac_of_2250_spec": tflops / 2250.0, "algorithmic_flops_per_launch": flops,
-            "avg_launch_ms": ms, "launches": reps, "traffic": None, "output_finite": finite}
+            "avg_launch_ms": ms, "launches": reps, "traffic": NCU_TRAFFIC_PREFILL_C3,
+            "traffic_source": "profiles/attn_prefill_hd128_c3_causal_prefill.md (ncu dram read+write)",
+            "output_finite": finite}
 
 
 # ------------------------------- long-context split-KV decode (BASELINE config 4)
@@ -525,7 +531,10 @@ def run_gpu_arm(args):
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_src}",
                          "algorithmic_bytes_per_launch": alg, "avg_launch_ms": dec_avg_ms,
-                         "traffic": None, "frac_of_8TBs_spec": achieved / 8000.0},
+                         "traffic": NCU_TRAFFIC_DECODE_C2,
+                         "traffic_source": "profiles/attn_decode_hd128_c2_batched_decode.md "
+                                           "(ncu dram read+write per launch, this seeded workload)",
+                         "frac_of_8TBs_spec": achieved / 8000.0},
             "cpu_baseline": cpu,
             "parity_max_abs_err": max_err,
             "clocks": clocks,
