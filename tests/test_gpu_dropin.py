@@ -132,11 +132,10 @@ def test_small_model_teacher_forced_argmax(libs):
 def test_config1_qwen3_0p6b_shape(libs):
     """BASELINE config 1: 28 layers, hidden 1024, 16 Q / 8 KV heads, head_dim 128,
     theta 1e6, QK-norm, SwiGLU 3072, vocab 151936, F16 weights ~N(0, 0.02);
-    64-token prompt, then teacher-forced greedy steps (128 with WR_TEST_FULL=1,
-    else 24 to keep the suite short: each step is a full CPU forward in both
-    libraries)."""
+    64-token prompt, then 128 teacher-forced greedy steps (24 with
+    WR_TEST_QUICK=1: each step is a full CPU forward in both libraries)."""
     shape = dict(n_layers=28, hidden=1024, n_q=16, n_kv=8, head_dim=128, ffn=3072, vocab=151936)
-    steps = 128 if os.environ.get("WR_TEST_FULL") == "1" else 24
+    steps = 24 if os.environ.get("WR_TEST_QUICK") == "1" else 128
     _teacher_forced(libs, shape, n_prompt=64, n_steps=steps, seed=20261125, logit_tol=2e-3)
 
 

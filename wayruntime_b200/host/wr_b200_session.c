@@ -545,13 +545,14 @@ static int fx_model(wr_model *m, uint32_t layers)
     for (uint32_t L = 0; L < layers; L++) {
         bad |= fx_alloc(&m->attn_norm[L], 1, 32, 0, 0, 0, 1.0f);
         bad |= fx_alloc(&m->ffn_norm[L], 1, 32, 0, 0, 0, 1.0f);
+        /* GGML matmul weights carry the logical [in, out] shape (src/core/session.c:909-911) */
         bad |= fx_alloc(&m->wq[L], 2, 32, 32, WR_TENSOR_GGML_WEIGHT, 7 + L, 0);
-        bad |= fx_alloc(&m->wk[L], 2, 16, 32, WR_TENSOR_GGML_WEIGHT, 9 + L, 0);
-        bad |= fx_alloc(&m->wv[L], 2, 16, 32, WR_TENSOR_GGML_WEIGHT, 11 + L, 0);
+        bad |= fx_alloc(&m->wk[L], 2, 32, 16, WR_TENSOR_GGML_WEIGHT, 9 + L, 0);
+        bad |= fx_alloc(&m->wv[L], 2, 32, 16, WR_TENSOR_GGML_WEIGHT, 11 + L, 0);
         bad |= fx_alloc(&m->wo[L], 2, 32, 32, WR_TENSOR_GGML_WEIGHT, 13 + L, 0);
-        bad |= fx_alloc(&m->w_gate[L], 2, 64, 32, WR_TENSOR_GGML_WEIGHT, 15 + L, 0);
-        bad |= fx_alloc(&m->w_up[L], 2, 64, 32, WR_TENSOR_GGML_WEIGHT, 17 + L, 0);
-        bad |= fx_alloc(&m->w_down[L], 2, 32, 64, WR_TENSOR_GGML_WEIGHT, 19 + L, 0);
+        bad |= fx_alloc(&m->w_gate[L], 2, 32, 64, WR_TENSOR_GGML_WEIGHT, 15 + L, 0);
+        bad |= fx_alloc(&m->w_up[L], 2, 32, 64, WR_TENSOR_GGML_WEIGHT, 17 + L, 0);
+        bad |= fx_alloc(&m->w_down[L], 2, 64, 32, WR_TENSOR_GGML_WEIGHT, 19 + L, 0);
     }
     return bad;
 }
