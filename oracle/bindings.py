@@ -37,6 +37,11 @@ def build(ref_root: str = "/root/reference") -> None:
     """Compile liboracle.so and, when the reference checkout exists, _ref/*.so."""
     subprocess.run(["make", "-C", _HERE, f"REF={ref_root}"], check=True,
                    stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    cuda_lib = os.path.join(_HERE, "..", "wayruntime_b200", "lib", "libwr_cuda.so")
+    if os.path.exists(os.path.join(ref_root, "src", "core", "kernels.c")) and os.path.exists(cuda_lib):
+        # the reference with the B200 session objects linked in (the drop-in parity tests' subject)
+        subprocess.run(["make", "-C", _HERE, f"REF={ref_root}", "dropin"], check=True,
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
 
 
 class Checker:
