@@ -137,3 +137,31 @@ int refshim_causal_prefill_rows(const void *q, int q_dtype, const uint16_t *k,
     }
     return worst;
 }
+
+#ifdef REFSHIM_TAP
+/* Whole-model capture (the `libwayruntime_ref_tap.so` variant only, linked
+ * with -Wl,--wrap=wri_op_gqa_attention): every attention call the reference's
+ * session code makes goes through here, runs the unmodified op, and hands the
+ * result to a test callback.  Calls arrive token-major, layer-minor
+ * (src/core/session.c:441-496), so the n-th call of a token is layer n. */
+typedef void (*refshim_tap_fn)(void *user, uint32_t seq_k, const float *out, uint32_t n_floats);
+static refshim_tap_fn g_tap;
+static void          *g_tap_user;
+
+void refshim_set_attn_tap(refshim_tap_fn fn, void *user) { g_tap = fn; g_tap_user = user; }
+
+int __real_wri_op_gqa_attention(const wr_tensor *Q, const wr_tensor *K, const wr_tensor *V,
+                                wr_tensor *C, float scale_override, uint32_t window);
+
+int __wrap_wri_op_gqa_attention(const wr_tensor *Q, const wr_tensor *K, const wr_tensor *V,
+                                wr_tensor *C, float scale_override, uint32_t window)
+{
+    int rc = __real_wri_op_gqa_attention(Q, K, V, C, scale_override, window);
+    if (rc == 0 && g_tap && C->dtype == WR_DTYPE_F32) {
+        uint32_t seq_k = (K->flags & WR_TENSOR_GROWABLE) ? K->valid_rows : K->shape[0];
+        g_tap(g_tap_user, seq_k, (const float *)C->data,
+              C->shape[0] * C->shape[1] * C->shape[2]);
+    }
+    return rc;
+}
+#endif

@@ -6,7 +6,11 @@ their place (oracle/Makefile, target `dropin`); `libwayruntime_ref.so` is the
 unmodified reference.  Both are driven through the reference's public API
 (include/wayruntime/wayruntime.h) on the same seeded GGUF and token ids:
   * teacher-forced greedy decoding: identical argmax at every step, logits
-    within tolerance (BASELINE config 1: Qwen3-0.6B shape, 64-token prompt);
+    within tolerance (BASELINE config 1: Qwen3-0.6B shape, 64-token prompt),
+    and every layer's attention output of every token within tolerance: the
+    reference's rows are captured by `libwayruntime_ref_tap.so` (same sources,
+    the session code's attention calls routed through a hook by the linker),
+    the device rows by the session objects' own observer;
   * batched step byte-equal to serial steps (test/sdk_gen.c:209-279 contract);
   * cursor / CTX_FULL / refusal semantics (src/core/session.c:888-999).
 Skipped where the two libraries were not built (they are built where the
@@ -23,8 +27,12 @@ import _mkgguf
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.path.join(ROOT, "oracle", "_ref", "libwayruntime_ref.so")
+REF = os.path.join(ROOT, "oracle", "_ref", "libwayruntime_ref_tap.so")
 B200 = os.path.join(ROOT, "oracle", "_ref", "libwayruntime_b200.so")
+
+
+REF_TAP = C.CFUNCTYPE(None, C.c_void_p, C.c_uint32, C.POINTER(C.c_float), C.c_uint32)
+B200_TAP = C.CFUNCTYPE(None, C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_float), C.c_uint32)
 
 
 class Lib:
@@ -77,7 +85,7 @@ def test_session_self_tests_pass_on_device(libs):
     assert b.L.wri_self_test_batch_step() == 0
 
 
-def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol):
+def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol, attn_tol=2e-3):
     ref, b = libs
     vocab = shape["vocab"]
     path = os.path.join(tempfile.mkdtemp(prefix="wr_gguf_"), "model.gguf")
@@ -86,6 +94,15 @@ def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol):
     prompt = [int(x) for x in rng.integers(0, vocab, n_prompt)]
     out = {}
     # the reference first: its greedy ids drive every other run (teacher forcing)
+    ref_rows, seen = {}, {}
+
+    def on_ref(_user, seq_k, data, n):          # calls for one token arrive in layer order
+        layer = seen.get(seq_k, 0)
+        seen[seq_k] = layer + 1
+        ref_rows[(layer, seq_k - 1)] = np.ctypeslib.as_array(data, (n,)).copy()
+
+    ref_cb = REF_TAP(on_ref)
+    ref.L.refshim_set_attn_tap(ref_cb, None)
     m = ref.load(path)
     s = ref.session(m)
     assert ref.prefill(s, prompt[:-1]) == n_prompt - 1
@@ -98,6 +115,17 @@ def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol):
         ids.append(tok)
     ref.L.wr_session_destroy(s)
     ref.L.wr_model_free(m)
+    ref.L.refshim_set_attn_tap(REF_TAP(0), None)
+    assert len(ref_rows) == shape["n_layers"] * (n_prompt - 1 + n_steps)
+    attn = {"worst": 0.0, "rows": 0}
+
+    def on_b200(_user, layer, pos, data, n):
+        got = np.ctypeslib.as_array(data, (n,))
+        attn["worst"] = max(attn["worst"], float(np.abs(got - ref_rows[(layer, pos)]).max()))
+        attn["rows"] += 1
+
+    b_cb = B200_TAP(on_b200)
+    b.L.wr_b200_set_attn_tap(b_cb, None)
     mb = b.load(path)
     for mode in ("kernel", "decode"):
         os.environ["WR_B200_PREFILL"] = mode
@@ -115,10 +143,18 @@ def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol):
             tok = ids[t]                                   # teacher forcing with the reference's ids
         b.L.wr_session_destroy(sb)
         out[mode] = (same, worst, min(margins))
+        # per-layer attention outputs of every prompt and generated token (the hidden states
+        # entering attention already differ by earlier layers' rounding, hence not 1e-6)
+        assert attn["rows"] == len(ref_rows), (mode, attn)
+        assert attn["worst"] <= attn_tol, (mode, attn)
+        out[mode] += (attn["worst"],)
+        attn.update(worst=0.0, rows=0)
+    b.L.wr_b200_set_attn_tap(B200_TAP(0), None)
     os.environ.pop("WR_B200_PREFILL", None)
     b.L.wr_model_free(mb)
     os.remove(path)
-    for mode, (same, worst, margin) in out.items():
+    print("teacher-forced parity (argmax matches, worst logit err, min top-2 margin, worst attn err):", out)
+    for mode, (same, worst, margin, _attn) in out.items():
         assert worst <= logit_tol, (mode, worst, margin)
         assert same == n_steps, (mode, same, n_steps, worst, margin)
     return out

@@ -65,6 +65,19 @@ static wr_cuda_ctx *cuda_ctx(int *rc_out)
     return c;
 }
 
+/* Optional observer of every attention result (tests compare these rows with
+ * the reference's per layer): called once per row after the device call. */
+typedef void (*wr_b200_attn_tap_fn)(void *user, uint32_t layer, uint32_t pos, const float *attn,
+                                    uint32_t n_floats);
+static wr_b200_attn_tap_fn g_attn_tap;
+static void               *g_attn_tap_user;
+
+void wr_b200_set_attn_tap(wr_b200_attn_tap_fn fn, void *user)
+{
+    g_attn_tap_user = user;
+    g_attn_tap = fn;
+}
+
 /* ------------------------------------------------------------------ session */
 
 typedef struct b200_session {
@@ -309,6 +322,10 @@ static wr_status forward_rows(const wr_model *m, row_buffers *rb, const uint32_t
             if (rc != 0) return fail("cuda prefill attention", L, rc);
         }
         WRI_CTR_ADD(WR_CTR_ATTENTION_CALLS, R);   /* one launch, R attention calls (kernels.c:1423) */
+        if (g_attn_tap)
+            for (uint32_t r = 0; r < R; r++)
+                g_attn_tap(g_attn_tap_user, L, mode == ATTN_DECODE ? pos[r] : pos[0] + r,
+                           rb->attn + r * s_q, nq);
 
         for (uint32_t r = 0; r < R; r++) {           /* output projection, FFN: per row */
             f32_tensor(&t_res, rb->resid + r * s_hid, 1, hid, 0, 0);
