@@ -141,3 +141,27 @@ def test_prefill_refusals(ctx):
     q64 = np.zeros((10, 8, 64), np.float32)
     assert status(lambda: ctx.attn_prefill(kv64, 0, 0, 10, q64, np.zeros_like(q64), 8)) == -3
     kv.close(), kv64.close()
+
+
+def test_prefill_row_maximum_grows_for_some_rows_only(ctx):
+    """Scores that keep growing along the keys for some query rows and stay flat
+    for their neighbours: the accumulator is rescaled again and again, and within
+    one warp only some rows need it (the reference rescales per row,
+    src/core/kernels.c:1496-1510)."""
+    P = port()
+    n, hq, hkv = 640, 4, 2
+    u = _gen.normal(711, (128,))
+    u /= np.linalg.norm(u)
+    k = 0.3 * _gen.normal(712, (n, hkv, 128))
+    k += (np.arange(n, dtype=np.float32)[:, None, None] / 8.0) * u          # component along u grows with the key index
+    q = 0.3 * _gen.normal(713, (n, hq, 128))
+    gain = np.where(np.arange(n) % 3 == 0, 6.0, 0.0).astype(np.float32)     # every third row looks along u
+    q += gain[:, None, None] * u
+    q16, k16 = P.f32_to_f16(q.astype(np.float32)), P.f32_to_f16(k.astype(np.float32))
+    v16 = P.f32_to_f16(_gen.normal(714, (n, hkv, 128)))
+    out = run_prefill(ctx, q16, k16, v16, 0, hq)
+    rows = np.arange(0, n, 5, dtype=np.uint32)
+    rc, want = P.causal_prefill_rows(q16, k16, v16, rows, p0=0, threads=8, max_seq=32768)
+    assert rc == 0
+    assert np.isfinite(out).all()
+    assert np.abs(out[rows] - want).max() <= TOL

@@ -15,7 +15,7 @@
 //     wants).  While it computes Q.K on tile t the V of tile t is in flight;
 //     while it computes P.V the K of tile t+1 is in flight — across item
 //     boundaries too.  No CTA-wide barrier exists.
-//   * items come from a global queue (the first one is static); an engine
+//   * items come from a global queue (the first two are static); an engine
 //     draws the index of a future item one item ahead and loads the page
 //     pointer of a future tile one tile ahead, so neither latency is exposed.
 //     Which engine runs an item has no effect on the item's result.

@@ -67,8 +67,10 @@ struct smem_layout {
     uint64_t full_v[kStages];
     uint64_t empty_v[kStages];
     uint64_t s_full[2][2];                               // [head][tile parity]
+    uint64_t s_free[2][2];                               // softmax has read S out of TMEM
     uint64_t p_ready[2][2];
-    uint64_t o_done[2];
+    uint64_t pv_done[2][2];                              // P.V of the tile using P[parity] has completed
+    uint64_t xu_turn[4][2];                              // [scheduler][head]: that head's warp may exponentiate
     uint32_t tmem_base;
 };
 
@@ -189,9 +191,13 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
         for (int h = 0; h < 2; ++h) {
             mbar_init(&sm.s_full[h][0], 1);
             mbar_init(&sm.s_full[h][1], 1);
+            mbar_init(&sm.s_free[h][0], kGroupThreads);
+            mbar_init(&sm.s_free[h][1], kGroupThreads);
             mbar_init(&sm.p_ready[h][0], kGroupThreads);
             mbar_init(&sm.p_ready[h][1], kGroupThreads);
-            mbar_init(&sm.o_done[h], 1);
+            mbar_init(&sm.pv_done[h][0], 1);
+            mbar_init(&sm.pv_done[h][1], 1);
+            for (int q = 0; q < 4; ++q) mbar_init(&sm.xu_turn[q][h], 1);
         }
         fence_barrier_init();
     }
@@ -269,7 +275,17 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 umma_commit(&sm.empty_k[i]);                     // this head is done with K tile i
             }
             for (uint32_t i = 0; ok && i < n_kt; ++i) {
-                // softmax of (head h, tile i) has consumed S[i&1] and written P[i&1]
+                if (i + 2 < n_kt) {
+                    // the softmax of tile i has its scores in registers: S[i&1] can take
+                    // tile i+2 while that softmax is still exponentiating
+                    ok = mbar_wait(&sm.s_free[h][i & 1], (i >> 1) & 1);
+                    if (ok) ok = mbar_wait(&sm.full_k[(i + 2) % kStages], ((i + 2) / kStages) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(h, i + 2);
+                    umma_commit(&sm.empty_k[(i + 2) % kStages]);
+                }
+                // softmax of (head h, tile i) has written P[i&1]
                 ok = mbar_wait(&sm.p_ready[h][i & 1], (i >> 1) & 1);
                 if (ok) ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1);
                 if (!ok) break;
@@ -280,18 +296,8 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk)
                     umma_f16(d, pd + ((kk * 32) >> 4), vd + ((kk * 2048) >> 4), idesc_o, (i > 0) || (kk > 0));
-                umma_commit(&sm.o_done[h]);                      // O_h holds tiles 0..i
+                umma_commit(&sm.pv_done[h][i & 1]);              // O_h holds tiles 0..i, P[i&1] is free
                 umma_commit(&sm.empty_v[i % kStages]);           // this head is done with V tile i
-                if (i + 2 < n_kt) {
-                    ok = mbar_wait(&sm.full_k[(i + 2) % kStages], ((i + 2) / kStages) & 1);
-                    if (!ok) break;
-                    tc_fence_after();
-                    // into the S buffer this softmax just released; being issued after
-                    // P.V of tile i, its completion also tells the softmax of tile i+2
-                    // that P[i&1] is free again
-                    issue_s(h, i + 2);
-                    umma_commit(&sm.empty_k[(i + 2) % kStages]);
-                }
             }
             if (!ok) atomicExch(p.err, 12);
         }
@@ -308,16 +314,21 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
         const float c2 = p.scale_log2;
         float m_ref = WR_NEG_SENTINEL;                      // reference max, log2 domain
         float l = 0.f;
-        bool ok = true;
-        for (uint32_t i = 0; i < n_kt; ++i) {
-            ok = mbar_wait(&sm.s_full[h][i & 1], (i >> 1) & 1);
-            if (!ok) break;
+        const uint32_t quad = warp & 3u;                    // scheduler this warp and its twin of the other head share
+        const bool two = (n_heads == 2);
+        // The scores of the current tile live in s[]; the next tile's are fetched
+        // from TMEM while this tile is still being exponentiated.
+        float s[kBN];
+        bool ok = mbar_wait(&sm.s_full[h][0], 0);
+        if (ok) {
             tc_fence_after();
-            const uint32_t s_addr = s_base + 64 * (i & 1);
-            float s[kBN];
-            tmem_ld32_nowait(s_addr, s);
-            tmem_ld32_nowait(s_addr + 32, s + 32);
+            tmem_ld32_nowait(s_base, s);
+            tmem_ld32_nowait(s_base + 32, s + 32);
             tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&sm.s_free[h][0]);                      // S[0] may take tile 2
+        }
+        for (uint32_t i = 0; ok && i < n_kt; ++i) {
             const uint32_t key0 = (t_first + i) * kBN;
             // tiles that no row's causal or window limit cuts through need no masking
             const bool edge = (key0 + kBN - 1 > p.p0 + tok0) || (p.window > 0);
@@ -338,38 +349,52 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 mx[3] = fmaxf(mx[3], s[j + 3]);
             }
             const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            if (tmax > WR_NEG_SENTINEL) {
-                const float tm2 = tmax * c2;
-                // Move the reference max (and rescale O) only when it is far behind.
-                if (m_ref == WR_NEG_SENTINEL) {
-                    m_ref = tm2;
-                } else if (tm2 > m_ref + kRescaleLog2) {
-                    const float a = ex2_approx(m_ref - tm2);
-                    l *= a;
-                    ok = mbar_wait(&sm.o_done[h], (i - 1) & 1);    // O must hold every earlier tile
-                    if (!ok) break;
-                    tc_fence_after();
+            // Move the reference max (and rescale O) only when it is far behind.
+            // The rescale uses warp-wide TMEM instructions, so the warp decides
+            // together; rows that do not need it multiply by one.
+            const float tm2 = tmax * c2;
+            const bool grow = (tmax > WR_NEG_SENTINEL) && (m_ref != WR_NEG_SENTINEL) && (tm2 > m_ref + kRescaleLog2);
+            if (tmax > WR_NEG_SENTINEL && m_ref == WR_NEG_SENTINEL) m_ref = tm2;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float a = grow ? ex2_approx(m_ref - tm2) : 1.0f;
+                // O must hold every earlier tile (tile i-1 was the last one issued)
+                ok = mbar_wait(&sm.pv_done[h][(i - 1) & 1], ((i - 1) >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
 #pragma unroll 1
-                    for (int c = 0; c < kHd; c += 32) {
-                        float o[32];
-                        tmem_ld32_nowait(o_addr + c, o);
-                        tmem_wait_ld();
+                for (int c = 0; c < kHd; c += 32) {
+                    float o[32];
+                    tmem_ld32_nowait(o_addr + c, o);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) o[j] *= a;
-                        tmem_st32(o_addr + c, o);
-                    }
-                    tmem_wait_st();
+                    for (int e = 0; e < 32; ++e) o[e] *= a;
+                    tmem_st32(o_addr + c, o);
+                }
+                tmem_wait_st();
+                if (grow) {
+                    l *= a;
                     m_ref = tm2;
                 }
             }
-            // P = 2^(s*c2 - m_ref) as F16 in operand order: row `row`, 8 chunks of 8 keys
-            // (P[i&1] is free: the scores of this tile were issued after the P.V of tile i-2)
+            // P = 2^(s*c2 - m_ref) as F16 in operand order: row `row`, 8 chunks of 8 keys;
+            // P[i&1] is free once the P.V of tile i-2 has read it
+            if (i >= 2) {
+                ok = mbar_wait(&sm.pv_done[h][i & 1], ((i >> 1) - 1) & 1);
+                if (!ok) break;
+            }
+            // The exponentials saturate the special-function unit, which this warp
+            // shares with the same-numbered warp of the other head: the two take
+            // turns, so that one's loads, max and hand-offs run under the other's
+            // exponentials instead of both queueing for the unit at once.
+            if (two && (h == 1 || i > 0)) {
+                ok = mbar_wait(&sm.xu_turn[quad][h], (h == 1 ? i : i - 1) & 1);
+                if (!ok) break;
+            }
             uint8_t *prow = sm.p[h][i & 1] + row * 128;
             // (no visible key yet for this row: every score is the sentinel and must give 0)
             const float neg_m = (m_ref == WR_NEG_SENTINEL) ? 0.f : -m_ref;
             float psum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            auto exp_chunk = [&](int c) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -381,12 +406,30 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                     w[e] = *reinterpret_cast<const uint32_t *>(&hh);
                 }
                 *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            };
+            const bool more = i + 1 < n_kt;
+            const uint32_t s_next = s_base + 64 * ((i + 1) & 1);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) exp_chunk(c);
+            if (more) {
+                // columns 0..31 are spent: refill them with the next tile's (its scores
+                // were issued two tiles ahead, so this wait normally falls through)
+                ok = mbar_wait(&sm.s_full[h][(i + 1) & 1], ((i + 1) >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                tmem_ld32_nowait(s_next, s);
             }
+#pragma unroll
+            for (int c = 4; c < 7; ++c) exp_chunk(c);
+            if (two && lane == 0) mbar_arrive(&sm.xu_turn[quad][h ^ 1]);   // a little early: hides the hand-off
+            exp_chunk(7);
+            if (more) tmem_ld32_nowait(s_next + 32, s + 32);
             l += (psum[0] + psum[1]) + (psum[2] + psum[3]);
-            if (i == n_kt - 1 && (key_end % kBN) != 0 && h == 0) {
+            if (i == n_kt - 1 && (key_end % kBN) != 0) {
                 // Cache rows past the last key were never written for this
                 // prompt (or belong to a rolled-back step): clear them in the
-                // staged V tile so that 0 * garbage cannot make a NaN.
+                // staged V tile so that 0 * garbage cannot make a NaN (each head's
+                // group does it before releasing its own P.V; the writes are equal).
                 ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1);
                 if (!ok) break;
                 if (row < kBN && key0 + row >= key_end) {
@@ -401,27 +444,49 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             fence_proxy_async();          // P (generic writes) is read by the tensor core
             tc_fence_before();
             mbar_arrive(&sm.p_ready[h][i & 1]);
+            if (more) {
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(&sm.s_free[h][(i + 1) & 1]);        // S[(i+1)&1] may take tile i+3
+            }
         }
+        tmem_wait_ld();                   // (an early exit may leave a fetch in flight)
         if (ok) {
-            // A parity wait may be at most one completion behind.  This group can
-            // be two tiles ahead of the tensor core here (only tile n_kt-3 is
-            // known to be done), so step through the last two completions.
-            if (n_kt >= 2) ok = mbar_wait(&sm.o_done[h], (n_kt - 2) & 1);
-            if (ok) ok = mbar_wait(&sm.o_done[h], (n_kt - 1) & 1);
+            // The last P.V completes after every earlier one (one issuing thread,
+            // in order); this group has already observed the previous phase of that
+            // barrier (tile n_kt-3), so the parity wait is one completion behind at most.
+            ok = mbar_wait(&sm.pv_done[h][(n_kt - 1) & 1], ((n_kt - 1) >> 1) & 1);
             if (ok) {
                 tc_fence_after();
                 const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-                float *orow = p.out + ((size_t)(tok0 + row) * p.n_q + head0 + h) * kHd;
+                // O leaves TMEM one row per thread; a row is 512 contiguous bytes of the
+                // output.  Each warp transposes its 32 rows through shared memory (this
+                // head's Q and P tiles are no longer needed: every MMA that read them has
+                // completed) so that one store instruction writes one whole row.  The
+                // 16-byte chunks of a row are XOR-swizzled with the row number, which
+                // keeps both the row-wise writes and the chunk-wise reads conflict free.
+                const uint32_t wq = warp & 3u;
+                uint8_t *stage = (wq < 2) ? sm.q[h] + wq * (kQBytes / 2) : sm.p[h][wq - 2];
+                float4 *srow = reinterpret_cast<float4 *>(stage + lane * (kHd * 4));
 #pragma unroll 1
                 for (int c = 0; c < kHd; c += 32) {
                     float o[32];
                     tmem_ld32_nowait(o_addr + c, o);
                     tmem_wait_ld();
-                    if (row < rows_here) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4 *>(orow + c + j) =
-                                make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
+                    for (int e = 0; e < 8; ++e)
+                        srow[((c >> 2) + e) ^ lane] = make_float4(o[4 * e] * inv, o[4 * e + 1] * inv,
+                                                                 o[4 * e + 2] * inv, o[4 * e + 3] * inv);
+                }
+                __syncwarp();
+                const uint32_t row0 = wq * 32u;                     // first row of this warp within the tile
+                float *obase = p.out + ((size_t)(tok0 + row0) * p.n_q + head0 + h) * kHd + lane * 4;
+                const size_t row_stride = (size_t)p.n_q * kHd;
+#pragma unroll 4
+                for (uint32_t r = 0; r < 32; ++r) {
+                    if (row0 + r < rows_here) {
+                        const float4 v = reinterpret_cast<const float4 *>(stage + r * (kHd * 4))[lane ^ r];
+                        *reinterpret_cast<float4 *>(obase + r * row_stride) = v;
                     }
                 }
             }
