@@ -210,7 +210,7 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
         p.page_bytes = wr_page_bytes(n_kv, hd);
         p.n_groups = n_sess * n_kv * qsubs;
         int rc = wr_ctx_reserve_ws(ctx, (size_t)std::max(items, 1u) * 8 * kTripleStride * sizeof(float),
-                                   (size_t)p.n_groups + 2);
+                                   (size_t)p.n_groups * kTicketsPerGroup + kTicketExtra);
         if (rc != WR_CUDA_OK) return rc;
         p.q = dq;
         p.out = dout;

@@ -15,7 +15,7 @@
 //     wants).  While it computes Q.K on tile t the V of tile t is in flight;
 //     while it computes P.V the K of tile t+1 is in flight — across item
 //     boundaries too.  No CTA-wide barrier exists.
-//   * items come from a global queue (the first two are static); an engine
+//   * items come from a global queue (the first one is static); an engine
 //     draws the index of a future item one item ahead and loads the page
 //     pointer of a future tile one tile ahead, so neither latency is exposed.
 //     Which engine runs an item has no effect on the item's result.
@@ -26,8 +26,16 @@
 //     low part, so scores keep F32-level query precision.  Probabilities are
 //     split the same way (movmatrix transposes them into the B operand) and
 //     O^T[dim, slot] += V^T[dim, key] . P^T[key, slot].  Accumulation is F32.
-//   * chunks of one (session, kv head, subgroup) are merged by the warp that
-//     finishes last (arrival ticket), in chunk order: deterministic.
+//   * chunks of one (session, kv head, subgroup) are merged in chunk order
+//     (deterministic) once the last of them has arrived.  The engines only
+//     count arrivals (a fire-and-forget release increment); the merging — L2
+//     round trips during which a stream would stand still — is done by two
+//     more warps per CTA: these share out (group, head pair) jobs over the
+//     whole grid from a counter, wait for the group's arrival count, and fetch
+//     all the rows of a job in one round trip.  While they wait they keep
+//     running the merge code on nothing, so that its instructions are still
+//     cached when the last groups — the end of the kernel's critical path —
+//     arrive.
 //   The kernel is HBM-bound by design: K and V are read exactly once.
 #pragma once
 
@@ -38,7 +46,10 @@ namespace wr_decode {
 constexpr int kHd = 128;
 constexpr int kTile = 64;                              // keys per tile = tokens per page
 constexpr int kWarps = 6;                              // engines per CTA
-constexpr int kThreads = kWarps * 32;
+constexpr int kMergeWarps = 2;                         // per CTA, after the engines
+constexpr int kThreads = (kWarps + kMergeWarps) * 32;
+constexpr int kTicketsPerGroup = 4;                    // arrival counters reserved per group: one per head pair (<= 8 heads)
+constexpr int kTicketExtra = 2;                        // after the tickets: work queue, engine exits
 constexpr uint32_t kBlockBytes = kTile * kHd * 2;      // one K or V tile of one head
 constexpr int kTripleStride = WR_CUDA_TRIPLE_PAD + kHd;  // m, l, 0, 0, o[128]
 constexpr int kMaxChunks = 16;
@@ -60,7 +71,7 @@ struct params {
     const float *q;
     float *out;        // [n_sess, n_q, hd] rows, or triples when emit_triples
     float *ws;         // per-item partial triples, 8 rows each
-    int *tickets;      // per-group arrival counters, then [n_groups] = queue, [n_groups+1] = exits
+    int *tickets;      // arrival counters [n_groups][kTicketsPerGroup], then the work queue and the engine exits
     int *err;
     uint32_t n_sess, n_q, n_kv, group, qsubs, emit_triples, n_groups;
     float scale;
@@ -90,11 +101,83 @@ __device__ __forceinline__ int atom_add_acq_rel(int *addr, int v)
     asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
     return old;
 }
+__device__ __forceinline__ void red_add_release(int *addr, int v)
+{
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_relaxed(const int *addr)
+{
+    int v;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 __device__ __forceinline__ int atom_add_relaxed(int *addr, int v)
 {
     int old;
     asm volatile("atom.add.relaxed.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
     return old;
+}
+
+// Merge the nc partial triples of two heads (hs0, hs0 + 1) of one (session, kv
+// head, subgroup), in chunk order, into their output rows.  Called by a whole
+// warp.  This is the end of the kernel's critical path and pure L2 latency, so
+// every load is issued before the first result is used: lane c holds (m, l) of
+// chunk c, and all chunk rows of both heads are in flight at once.
+__device__ __forceinline__ void merge_head_pair(const params &p, size_t row0, size_t first_item, uint32_t nc,
+                                             uint32_t hs0, uint32_t heads_here, uint32_t lane, bool dry_run)
+{
+    float mc[2], lc[2];
+    float4 ov[2][kMaxChunks];
+#pragma unroll
+    for (uint32_t e = 0; e < 2; ++e) {
+        const uint32_t hs = hs0 + e;
+        mc[e] = WR_NEG_SENTINEL;
+        lc[e] = 0.f;
+        if (lane < nc && hs < heads_here) {
+            const float *tr = p.ws + ((first_item + lane) * 8 + hs) * kTripleStride;
+            mc[e] = __ldcg(tr);
+            lc[e] = __ldcg(tr + 1);
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; ++j)
+            ov[e][j] = ((uint32_t)j < nc && hs < heads_here)
+                           ? __ldcg(reinterpret_cast<const float4 *>(
+                                 p.ws + ((first_item + j) * 8 + hs) * kTripleStride + WR_CUDA_TRIPLE_PAD) + lane)
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (uint32_t e = 0; e < 2; ++e) {
+        const uint32_t hs = hs0 + e;
+        if (hs >= heads_here) break;
+        float mstar = mc[e];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, off));
+        const float wgt = (mc[e] == WR_NEG_SENTINEL) ? 0.f : __expf(mc[e] - mstar);
+        const float wl = wgt * lc[e];
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; ++j) {
+            const float wj = __shfl_sync(0xffffffffu, wgt, j);
+            L += __shfl_sync(0xffffffffu, wl, j);
+            acc.x += wj * ov[e][j].x; acc.y += wj * ov[e][j].y;
+            acc.z += wj * ov[e][j].z; acc.w += wj * ov[e][j].w;
+        }
+        if (dry_run) continue;
+        if (p.emit_triples) {
+            float *tr = p.out + (row0 + hs) * kTripleStride;
+            reinterpret_cast<float4 *>(tr + WR_CUDA_TRIPLE_PAD)[lane] = acc;
+            if (lane == 0) {
+                tr[0] = mstar; tr[1] = L; tr[2] = 0.f; tr[3] = 0.f;
+            }
+        } else {
+            const float inv = (L > 0.f) ? 1.0f / L : 0.f;
+            acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+            reinterpret_cast<float4 *>(p.out + (row0 + hs) * kHd)[lane] = acc;
+        }
+    }
 }
 
 // One tile of work, with everything the compute loop needs to know about it.
@@ -109,8 +192,7 @@ struct tile_desc {
 // Walks this engine's tiles in order, across items.
 struct tile_stream {
     uint32_t it, s, h, qs, t, t_end;
-    uint32_t idx_next;    // index of the item after the current one (all lanes)
-    int pending;          // lane 0: result of the queue draw issued one item ago
+    int pending;          // lane 0: the next item's index, drawn from the queue one item ago
     bool have;
 };
 
@@ -125,10 +207,52 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
     const uint32_t engine = warp * gridDim.x + blockIdx.x;   // neighbours in item order sit on different SMs
     warp_smem &ws = sm.w[warp];
     uint64_t *bar_k = &sm.full_k[warp], *bar_v = &sm.full_v[warp];
-    int *queue = p.tickets + p.n_groups, *exits = queue + 1;
+    int *queue = p.tickets + (size_t)p.n_groups * kTicketsPerGroup, *exits = queue + 1;
     constexpr uint32_t kHeadsMax = 4 * NT;
     const uint32_t g = lane >> 2, t4 = lane & 3;
     const uint64_t stream_policy = l2_policy_evict_first();
+
+    if (warp >= kWarps) {
+        // ----------------------------------------------------------- merge warps
+        // Jobs are (group, head pair) in group order, which is also roughly the
+        // order in which groups complete; merge warp w of the grid takes jobs
+        // w, w + W, ...  Each job has its own arrival counter.
+        // While its group is incomplete the warp keeps running the merge code on
+        // nothing (no memory access): the engines' loop would otherwise push that
+        // code out of the instruction caches, and fetching it back costs several
+        // microseconds exactly when the last groups arrive.
+        constexpr uint32_t kPairs = kHeadsMax / 2;
+        const uint32_t n_mergers = gridDim.x * kMergeWarps;
+        const long long t_start = clock64();
+        for (uint32_t job = (warp - kWarps) * gridDim.x + blockIdx.x; job < p.n_groups * kPairs; job += n_mergers) {
+            const uint32_t gidx = job / kPairs, pair = job % kPairs;
+            const uint32_t qs = gidx % p.qsubs, sh = gidx / p.qsubs;
+            const uint32_t h = sh % p.n_kv, s = sh / p.n_kv;
+            const uint32_t nc = p.n_chunks[s];
+            const uint32_t heads = min(kHeadsMax, p.group - qs * kHeadsMax);
+            if (nc <= 1 || 2 * pair >= heads) continue;          // written directly by its engine / no such heads
+            const size_t row0 = (size_t)p.row[s] * p.n_q + h * p.group + qs * kHeadsMax;
+            const size_t first_item = (size_t)p.item_base[s] + (size_t)(h * p.qsubs + qs) * nc;
+            int *ticket = p.tickets + (size_t)gidx * kTicketsPerGroup + pair;
+            for (;;) {
+                int ready = 0;
+                if (lane == 0) {
+                    ready = ((uint32_t)ld_relaxed(ticket) == nc);
+                    if (ready) fence_acq_rel_gpu();
+                    else if (clock64() - t_start > 8000000000LL) {
+                        atomicExch(p.err, 4);
+                        ready = -1;
+                    }
+                }
+                ready = __shfl_sync(0xffffffffu, ready, 0);
+                if (ready < 0) return;
+                merge_head_pair(p, row0, first_item, ready ? nc : 0u, 2 * pair, heads, lane, !ready);
+                if (ready) break;
+            }
+            if (lane == 0) *ticket = 0;                          // ready for the next launch
+        }
+        return;
+    }
 
     if (lane == 0) {
         mbar_init(bar_k, 1);
@@ -143,22 +267,23 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         for (uint32_t s = 0; s < p.n_sess; ++s) {
             if (p.n_chunks[s] != 0) continue;
             float *base = p.out + (size_t)p.row[s] * p.n_q * kTripleStride;
-            for (uint32_t i = threadIdx.x; i < p.n_q * kTripleStride; i += kThreads)
+            for (uint32_t i = threadIdx.x; i < p.n_q * kTripleStride; i += kWarps * 32)   // (engine threads only)
                 base[i] = (i % kTripleStride == 0) ? WR_NEG_SENTINEL : 0.f;
         }
     }
 
-    // The first two items of an engine are fixed (engine, engine + n_engines);
-    // later ones come from the queue, drawn one item before they are needed.
+    // The first item of an engine is fixed (its own number); later ones come
+    // from the queue, drawn one item before they are needed.  Items are ordered
+    // longest chunks first, so the queue hands the short ones to whoever is
+    // free near the end.
     auto draw = [&]() -> int {       // lane 0: take the next item index from the queue
-        return 2 * (int)n_engines + atom_add_relaxed(queue, 1);
+        return (int)n_engines + atom_add_relaxed(queue, 1);
     };
     tile_stream ts;
     ts.have = false;
     ts.it = engine;
     ts.t = ts.t_end = 0;
     ts.s = ts.h = ts.qs = 0;
-    ts.idx_next = engine + n_engines;
     ts.pending = 0;
     if (lane == 0) ts.pending = draw();
     bool started = false;
@@ -169,8 +294,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         d.page = nullptr;
         if (!ts.have || ts.t >= ts.t_end) {
             if (started) {
-                ts.it = ts.idx_next;
-                ts.idx_next = (uint32_t)__shfl_sync(0xffffffffu, ts.pending, 0);
+                ts.it = (uint32_t)__shfl_sync(0xffffffffu, ts.pending, 0);
                 if (lane == 0) ts.pending = draw();
             }
             started = true;
@@ -431,70 +555,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
             }
 
             if (!direct) {
-                // Arrival ticket: the warp that completes the group merges it.
-                // __syncwarp orders every lane's partial stores before lane
-                // 0's release; the acquire side re-reads through L2.
+                // Count the arrival.  __syncwarp orders every lane's partial
+                // stores before lane 0's release; the merge warp that sees the
+                // full count acquires it and re-reads the partials through L2.
                 __syncwarp();
                 const uint32_t gidx = (d0.s * p.n_kv + d0.h) * p.qsubs + d0.qs;
-                int last = 0;
-                if (lane == 0) last = (atom_add_acq_rel(&p.tickets[gidx], 1) == (int)nc - 1);
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __syncwarp();
-                    const uint32_t c_here = (d0.it - p.item_base[d0.s]) % nc;
-                    const size_t first_item = (size_t)d0.it - c_here;
-                    // One load round for every head's (m, l): lane c holds chunk c.
-                    float mc[kHeadsMax], lc[kHeadsMax];
-#pragma unroll
-                    for (uint32_t hs = 0; hs < kHeadsMax; ++hs) {
-                        mc[hs] = WR_NEG_SENTINEL;
-                        lc[hs] = 0.f;
-                        if (lane < nc && hs < heads_here) {
-                            const float *tr = p.ws + ((first_item + lane) * 8 + hs) * kTripleStride;
-                            mc[hs] = __ldcg(tr);
-                            lc[hs] = __ldcg(tr + 1);
-                        }
-                    }
-#pragma unroll
-                    for (uint32_t hs = 0; hs < kHeadsMax; ++hs) {
-                        if (hs >= heads_here) break;
-                        // all chunk rows of this head in flight at once, merged in chunk order
-                        float4 ov[kMaxChunks];
-#pragma unroll
-                        for (int j = 0; j < kMaxChunks; ++j)
-                            ov[j] = ((uint32_t)j < nc)
-                                        ? __ldcg(reinterpret_cast<const float4 *>(
-                                              p.ws + ((first_item + j) * 8 + hs) * kTripleStride +
-                                              WR_CUDA_TRIPLE_PAD) + lane)
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
-                        float mstar = mc[hs];
-#pragma unroll
-                        for (int off = 16; off > 0; off >>= 1)
-                            mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, off));
-                        const float wgt = (mc[hs] == WR_NEG_SENTINEL) ? 0.f : __expf(mc[hs] - mstar);
-                        const float wl = wgt * lc[hs];
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                        float L = 0.f;
-#pragma unroll
-                        for (int j = 0; j < kMaxChunks; ++j) {
-                            const float wj = __shfl_sync(0xffffffffu, wgt, j);
-                            L += __shfl_sync(0xffffffffu, wl, j);
-                            acc.x += wj * ov[j].x; acc.y += wj * ov[j].y;
-                            acc.z += wj * ov[j].z; acc.w += wj * ov[j].w;
-                        }
-                        if (p.emit_triples) {
-                            float *tr = p.out + (row0 + hs) * kTripleStride;
-                            reinterpret_cast<float4 *>(tr + WR_CUDA_TRIPLE_PAD)[lane] = acc;
-                            if (lane == 0) {
-                                tr[0] = mstar; tr[1] = L; tr[2] = 0.f; tr[3] = 0.f;
-                            }
-                        } else {
-                            const float inv = (L > 0.f) ? 1.0f / L : 0.f;
-                            acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-                            reinterpret_cast<float4 *>(p.out + (row0 + hs) * kHd)[lane] = acc;
-                        }
-                    }
-                    if (lane == 0) p.tickets[gidx] = 0;   // ready for the next launch
+                if (lane == 0) {
+                    int *ticket = p.tickets + (size_t)gidx * kTicketsPerGroup;
+                    for (uint32_t pr = 0; 2 * pr < heads_here; ++pr) red_add_release(ticket + pr, 1);
                 }
             }
         }

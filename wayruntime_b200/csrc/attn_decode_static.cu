@@ -36,7 +36,7 @@ namespace {
 using namespace wr_decode;
 
 constexpr size_t kScratchFloats = (size_t)WR_CUDA_STATIC_MAX_ITEMS * 8 * kTripleStride;
-constexpr size_t kTicketInts = WR_CUDA_STATIC_MAX_GROUPS + 2;     // + queue, + exits
+constexpr size_t kTicketInts = (size_t)WR_CUDA_STATIC_MAX_GROUPS * kTicketsPerGroup + kTicketExtra;     // + queue, exits
 
 // In host code these names are host-side stand-ins, not device addresses: the
 // kernel gets the pointers that cudaGetSymbolAddress returns.
@@ -157,7 +157,7 @@ extern "C" int wr_cuda_attn_decode_static(wr_cuda_ctx *ctx, uint32_t n_sess, wr_
     p.scale = (scale_override > 0.0f) ? scale_override : 1.0f / sqrtf((float)hd);
     // The array keeps whatever the previous call (or an aborted one) left:
     // the counters must start at zero.
-    WR_CUDA_TRY(cudaMemsetAsync(sp->tickets, 0, (p.n_groups + 2) * sizeof(int), ctx->stream));
+    WR_CUDA_TRY(cudaMemsetAsync(sp->tickets, 0, ((size_t)p.n_groups * kTicketsPerGroup + kTicketExtra) * sizeof(int), ctx->stream));
     const uint32_t grid = std::max(1u, std::min<uint32_t>(items, (uint32_t)ctx->sm_count));
     if (nt == 1)
         attn_decode_hd128_kernel<1><<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(p);
