@@ -360,6 +360,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
     uint32_t qb[NT][kHd / 16][2];       // B operand: Q^T, slot column g
     float m[NT], l[NT];
     float oacc[NT][kHd / 16][4];        // O^T: dims on M, slots on N
+    // Arrival of a finished item is signalled with a release, which has to wait
+    // for the item's partial stores to be acknowledged (about a microsecond).
+    // Mid-stream that wait is avoided by signalling one item late, just before
+    // the next item's stores are issued: by then the old ones completed long ago.
+    int *pend_ticket = nullptr;         // lane 0: counters of the item not yet signalled
+    uint32_t pend_pairs = 0;
+    auto signal_pending = [&]() {       // lane 0 only
+        for (uint32_t pr = 0; pr < pend_pairs; ++pr) red_add_release(pend_ticket + pr, 1);
+        pend_ticket = nullptr;
+        pend_pairs = 0;
+    };
 
     while (d0.flags & 1u) {
         const uint32_t seq_len = p.b.seq_len[d0.s];
@@ -523,6 +534,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
             const uint32_t nc = p.n_chunks[d0.s];
             const bool direct = (nc == 1);
             const size_t row0 = (size_t)p.row[d0.s] * p.n_q + d0.h * p.group + d0.qs * kHeadsMax;
+            if (lane == 0 && pend_ticket) signal_pending();      // the previous item (before new stores are in flight)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 float lt = l[nt];
@@ -555,20 +567,23 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
             }
 
             if (!direct) {
-                // Count the arrival.  __syncwarp orders every lane's partial
-                // stores before lane 0's release; the merge warp that sees the
-                // full count acquires it and re-reads the partials through L2.
+                // Note the arrival (signalled as described above).  __syncwarp
+                // orders every lane's partial stores before lane 0's release; the
+                // merge warp that sees the full count acquires it and re-reads
+                // the partials through L2.
                 __syncwarp();
                 const uint32_t gidx = (d0.s * p.n_kv + d0.h) * p.qsubs + d0.qs;
                 if (lane == 0) {
-                    int *ticket = p.tickets + (size_t)gidx * kTicketsPerGroup;
-                    for (uint32_t pr = 0; 2 * pr < heads_here; ++pr) red_add_release(ticket + pr, 1);
+                    pend_ticket = p.tickets + (size_t)gidx * kTicketsPerGroup;
+                    pend_pairs = (heads_here + 1) / 2;
+                    if (!(d1.flags & 1u)) signal_pending();      // the engine's last item: nothing to wait for
                 }
             }
         }
         d0 = d1;
         d1 = next_tile();
     }
+    if (lane == 0 && pend_ticket) signal_pending();
 
     // The last engine to leave rewinds the queue for the next launch.
     if (lane == 0) {
