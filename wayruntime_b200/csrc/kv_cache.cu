@@ -376,14 +376,18 @@ struct append_params {
     uint32_t rope;
 };
 
-// A pair's cos/sin depend only on (position, j): they are computed once per
-// token and reused for every KV head and every Q head of that token.
+// A pair's cos/sin depend only on (position, j): each CTA computes the table
+// of its token once and applies it to its share of the heads.
 //
-// One CTA per token.  Phase 1: thread j < hd/2 evaluates the pair's angle
-// (the reference's range reduction is a serial float loop, so this is the
-// latency of the kernel).  Phase 2: every thread takes (head, pair) work
-// items across K, V and Q — independent loads and stores.
+// A token's work is split over 1 + ceil(n_q / 8) CTAs: CTA y = 0 of a token
+// takes K and V of every KV head, CTA y >= 1 takes eight Q heads.  The kernel
+// is latency bound (a few hundred KB per step), so every thread first issues
+// the loads of its first (head, pair) items, then the pair angles are
+// evaluated (by the first hd/2 threads) while those loads are in flight, and
+// only then are the rows rotated and stored.
 constexpr int kAppendThreads = 256;
+constexpr int kAppendQHeads = 8;          // Q heads per CTA
+constexpr int kAppendBatch = 2;           // (head, pair) items per thread whose loads are issued together
 
 __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const append_params p)
 {
@@ -393,50 +397,98 @@ __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const ap
     const uint32_t s = tok_idx / p.n_tokens, t = tok_idx % p.n_tokens;
     const uint32_t row = p.b.seq_len[s] + t;                     // absolute position = cache row
     float *cs_tab = trig, *sn_tab = trig + half;
-    if (p.rope) {
-        const float ln_theta = wrmath::log_ref(p.theta);
-        for (uint32_t j = threadIdx.x; j < p.n_rot; j += blockDim.x) {
-            float sn, cs;
-            wrmath::rope_angle(row, j, p.hd, ln_theta, sn, cs);
-            cs_tab[j] = cs;
-            sn_tab[j] = sn;
+    auto build_table = [&]() {
+        if (p.rope) {
+            const float ln_theta = wrmath::log_ref(p.theta);
+            for (uint32_t j = threadIdx.x; j < p.n_rot; j += blockDim.x) {
+                float sn, cs;
+                wrmath::rope_angle(row, j, p.hd, ln_theta, sn, cs);
+                cs_tab[j] = cs;
+                sn_tab[j] = sn;
+            }
         }
-    }
-    char *page = (char *)p.b.pages[s][row / kPageTokens];
-    const uint32_t tk = row % kPageTokens;
-    __syncthreads();
+        __syncthreads();
+    };
+    constexpr uint32_t kStep = kAppendThreads * kAppendBatch;
 
-    const float *__restrict__ krow = p.k_rows + (size_t)tok_idx * p.n_kv * p.hd;
-    const float *__restrict__ vrow = p.v_rows + (size_t)tok_idx * p.n_kv * p.hd;
-    const uint32_t kv_work = p.n_kv * half;
-    for (uint32_t i = threadIdx.x; i < kv_work; i += blockDim.x) {
-        const uint32_t h = i / half, j = i % half;
-        const bool rot = p.rope && j < p.n_rot;
-        const float x0 = krow[h * p.hd + j], x1 = krow[h * p.hd + j + half];
-        const float v0 = vrow[h * p.hd + j], v1 = vrow[h * p.hd + j + half];
-        float y0 = x0, y1 = x1;
-        if (rot) {   // kernels.c:1406-1407, products rounded separately
-            const float cs = cs_tab[j], sn = sn_tab[j];
-            y0 = wrmath::sub(wrmath::mul(x0, cs), wrmath::mul(x1, sn));
-            y1 = wrmath::add(wrmath::mul(x0, sn), wrmath::mul(x1, cs));
+    if (blockIdx.y == 0) {
+        // ---- K and V rows of this token into the page
+        char *page = (char *)p.b.pages[s][row / kPageTokens];
+        const uint32_t tk = row % kPageTokens;
+        const float *__restrict__ krow = p.k_rows + (size_t)tok_idx * p.n_kv * p.hd;
+        const float *__restrict__ vrow = p.v_rows + (size_t)tok_idx * p.n_kv * p.hd;
+        const uint32_t work = p.n_kv * half;
+        bool table_ready = false;
+        for (uint32_t base = 0; base < work; base += kStep) {
+            float x0[kAppendBatch], x1[kAppendBatch], v0[kAppendBatch], v1[kAppendBatch];
+#pragma unroll
+            for (int u = 0; u < kAppendBatch; ++u) {
+                const uint32_t i = base + u * kAppendThreads + threadIdx.x;
+                if (i < work) {
+                    const uint32_t h = i / half, j = i % half;
+                    x0[u] = krow[h * p.hd + j];
+                    x1[u] = krow[h * p.hd + j + half];
+                    v0[u] = vrow[h * p.hd + j];
+                    v1[u] = vrow[h * p.hd + j + half];
+                }
+            }
+            if (!table_ready) {
+                build_table();
+                table_ready = true;
+            }
+#pragma unroll
+            for (int u = 0; u < kAppendBatch; ++u) {
+                const uint32_t i = base + u * kAppendThreads + threadIdx.x;
+                if (i >= work) continue;
+                const uint32_t h = i / half, j = i % half;
+                float y0 = x0[u], y1 = x1[u];
+                if (p.rope && j < p.n_rot) {   // kernels.c:1406-1407, products rounded separately
+                    const float cs = cs_tab[j], sn = sn_tab[j];
+                    y0 = wrmath::sub(wrmath::mul(x0[u], cs), wrmath::mul(x1[u], sn));
+                    y1 = wrmath::add(wrmath::mul(x0[u], sn), wrmath::mul(x1[u], cs));
+                }
+                const uint32_t off0 = wr_elem_off(tk, j, p.hd), off1 = wr_elem_off(tk, j + half, p.hd);
+                char *kb = page + wr_block_off(h, 0, p.hd);
+                char *vb = page + wr_block_off(h, 1, p.hd);
+                *(uint16_t *)(kb + off0) = wr_f32_to_f16_trunc(y0);
+                *(uint16_t *)(kb + off1) = wr_f32_to_f16_trunc(y1);
+                *(uint16_t *)(vb + off0) = wr_f32_to_f16_trunc(v0[u]);
+                *(uint16_t *)(vb + off1) = wr_f32_to_f16_trunc(v1[u]);
+            }
         }
-        const uint32_t off0 = wr_elem_off(tk, j, p.hd), off1 = wr_elem_off(tk, j + half, p.hd);
-        char *kb = page + wr_block_off(h, 0, p.hd);
-        char *vb = page + wr_block_off(h, 1, p.hd);
-        *(uint16_t *)(kb + off0) = wr_f32_to_f16_trunc(y0);
-        *(uint16_t *)(kb + off1) = wr_f32_to_f16_trunc(y1);
-        *(uint16_t *)(vb + off0) = wr_f32_to_f16_trunc(v0);
-        *(uint16_t *)(vb + off1) = wr_f32_to_f16_trunc(v1);
+        return;
     }
-    if (p.q_rows && p.rope) {
-        float *qrow = p.q_rows + (size_t)tok_idx * p.n_q * p.hd;
-        const uint32_t q_work = p.n_q * p.n_rot;
-        for (uint32_t i = threadIdx.x; i < q_work; i += blockDim.x) {
+
+    // ---- eight Q heads of this token, rotated in place
+    if (!(p.q_rows && p.rope)) return;
+    const uint32_t head0 = (blockIdx.y - 1) * kAppendQHeads;
+    const uint32_t n_heads = min((uint32_t)kAppendQHeads, p.n_q - head0);
+    float *qrow = p.q_rows + ((size_t)tok_idx * p.n_q + head0) * p.hd;
+    const uint32_t work = n_heads * p.n_rot;
+    bool table_ready = false;
+    for (uint32_t base = 0; base < work; base += kStep) {
+        float x0[kAppendBatch], x1[kAppendBatch];
+#pragma unroll
+        for (int u = 0; u < kAppendBatch; ++u) {
+            const uint32_t i = base + u * kAppendThreads + threadIdx.x;
+            if (i < work) {
+                const uint32_t h = i / p.n_rot, j = i % p.n_rot;
+                x0[u] = qrow[h * p.hd + j];
+                x1[u] = qrow[h * p.hd + j + half];
+            }
+        }
+        if (!table_ready) {
+            build_table();
+            table_ready = true;
+        }
+#pragma unroll
+        for (int u = 0; u < kAppendBatch; ++u) {
+            const uint32_t i = base + u * kAppendThreads + threadIdx.x;
+            if (i >= work) continue;
             const uint32_t h = i / p.n_rot, j = i % p.n_rot;
             const float cs = cs_tab[j], sn = sn_tab[j];
-            const float x0 = qrow[h * p.hd + j], x1 = qrow[h * p.hd + j + half];
-            qrow[h * p.hd + j] = wrmath::sub(wrmath::mul(x0, cs), wrmath::mul(x1, sn));
-            qrow[h * p.hd + j + half] = wrmath::add(wrmath::mul(x0, sn), wrmath::mul(x1, cs));
+            qrow[h * p.hd + j] = wrmath::sub(wrmath::mul(x0[u], cs), wrmath::mul(x1[u], sn));
+            qrow[h * p.hd + j + half] = wrmath::add(wrmath::mul(x0[u], sn), wrmath::mul(x1[u], cs));
         }
     }
 }
@@ -479,7 +531,9 @@ int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
     p.n_rot = (n_rot_pairs >= 1 && n_rot_pairs < half) ? n_rot_pairs : half;  // kernels.c:1381-1383
     p.theta = (theta_base < 1.0f) ? 10000.0f : theta_base;                    // kernels.c:1374
     p.rope = (flags & WR_CUDA_APPEND_ROPE) ? 1u : 0u;
-    rope_kv_append_kernel<<<n_sess * n_tokens, kAppendThreads, hd * sizeof(float), ctx->stream>>>(p);
+    const uint32_t q_ctas = (dq && p.rope) ? (n_q_heads + kAppendQHeads - 1) / kAppendQHeads : 0u;
+    const dim3 grid(n_sess * n_tokens, 1 + q_ctas);
+    rope_kv_append_kernel<<<grid, kAppendThreads, hd * sizeof(float), ctx->stream>>>(p);
     ctx->launches++;
     WR_CUDA_TRY(cudaGetLastError());
     return WR_CUDA_OK;
