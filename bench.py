@@ -300,6 +300,78 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
             "output_finite": finite}
 
 
+# --------------------- KV-head-sharded serving shape (BASELINE config 5)
+
+C5_SESS, C5_PREFILL, C5_HKV, C5_GROUP = 8, 8192, 8, 5
+
+
+def measure_kv_head_sharded(ctx, stream, torch, rank, world, reps):
+    """8 sessions, 40Q/8KV heads, hd 128: an 8192-token causal prefill per
+    session, then batched decode steps over the 8193 cached keys.  KV-head
+    groups are independent (src/core/kernels.c:1477), so rank r holds
+    8/world KV heads with their five Q heads each and no collective is
+    needed; at one GPU it holds all eight.  Prefill: `reps` launches of one
+    session's prompt; decode: 4*reps launches of the 8-session step."""
+    hkv = max(1, C5_HKV // world)
+    hq = hkv * C5_GROUP
+    ctx.set_attn_max_seq(LC_CTX)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED + 55 + rank)
+    n_ctx = C5_PREFILL + 1
+    kvs = [ctx.kv_create(1, hkv, HD, n_ctx) for _ in range(C5_SESS)]
+    for kv in kvs:
+        for which in (0, 1):
+            rows = torch.randn((n_ctx, hkv, HD), generator=gen, device="cuda").to(torch.float16)
+            kv.write_rows(0, which, 0, rows.view(torch.int16))
+    qp = torch.randn((C5_PREFILL, hq, HD), generator=gen, device="cuda").to(torch.float16)
+    outp = torch.empty((C5_PREFILL, hq, HD), device="cuda", dtype=torch.float32)
+    qd = torch.randn((C5_SESS, hq, HD), generator=gen, device="cuda", dtype=torch.float32)
+    outd = torch.empty_like(qd)
+    batch = wr_batch(kvs)
+    lens = [n_ctx] * C5_SESS
+
+    def timed(fn, n):
+        for _ in range(2):
+            fn(0)
+        ctx.sync()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(n):
+            fn(i)
+        b.record(stream)
+        ctx.sync()
+        ms = a.elapsed_time(b) / n
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    pf_ms = timed(lambda i: ctx.attn_prefill(kvs[i % C5_SESS], 0, 0, C5_PREFILL, qp, outp, hq), reps)
+    dec_ms = timed(lambda i: ctx.attn_decode(batch, 0, lens, qd, outd, hq), 4 * reps)
+    finite = bool(torch.isfinite(outp).all().item() and torch.isfinite(outd).all().item())
+    for kv in kvs:
+        kv.close()
+    ctx.set_attn_max_seq(LC_CTX)
+    flops = 4.0 * hq * HD * C5_PREFILL * (C5_PREFILL + 1) / 2            # per session, per rank
+    dec_bytes = C5_SESS * n_ctx * hkv * HD * 2 * 2 + 2 * C5_SESS * hq * HD * 4
+    peak_bw, src = measured_peaks()
+    peak_tf = 1590.0
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak_tf = float(json.load(f)["bf16_tflops"])
+    tf = flops / (pf_ms * 1e-3) / 1e12
+    gbs = dec_bytes / (dec_ms * 1e-3) / 1e9
+    return {"workload": f"c5_kv_head_sharded: 8 sessions, 8192-token prefill + decode, {hq}Q/{hkv}KV heads "
+                        f"per GPU ({world} GPU(s), no collective)",
+            "prefill_ms_per_session": pf_ms, "prefill_tflops_per_gpu": tf, "prefill_frac": tf / peak_tf,
+            "decode_ms_per_step": dec_ms, "decode_gbs_per_gpu": gbs, "decode_frac": gbs / peak_bw,
+            "decode_tokens_per_s": C5_SESS / (dec_ms * 1e-3), "peak_source": f"of {src}",
+            "output_finite": finite}
+
+
 def wr_batch(kvs):
     import wayruntime_b200 as wr
     return wr.Batch(kvs)
@@ -490,6 +562,13 @@ def run_gpu_arm(args):
         if world > 1:
             raise
 
+    try:
+        kv_head_sharded = measure_kv_head_sharded(ctx, stream, torch, rank, world, 5)
+    except Exception as exc:
+        kv_head_sharded = {"error": f"{type(exc).__name__}: {exc}"}
+        if world > 1:
+            raise
+
     # ---- parity spot check + CPU baseline on rank 0 (bounded sample)
     cpu = None
     max_err = None
@@ -526,7 +605,7 @@ def run_gpu_arm(args):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": 1e3 * e2e_s / args.steps},
             "gpu_launches": int(launches), "launch_mode": launch_mode,
-            "roofline_prefill": prefill, "split_kv": split_kv,
+            "roofline_prefill": prefill, "split_kv": split_kv, "kv_head_sharded": kv_head_sharded,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_hd128_kernel",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_src}",

@@ -77,6 +77,22 @@ def test_decode_ragged_batch_group_sizes(ctx, hq, hkv):
         kv.close()
 
 
+def test_decode_more_merge_jobs_than_merge_warps(ctx):
+    """16 sessions x 32 KV heads, every one split into chunks: 512 groups, i.e.
+    more (group, head pair) merge jobs than the grid has merge warps, so that
+    each merge warp has to work through several of them in turn."""
+    lens = [600 + 37 * i for i in range(16)]
+    q, ks, vs, kvs = _ragged_batch(ctx, lens, 64, 32, 128, 333)
+    out = decode(ctx, kvs, lens, q, 64)
+    rc, want = port().decode_batch(q, ks, vs, threads=8)
+    assert rc == 0
+    assert np.abs(out - want).max() <= TOL
+    again = decode(ctx, kvs, lens, q, 64)                   # counters were left ready for the next launch
+    assert np.array_equal(again.view(np.uint32), out.view(np.uint32))
+    for kv in kvs:
+        kv.close()
+
+
 def test_decode_full_length_sessions(ctx):
     """Llama-3-8B geometry at the config's longest context (4096) and the
     seed-uniform lengths in between; 16 sessions in one grid."""

@@ -189,7 +189,7 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
             const uint32_t tile_lo = key_lo / kTile;
             const uint32_t span = n_tiles - tile_lo;
             // Chunk length is a function of this session alone.
-            const uint32_t ct = std::max<uint32_t>(kMinChunkTiles, (span + kMaxChunks - 1) / kMaxChunks);
+            const uint32_t ct = chunk_tiles_for(span);
             const uint32_t nc = (span + ct - 1) / ct;          // 0 for an empty shard
             p.b.pages[i] = kv[s]->d_pages + (size_t)layer * kv[s]->n_pages;
             p.b.seq_len[i] = len;

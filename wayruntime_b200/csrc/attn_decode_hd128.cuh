@@ -52,8 +52,20 @@ constexpr int kTicketsPerGroup = 4;                    // arrival counters reser
 constexpr int kTicketExtra = 2;                        // after the tickets: work queue, engine exits
 constexpr uint32_t kBlockBytes = kTile * kHd * 2;      // one K or V tile of one head
 constexpr int kTripleStride = WR_CUDA_TRIPLE_PAD + kHd;  // m, l, 0, 0, o[128]
-constexpr int kMaxChunks = 16;
+constexpr int kMaxChunks = 32;                         // per session (lane c of a merge warp holds chunk c)
+constexpr int kChunkBatch = 16;                        // chunk rows a merge keeps in flight per head
 constexpr int kMinChunkTiles = 2;
+
+// Tiles per chunk: a function of the session's own span only (batch
+// invariance).  Up to 16 chunks for sessions of at most 64 tiles; longer ones
+// may use up to 32, which keeps items short enough to balance a small batch of
+// long sessions over all engines.
+__host__ __device__ inline uint32_t chunk_tiles_for(uint32_t span_tiles)
+{
+    const uint32_t max_chunks = span_tiles > 64u ? (uint32_t)kMaxChunks : 16u;
+    const uint32_t ct = (span_tiles + max_chunks - 1) / max_chunks;
+    return ct < (uint32_t)kMinChunkTiles ? (uint32_t)kMinChunkTiles : ct;
+}
 
 // Sessions appear here sorted by descending length (longest chunks are drawn
 // first); row[i] is the caller's index of entry i.
@@ -128,7 +140,6 @@ __device__ __forceinline__ void merge_head_pair(const params &p, size_t row0, si
                                              uint32_t hs0, uint32_t heads_here, uint32_t lane, bool dry_run)
 {
     float mc[2], lc[2];
-    float4 ov[2][kMaxChunks];
 #pragma unroll
     for (uint32_t e = 0; e < 2; ++e) {
         const uint32_t hs = hs0 + e;
@@ -139,43 +150,61 @@ __device__ __forceinline__ void merge_head_pair(const params &p, size_t row0, si
             mc[e] = __ldcg(tr);
             lc[e] = __ldcg(tr + 1);
         }
+    }
+    float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+    float mstar[2], wgt[2], L[2] = {0.f, 0.f};
+    // chunk rows in batches of kChunkBatch (one batch unless the session is long)
+#pragma unroll 1
+    for (uint32_t c0 = 0; c0 == 0 || c0 < nc; c0 += kChunkBatch) {
+        float4 ov[2][kChunkBatch];
 #pragma unroll
-        for (int j = 0; j < kMaxChunks; ++j)
-            ov[e][j] = ((uint32_t)j < nc && hs < heads_here)
-                           ? __ldcg(reinterpret_cast<const float4 *>(
-                                 p.ws + ((first_item + j) * 8 + hs) * kTripleStride + WR_CUDA_TRIPLE_PAD) + lane)
-                           : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t e = 0; e < 2; ++e) {
+            const uint32_t hs = hs0 + e;
+#pragma unroll
+            for (int j = 0; j < kChunkBatch; ++j)
+                ov[e][j] = (c0 + j < nc && hs < heads_here)
+                               ? __ldcg(reinterpret_cast<const float4 *>(
+                                     p.ws + ((first_item + c0 + j) * 8 + hs) * kTripleStride + WR_CUDA_TRIPLE_PAD) + lane)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (c0 == 0) {
+#pragma unroll
+            for (uint32_t e = 0; e < 2; ++e) {
+                mstar[e] = mc[e];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1)
+                    mstar[e] = fmaxf(mstar[e], __shfl_xor_sync(0xffffffffu, mstar[e], off));
+                wgt[e] = (mc[e] == WR_NEG_SENTINEL) ? 0.f : __expf(mc[e] - mstar[e]);
+            }
+        }
+#pragma unroll
+        for (uint32_t e = 0; e < 2; ++e) {
+            const float wl = wgt[e] * lc[e];
+#pragma unroll
+            for (int j = 0; j < kChunkBatch; ++j) {
+                const float wj = __shfl_sync(0xffffffffu, wgt[e], (c0 + j) & 31);
+                L[e] += __shfl_sync(0xffffffffu, wl, (c0 + j) & 31);
+                acc[e].x += wj * ov[e][j].x; acc[e].y += wj * ov[e][j].y;
+                acc[e].z += wj * ov[e][j].z; acc[e].w += wj * ov[e][j].w;
+            }
+        }
     }
 #pragma unroll
     for (uint32_t e = 0; e < 2; ++e) {
         const uint32_t hs = hs0 + e;
         if (hs >= heads_here) break;
-        float mstar = mc[e];
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1)
-            mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, off));
-        const float wgt = (mc[e] == WR_NEG_SENTINEL) ? 0.f : __expf(mc[e] - mstar);
-        const float wl = wgt * lc[e];
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        float L = 0.f;
-#pragma unroll
-        for (int j = 0; j < kMaxChunks; ++j) {
-            const float wj = __shfl_sync(0xffffffffu, wgt, j);
-            L += __shfl_sync(0xffffffffu, wl, j);
-            acc.x += wj * ov[e][j].x; acc.y += wj * ov[e][j].y;
-            acc.z += wj * ov[e][j].z; acc.w += wj * ov[e][j].w;
-        }
+        float4 &a4 = acc[e];
         if (dry_run) continue;
         if (p.emit_triples) {
             float *tr = p.out + (row0 + hs) * kTripleStride;
-            reinterpret_cast<float4 *>(tr + WR_CUDA_TRIPLE_PAD)[lane] = acc;
+            reinterpret_cast<float4 *>(tr + WR_CUDA_TRIPLE_PAD)[lane] = a4;
             if (lane == 0) {
-                tr[0] = mstar; tr[1] = L; tr[2] = 0.f; tr[3] = 0.f;
+                tr[0] = mstar[e]; tr[1] = L[e]; tr[2] = 0.f; tr[3] = 0.f;
             }
         } else {
-            const float inv = (L > 0.f) ? 1.0f / L : 0.f;
-            acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-            reinterpret_cast<float4 *>(p.out + (row0 + hs) * kHd)[lane] = acc;
+            const float inv = (L[e] > 0.f) ? 1.0f / L[e] : 0.f;
+            a4.x *= inv; a4.y *= inv; a4.z *= inv; a4.w *= inv;
+            reinterpret_cast<float4 *>(p.out + (row0 + hs) * kHd)[lane] = a4;
         }
     }
 }

@@ -122,7 +122,7 @@ extern "C" int wr_cuda_attn_decode_static(wr_cuda_ctx *ctx, uint32_t n_sess, wr_
         const uint32_t n_tiles = (len + kTile - 1) / kTile;
         const uint32_t tile_lo = key_lo / kTile;
         const uint32_t span = n_tiles - tile_lo;
-        const uint32_t ct = std::max<uint32_t>(kMinChunkTiles, (span + kMaxChunks - 1) / kMaxChunks);
+        const uint32_t ct = chunk_tiles_for(span);
         const uint32_t nc = (span + ct - 1) / ct;
         p.b.pages[i] = kv[s]->d_pages + (size_t)layer * kv[s]->n_pages;
         p.b.seq_len[i] = len;
