@@ -286,6 +286,33 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     finite = bool(torch.isfinite(out).all().item())
+    # the same step with all-gather + merge as ONE kernel over NVLink peer memory
+    fused = None
+    if world > 1:
+        try:
+            xchg = splitkv.make_exchange(ctx, rows_n, HD)
+            out_f = torch.empty_like(q)
+
+            def step_fused():
+                splitkv.decode_split_kv(ctx, batch, 0, lens, q, out_f, HQ, triples=triples, exchange=xchg)
+
+            for _ in range(3):
+                step_fused()
+            ctx.sync()
+            dist.barrier()
+            a.record(stream)
+            for _ in range(reps):
+                step_fused()
+            b.record(stream)
+            ctx.sync()
+            t = torch.tensor([a.elapsed_time(b) / reps], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            fused = {"ms_per_step": float(t.item()),
+                     "identical_to_allgather_path": bool(torch.equal(out_f, out))}
+            dist.barrier()
+            xchg.close()
+        except Exception as exc:
+            fused = {"error": f"{type(exc).__name__}: {exc}"}
     for kv in kvs:
         kv.close()
     total_bytes = N_SESS * LC_CTX * HKV * HD * 2 * 2
@@ -297,7 +324,7 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
             "kv_bytes_total": total_bytes, "hbm_gbs_per_gpu": per_gpu, "frac_per_gpu": per_gpu / peak,
             "peak_source": f"of {src}", "allgather_bytes_per_rank": rows_n * (4 + HD) * 4,
             "collective": "none" if world == 1 else "one NCCL all-gather of triples per step",
-            "output_finite": finite}
+            "fused_exchange_merge": fused, "output_finite": finite}
 
 
 # --------------------- KV-head-sharded serving shape (BASELINE config 5)

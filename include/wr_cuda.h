@@ -209,6 +209,36 @@ int wr_cuda_attn_combine(wr_cuda_ctx *ctx, uint32_t n_shards, uint32_t n_rows,
                          uint32_t head_dim, const float *triples, float *out,
                          int mem);
 
+/* ---- Peer exchange for key-sharded decode (no reference counterpart: the
+ * reference is single-device; this is the multi-GPU form of the merge above).
+ *
+ * One process per GPU.  Every rank creates an exchange object (a device
+ * buffer for world x max_rows triples, twice, plus flags), publishes its
+ * handle (WR_CUDA_XCHG_HANDLE_BYTES opaque bytes, valid in other processes of
+ * this machine), receives everybody's handles in rank order by whatever
+ * transport the host has, and connects: the peers' buffers are then mapped
+ * over NVLink.  WR_CUDA_ERR_UNSUPPORTED when two of the devices cannot reach
+ * each other's memory. */
+typedef struct wr_cuda_xchg wr_cuda_xchg;
+#define WR_CUDA_XCHG_MAX_WORLD    8
+#define WR_CUDA_XCHG_HANDLE_BYTES 64
+
+int  wr_cuda_xchg_create(wr_cuda_ctx *ctx, uint32_t world, uint32_t rank,
+                         uint32_t max_rows, uint32_t head_dim, wr_cuda_xchg **out);
+int  wr_cuda_xchg_handle(wr_cuda_xchg *x, void *handle_out);
+int  wr_cuda_xchg_connect(wr_cuda_xchg *x, const void *handles /* world x 64 bytes */);
+void wr_cuda_xchg_destroy(wr_cuda_xchg *x);
+
+/* All-gather + merge in one kernel: stores this rank's triples (device, F32
+ * [n_rows, WR_CUDA_TRIPLE_PAD + head_dim], as written by
+ * wr_cuda_attn_decode_partial) into every rank's buffer, waits (bounded; an
+ * expired wait surfaces at wr_cuda_ctx_sync as WR_CUDA_ERR_INTERNAL) for every
+ * rank's triples of the same step, and merges them in rank order into out
+ * (device, F32 [n_rows, head_dim]).  Every rank must make the same sequence of
+ * calls with the same n_rows.  Enqueues on the context's stream and returns. */
+int wr_cuda_attn_exchange_combine(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_rows,
+                                  const float *triples, float *out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,8 @@
 """GPU, 2 ranks over NCCL: long-context decode with the key sequence sharded
 across devices (partial attention per rank -> one all-gather of the triples ->
-local merge) against the unsharded reference attention.  Skipped on a box with
+local merge) against the unsharded reference attention, and the same step with
+the all-gather and the merge fused into one kernel over NVLink peer memory
+(wr_cuda_attn_exchange_combine), which must give identical bits.  Skipped on a box with
 fewer than two GPUs; the same plumbing runs on CPU ranks in
 tests/test_splitkv_gloo.py."""
 import os
@@ -50,8 +52,19 @@ def _worker(rank, world, port_no, result_q):
     ctx.sync()
     torch.cuda.synchronize()
     got = out.cpu().numpy()
+    # the same step with the all-gather and the merge fused into one kernel over
+    # peer memory: same merge order, so the result has to be identical
+    xchg = splitkv.make_exchange(ctx, len(lens) * hq, hd)
+    out2 = torch.full_like(qd, float("nan"))
+    for _ in range(3):                      # three times: both buffer parities are used again
+        splitkv.decode_split_kv(ctx, kvs, 0, local, qd, out2, hq, exchange=xchg)
+    ctx.sync()
+    torch.cuda.synchronize()
+    same = bool(np.array_equal(out2.cpu().numpy().view(np.uint32), got.view(np.uint32)))
+    dist.barrier()
+    xchg.close()
     rc, want = P.decode_batch(q, ks, vs, threads=4, max_seq=32768)
-    result_q.put((rank, rc, float(np.abs(got - want).max())))
+    result_q.put((rank, rc, float(np.abs(got - want).max()), same))
     for kv in kvs:
         kv.close()
     ctx.close()
@@ -73,6 +86,7 @@ def test_key_sharded_decode_two_gpus():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for _rank, rc, err in results:
+    for _rank, rc, err, fused_same in results:
         assert rc == 0
         assert err <= 2e-3
+        assert fused_same, "fused exchange+merge differs from all-gather + merge"

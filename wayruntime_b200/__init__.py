@@ -7,6 +7,7 @@ library is missing.
 """
 from .binding import (  # noqa: F401
     Batch,
+    Exchange,
     Context,
     KVCache,
     WrCudaError,
@@ -22,6 +23,6 @@ from .binding import (  # noqa: F401
 )
 
 __all__ = [
-    "Batch", "Context", "KVCache", "WrCudaError", "MEM_DEVICE", "MEM_HOST", "F16", "F32",
+    "Batch", "Context", "Exchange", "KVCache", "WrCudaError", "MEM_DEVICE", "MEM_HOST", "F16", "F32",
     "APPEND_ROPE", "TRIPLE_PAD", "device_check", "load_library", "status_name",
 ]

@@ -34,6 +34,8 @@ EXPORTS = [
     "wr_cuda_kv_read_rows", "wr_cuda_kv_append", "wr_cuda_attn_decode", "wr_cuda_attn_prefill",
     "wr_cuda_attn_decode_partial", "wr_cuda_attn_combine", "wr_cuda_decode_step",
     "wr_cuda_attn_decode_static",
+    "wr_cuda_xchg_create", "wr_cuda_xchg_handle", "wr_cuda_xchg_connect", "wr_cuda_xchg_destroy",
+    "wr_cuda_attn_exchange_combine",
 ]
 
 
@@ -86,6 +88,11 @@ def load_library():
                                       u32, f32, u32, u32, f32, u32, i32]),
         "wr_cuda_attn_decode_static": (i32, [vp, u32, C.POINTER(vp), u32, C.POINTER(u32), vp, vp,
                                              u32, f32, u32]),
+        "wr_cuda_xchg_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
+        "wr_cuda_xchg_handle": (i32, [vp, vp]),
+        "wr_cuda_xchg_connect": (i32, [vp, vp]),
+        "wr_cuda_xchg_destroy": (None, [vp]),
+        "wr_cuda_attn_exchange_combine": (i32, [vp, vp, u32, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -254,6 +261,49 @@ class Context:
         rc = self._lib.wr_cuda_attn_prefill(self._h, kv._h, layer, p0, n, qp, q_dtype, op,
                                             n_q_heads, scale, window, mem)
         _check(rc, "wr_cuda_attn_prefill")
+
+
+XCHG_HANDLE_BYTES = 64
+
+
+class Exchange:
+    """Peer buffers for the fused all-gather + merge of split-KV triples
+    (wr_cuda_xchg): create on every rank, pass everybody's `handle` (rank order)
+    to `connect`, then call `combine` once per step on every rank."""
+
+    def __init__(self, ctx: "Context", world: int, rank: int, max_rows: int, head_dim: int):
+        self._ctx = ctx
+        self._lib = ctx._lib
+        self.world, self.rank = world, rank
+        h = C.c_void_p()
+        _check(self._lib.wr_cuda_xchg_create(ctx._h, world, rank, max_rows, head_dim, C.byref(h)),
+               "wr_cuda_xchg_create")
+        self._h = h
+
+    @property
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(XCHG_HANDLE_BYTES)
+        _check(self._lib.wr_cuda_xchg_handle(self._h, buf), "wr_cuda_xchg_handle")
+        return buf.raw
+
+    def connect(self, handles) -> None:
+        blob = b"".join(handles)
+        if len(blob) != self.world * XCHG_HANDLE_BYTES:
+            raise ValueError("one 64-byte handle per rank, in rank order")
+        _check(self._lib.wr_cuda_xchg_connect(self._h, C.c_char_p(blob)), "wr_cuda_xchg_connect")
+
+    def combine(self, n_rows: int, triples, out) -> None:
+        tp, tm, _t = _buf(triples)
+        op, om, _o = _buf(out)
+        if tm != MEM_DEVICE or om != MEM_DEVICE:
+            raise ValueError("wr_cuda_attn_exchange_combine takes device buffers only")
+        _check(self._lib.wr_cuda_attn_exchange_combine(self._ctx._h, self._h, n_rows, tp, op),
+               "wr_cuda_attn_exchange_combine")
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.wr_cuda_xchg_destroy(self._h)
+            self._h = None
 
 
 class Batch:

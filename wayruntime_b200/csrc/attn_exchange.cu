@@ -1,0 +1,258 @@
+// attn_exchange.cu — all-gather of split-KV partial triples and their merge in
+// ONE kernel, over NVLink peer memory.
+//
+// Key-sharded long-context decode leaves every rank with one (m, l, o) triple
+// per (session, q head) for its range of keys (wr_cuda_attn_decode_partial);
+// the result is the online-softmax merge of the ranks' triples in rank order
+// (the reference's update, src/core/kernels.c:1503-1506, across shards).  The
+// library path is an NCCL all-gather followed by wr_cuda_attn_combine: two more
+// launches and a collective's latency for 270 KB.  Here each rank's kernel
+//   1. stores its own triples into every rank's exchange buffer (plain 16-byte
+//      stores to peer memory mapped through CUDA IPC; its own buffer included),
+//   2. publishes them: the last CTA to finish sets this rank's flag in every
+//      peer's buffer to the step number (system-scope release),
+//   3. waits — with a time limit — until its own buffer carries every rank's
+//      flag for this step (system-scope acquire),
+//   4. merges the world's triples from its own buffer into the output rows.
+// Buffers and flags are double-buffered by step parity: a rank can be at most
+// one step ahead of a peer that still reads the previous step's triples.
+// No multicast, no TMA: ordinary loads and stores only.
+#include <algorithm>
+
+#include "wr_internal.cuh"
+
+struct wr_cuda_xchg {
+    wr_cuda_ctx *ctx = nullptr;
+    uint32_t world = 0, rank = 0, max_rows = 0, hd = 0;
+    size_t bytes = 0;
+    char *local = nullptr;                       // this rank's buffer (cudaMalloc, IPC-exported)
+    char *peer[WR_CUDA_XCHG_MAX_WORLD] = {};     // every rank's buffer as mapped here (peer[rank] == local)
+    bool opened[WR_CUDA_XCHG_MAX_WORLD] = {};
+    int *done = nullptr;                         // CTAs of the current launch that finished storing
+    uint32_t step = 0;
+    bool connected = false;
+};
+
+namespace {
+
+constexpr size_t kFlagBytes = 1024;              // flags[2][world] at the head of a buffer
+
+struct xchg_params {
+    char *peer[WR_CUDA_XCHG_MAX_WORLD];
+    const float *local_triples;
+    float *out;
+    int *done;
+    int *err;
+    uint32_t world, rank, max_rows, hd, n_rows, step, parity;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t *addr, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *addr)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float *slot_rows(char *buf, uint32_t parity, uint32_t src, const xchg_params &p)
+{
+    const size_t stride = WR_CUDA_TRIPLE_PAD + p.hd;
+    return reinterpret_cast<float *>(buf + kFlagBytes) + ((size_t)parity * p.world + src) * p.max_rows * stride;
+}
+__device__ __forceinline__ uint32_t *slot_flag(char *buf, uint32_t parity, uint32_t src, const xchg_params &p)
+{
+    return reinterpret_cast<uint32_t *>(buf) + parity * p.world + src;
+}
+
+__global__ void __launch_bounds__(256) attn_exchange_combine_kernel(const xchg_params p)
+{
+    const uint32_t stride = WR_CUDA_TRIPLE_PAD + p.hd;
+    const uint32_t row_f4 = stride / 4;
+    const uint32_t total_f4 = p.n_rows * row_f4;
+    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, gsize = gridDim.x * blockDim.x;
+
+    // 1. this rank's triples into every rank's buffer
+    const float4 *src = reinterpret_cast<const float4 *>(p.local_triples);
+    for (uint32_t peer = 0; peer < p.world; ++peer) {
+        float4 *dst = reinterpret_cast<float4 *>(slot_rows(p.peer[peer], p.parity, p.rank, p));
+        for (uint32_t i = gtid; i < total_f4; i += gsize) dst[i] = src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+
+    // 2. the last CTA to get here publishes the step number to every rank
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+        s_ok = 1;
+        if (atomicAdd(p.done, 1) == (int)gridDim.x - 1) {
+            __threadfence_system();
+            for (uint32_t peer = 0; peer < p.world; ++peer)
+                st_release_sys(slot_flag(p.peer[peer], p.parity, p.rank, p), p.step);
+            *p.done = 0;                                  // ready for the next launch
+        }
+    }
+    __syncthreads();
+
+    // 3. wait for every rank's triples of this step (bounded)
+    if (threadIdx.x < p.world) {
+        const uint32_t *flag = slot_flag(p.peer[p.rank], p.parity, threadIdx.x, p);
+        const long long t0 = clock64();
+        while (ld_acquire_sys(flag) != p.step) {
+            if (clock64() - t0 > 4000000000LL) {          // about two seconds
+                atomicExch(p.err, 21);
+                s_ok = 0;
+                break;
+            }
+            __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+
+    // 4. merge in rank order: one thread per four output elements
+    const uint32_t out_f4 = p.hd / 4;
+    const uint32_t total_out = p.n_rows * out_f4;
+    for (uint32_t i = gtid; i < total_out; i += gsize) {
+        const uint32_t row = i / out_f4, c = i % out_f4;
+        float mstar = WR_NEG_SENTINEL;
+        for (uint32_t g = 0; g < p.world; ++g)
+            mstar = fmaxf(mstar, __ldcg(slot_rows(p.peer[p.rank], p.parity, g, p) + (size_t)row * stride));
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t g = 0; g < p.world; ++g) {
+            const float *tr = slot_rows(p.peer[p.rank], p.parity, g, p) + (size_t)row * stride;
+            const float m = __ldcg(tr);
+            const float wgt = (m == WR_NEG_SENTINEL) ? 0.f : __expf(m - mstar);
+            L += wgt * __ldcg(tr + 1);
+            const float4 o = __ldcg(reinterpret_cast<const float4 *>(tr + WR_CUDA_TRIPLE_PAD) + c);
+            acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
+        }
+        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (L > 0.f) r = make_float4(acc.x / L, acc.y / L, acc.z / L, acc.w / L);
+        reinterpret_cast<float4 *>(p.out)[i] = r;
+    }
+}
+
+}  // namespace
+
+extern "C" int wr_cuda_xchg_create(wr_cuda_ctx *ctx, uint32_t world, uint32_t rank, uint32_t max_rows,
+                                   uint32_t head_dim, wr_cuda_xchg **out)
+{
+    if (!ctx || !out) return WR_CUDA_ERR_INVAL;
+    *out = nullptr;
+    if (world == 0 || world > WR_CUDA_XCHG_MAX_WORLD || rank >= world || max_rows == 0) return WR_CUDA_ERR_INVAL;
+    if (head_dim == 0 || head_dim % 4 != 0 || head_dim > 1024) return WR_CUDA_ERR_INVAL;
+    std::lock_guard<std::mutex> g(ctx->lock);
+    WR_CUDA_TRY(cudaSetDevice(ctx->device));
+    wr_cuda_xchg *x = new (std::nothrow) wr_cuda_xchg();
+    if (!x) return WR_CUDA_ERR_NOMEM;
+    x->ctx = ctx;
+    x->world = world;
+    x->rank = rank;
+    x->max_rows = max_rows;
+    x->hd = head_dim;
+    x->bytes = kFlagBytes + (size_t)2 * world * max_rows * (WR_CUDA_TRIPLE_PAD + head_dim) * sizeof(float);
+    if (cudaMalloc((void **)&x->local, x->bytes) != cudaSuccess ||
+        cudaMalloc((void **)&x->done, sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (x->local) (void)cudaFree(x->local);
+        delete x;
+        return WR_CUDA_ERR_NOMEM;
+    }
+    if (cudaMemset(x->local, 0, x->bytes) != cudaSuccess || cudaMemset(x->done, 0, sizeof(int)) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess) {
+        (void)cudaGetLastError();
+        (void)cudaFree(x->local);
+        (void)cudaFree(x->done);
+        delete x;
+        return WR_CUDA_ERR_INTERNAL;
+    }
+    x->peer[rank] = x->local;
+    x->connected = (world == 1);
+    *out = x;
+    return WR_CUDA_OK;
+}
+
+extern "C" int wr_cuda_xchg_handle(wr_cuda_xchg *x, void *handle_out)
+{
+    if (!x || !handle_out) return WR_CUDA_ERR_INVAL;
+    static_assert(sizeof(cudaIpcMemHandle_t) <= WR_CUDA_XCHG_HANDLE_BYTES, "handle size");
+    std::lock_guard<std::mutex> g(x->ctx->lock);
+    WR_CUDA_TRY(cudaSetDevice(x->ctx->device));
+    cudaIpcMemHandle_t h;
+    WR_CUDA_TRY(cudaIpcGetMemHandle(&h, x->local));
+    memset(handle_out, 0, WR_CUDA_XCHG_HANDLE_BYTES);
+    memcpy(handle_out, &h, sizeof(h));
+    return WR_CUDA_OK;
+}
+
+extern "C" int wr_cuda_xchg_connect(wr_cuda_xchg *x, const void *handles)
+{
+    if (!x || !handles) return WR_CUDA_ERR_INVAL;
+    if (x->connected) return WR_CUDA_ERR_STATE;
+    std::lock_guard<std::mutex> g(x->ctx->lock);
+    WR_CUDA_TRY(cudaSetDevice(x->ctx->device));
+    for (uint32_t r = 0; r < x->world; ++r) {
+        if (r == x->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)r * WR_CUDA_XCHG_HANDLE_BYTES, sizeof(h));
+        void *ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return WR_CUDA_ERR_UNSUPPORTED;               // no peer access between these two devices
+        }
+        x->peer[r] = (char *)ptr;
+        x->opened[r] = true;
+    }
+    x->connected = true;
+    return WR_CUDA_OK;
+}
+
+extern "C" void wr_cuda_xchg_destroy(wr_cuda_xchg *x)
+{
+    if (!x) return;
+    {
+        std::lock_guard<std::mutex> g(x->ctx->lock);
+        (void)cudaSetDevice(x->ctx->device);
+        (void)cudaStreamSynchronize(x->ctx->stream);
+        for (uint32_t r = 0; r < x->world; ++r)
+            if (x->opened[r]) (void)cudaIpcCloseMemHandle(x->peer[r]);
+        if (x->local) (void)cudaFree(x->local);
+        if (x->done) (void)cudaFree(x->done);
+        (void)cudaGetLastError();
+    }
+    delete x;
+}
+
+extern "C" int wr_cuda_attn_exchange_combine(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_rows,
+                                             const float *triples, float *out)
+{
+    if (!ctx || !x || x->ctx != ctx || !triples || !out) return WR_CUDA_ERR_INVAL;
+    if (!x->connected) return WR_CUDA_ERR_STATE;
+    if (n_rows == 0 || n_rows > x->max_rows) return WR_CUDA_ERR_INVAL;
+    if (((uintptr_t)triples | (uintptr_t)out) & 15u) return WR_CUDA_ERR_INVAL;   // rows move as 16-byte vectors
+    std::lock_guard<std::mutex> g(ctx->lock);
+    WR_CUDA_TRY(cudaSetDevice(ctx->device));
+    xchg_params p;
+    for (uint32_t r = 0; r < WR_CUDA_XCHG_MAX_WORLD; ++r) p.peer[r] = x->peer[r];
+    p.local_triples = triples;
+    p.out = out;
+    p.done = x->done;
+    p.err = ctx->dev_err;
+    p.world = x->world;
+    p.rank = x->rank;
+    p.max_rows = x->max_rows;
+    p.hd = x->hd;
+    p.n_rows = n_rows;
+    p.step = ++x->step;
+    p.parity = x->step & 1u;
+    // few CTAs: every one of them has to be resident while it waits for the peers
+    const uint32_t work = n_rows * ((WR_CUDA_TRIPLE_PAD + x->hd) / 4);
+    const uint32_t blocks = std::max(1u, std::min((work + 255u) / 256u, (uint32_t)ctx->sm_count / 2u));
+    attn_exchange_combine_kernel<<<blocks, 256, 0, ctx->stream>>>(p);
+    ctx->launches++;
+    WR_CUDA_TRY(cudaGetLastError());
+    return WR_CUDA_OK;
+}

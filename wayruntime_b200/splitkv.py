@@ -52,11 +52,28 @@ def merge_triples_reference(triples: np.ndarray) -> np.ndarray:
     return np.where(den[:, None] > 0, num / safe[:, None], np.float32(0)).astype(np.float32)
 
 
+def make_exchange(ctx, max_rows, head_dim, group=None):
+    """An `Exchange` connected to every rank of `group` (handles travel through
+    torch.distributed's object all-gather; the data path afterwards is the
+    kernel's own NVLink stores)."""
+    import torch.distributed as dist
+    import wayruntime_b200 as wr
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    x = wr.Exchange(ctx, world, rank, max_rows, head_dim)
+    handles = [None] * world
+    dist.all_gather_object(handles, x.handle, group=group)
+    x.connect(handles)
+    dist.barrier(group)
+    return x
+
+
 def decode_split_kv(ctx, kvs, layer, local_lens, q, out, n_q_heads, scale=0.0, group=None,
-                    triples=None, gathered=None):
+                    triples=None, gathered=None, exchange=None):
     """One decode step over key-sharded caches.  q, out: CUDA float32 tensors
     [n_sess, n_q_heads, hd]; local_lens: keys of each session held by this rank.
-    Everything is enqueued on the context's stream (set it current for NCCL)."""
+    Everything is enqueued on the context's stream (set it current for NCCL).
+    With `exchange` (see make_exchange) the all-gather and the merge are one
+    kernel over peer memory instead of an NCCL collective and a merge kernel."""
     import torch
     import torch.distributed as dist
     n_sess, _, hd = q.shape
@@ -64,6 +81,9 @@ def decode_split_kv(ctx, kvs, layer, local_lens, q, out, n_q_heads, scale=0.0, g
     if triples is None:
         triples = torch.empty((rows, TRIPLE_PAD + hd), dtype=torch.float32, device=q.device)
     ctx.attn_decode_partial(kvs, layer, local_lens, q, triples, n_q_heads, scale=scale)
+    if exchange is not None:
+        exchange.combine(rows, triples, out)
+        return out
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         gathered = triples
