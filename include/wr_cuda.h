@@ -149,7 +149,9 @@ int wr_cuda_attn_decode(wr_cuda_ctx *ctx, uint32_t n_sess,
  * (src/core/batch.c:152-164 -> session.c:471-496) for all sessions at once.
  * q: F32 [n_sess, n_q_heads, head_dim], un-rotated on entry (rotated in
  * place when it is device memory); out: F32 of the same shape.  With host
- * buffers q, k_rows and v_rows cross the bus once and only out comes back. */
+ * buffers q, k_rows and v_rows cross the bus once and only out comes back;
+ * page-locked host buffers are read and written by the kernels themselves (no
+ * copy operations), pageable ones are staged.  Host q rows are left as given. */
 int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv,
                         uint32_t layer, const uint32_t *positions, float *q,
                         const float *k_rows, const float *v_rows, float *out,

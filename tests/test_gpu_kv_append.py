@@ -150,3 +150,62 @@ def test_rows_round_trip_all_layers(ctx):
                 kv.write_rows(layer, which, 25, rows)
                 assert np.array_equal(kv.read_rows(layer, which, 25, 150), rows)
         kv.close()
+
+
+@pytest.mark.parametrize("n_rot", [0, 20])
+def test_decode_step_host_buffer_paths_agree(ctx, n_rot):
+    """wr_cuda_decode_step with host buffers: pageable arrays are staged through
+    copies, page-locked ones are read and written by the kernels directly.  Both
+    must leave the same cache bytes and attention rows as the device-buffer
+    sequence append -> decode, and must leave the host's Q rows untouched."""
+    import torch
+    P = port()
+    hq, hkv, hd, theta = 32, 8, 128, 5e5
+    lens = [130, 1, 700, 64]
+    n = len(lens)
+    q = _gen.normal(41, (n, hq, hd))
+    k_new = _gen.normal(42, (n, hkv, hd))
+    v_new = _gen.normal(43, (n, hkv, hd))
+    hist_k = [P.f32_to_f16(_gen.normal(50 + i, (ln - 1, hkv, hd))) for i, ln in enumerate(lens)]
+    hist_v = [P.f32_to_f16(_gen.normal(60 + i, (ln - 1, hkv, hd))) for i, ln in enumerate(lens)]
+
+    def fresh():
+        kvs = [ctx.kv_create(1, hkv, hd, 1024) for _ in lens]
+        for kv, hk, hv in zip(kvs, hist_k, hist_v):
+            if hk.shape[0]:
+                kv.write_rows(0, 0, 0, hk)
+                kv.write_rows(0, 1, 0, hv)
+        return kvs
+
+    pos = [ln - 1 for ln in lens]
+    # device buffers: append (rotates q in place), then decode
+    kvs = fresh()
+    qd = torch.from_numpy(q.copy()).cuda()
+    outd = torch.empty_like(qd)
+    ctx.kv_append(kvs, 0, pos, torch.from_numpy(k_new).cuda(), torch.from_numpy(v_new).cuda(), qd, hq,
+                  theta=theta, n_rot_pairs=n_rot)
+    ctx.attn_decode(kvs, 0, lens, qd, outd, hq)
+    ctx.sync()
+    want = outd.cpu().numpy()
+    want_rows = [(kv.read_rows(0, 0, ln - 1, 1), kv.read_rows(0, 1, ln - 1, 1)) for kv, ln in zip(kvs, lens)]
+    for kv in kvs:
+        kv.close()
+    # pageable host arrays, then page-locked host tensors
+    for pinned in (False, True):
+        kvs = fresh()
+        if pinned:
+            hq_, hk_, hv_ = (torch.from_numpy(a.copy()).pin_memory() for a in (q, k_new, v_new))
+            hout = torch.full((n, hq, hd), float("nan")).pin_memory()
+        else:
+            hq_, hk_, hv_ = q.copy(), k_new.copy(), v_new.copy()
+            hout = np.full((n, hq, hd), np.nan, np.float32)
+        ctx.decode_step(kvs, 0, pos, hq_, hk_, hv_, hout, hq, theta=theta, n_rot_pairs=n_rot)
+        got = hout.numpy() if pinned else hout
+        assert np.array_equal(bits(got), bits(want)), f"pinned={pinned}"
+        q_after = hq_.numpy() if pinned else hq_
+        assert np.array_equal(bits(q_after), bits(q)), "host Q rows must stay as given"
+        for kv, ln, (wk, wv) in zip(kvs, lens, want_rows):
+            assert np.array_equal(kv.read_rows(0, 0, ln - 1, 1), wk)
+            assert np.array_equal(kv.read_rows(0, 1, ln - 1, 1), wv)
+        for kv in kvs:
+            kv.close()

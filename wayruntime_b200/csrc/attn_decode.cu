@@ -318,28 +318,47 @@ extern "C" int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv
     const uint32_t hd = kv[0]->hd, n_kv = kv[0]->n_kv;
     const size_t kv_bytes = (size_t)n_sess * n_kv * hd * sizeof(float);
     const size_t q_bytes = (size_t)n_sess * n_q_heads * hd * sizeof(float);
-    const float *dk = k_rows, *dv = v_rows;
+    const float *dk = k_rows, *dv = v_rows, *dq_in = nullptr;
     float *dq = q, *dout = out;
+    bool staged_out = false;
     if (mem == WR_CUDA_MEM_HOST) {
+        // Page-locked host buffers (cudaHostAlloc / cudaHostRegister) are read and
+        // written by the kernels themselves: the K/V/Q rows cross the bus as the
+        // append kernel's loads and the attention rows as the decode kernel's
+        // stores, with no copy operations in the stream.  Q is rotated into a
+        // device buffer (the decode kernel reads it many times); the host's Q
+        // rows stay as they are.  Pageable buffers take the staged path.
+        const void *dev_k = wr_host_device_alias(k_rows), *dev_v = wr_host_device_alias(v_rows);
+        const void *dev_q = wr_host_device_alias(q), *dev_o = wr_host_device_alias(out);
+        const bool zero_copy = dev_k && dev_v && dev_q && dev_o && (flags & WR_CUDA_APPEND_ROPE);
         rc = wr_ctx_reserve_stage(ctx, 2 * kv_bytes + 2 * q_bytes, 0);
         if (rc != WR_CUDA_OK) return rc;
         char *d = (char *)ctx->stage_dev;
-        dk = (const float *)d;
-        dv = (const float *)(d + kv_bytes);
         dq = (float *)(d + 2 * kv_bytes);
-        dout = (float *)(d + 2 * kv_bytes + q_bytes);
-        WR_CUDA_TRY(cudaMemcpyAsync((void *)dk, k_rows, kv_bytes, cudaMemcpyHostToDevice, ctx->stream));
-        WR_CUDA_TRY(cudaMemcpyAsync((void *)dv, v_rows, kv_bytes, cudaMemcpyHostToDevice, ctx->stream));
-        WR_CUDA_TRY(cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
+        if (zero_copy) {
+            dk = (const float *)dev_k;
+            dv = (const float *)dev_v;
+            dq_in = (const float *)dev_q;
+            dout = (float *)dev_o;
+        } else {
+            dk = (const float *)d;
+            dv = (const float *)(d + kv_bytes);
+            dout = (float *)(d + 2 * kv_bytes + q_bytes);
+            staged_out = true;
+            WR_CUDA_TRY(cudaMemcpyAsync((void *)dk, k_rows, kv_bytes, cudaMemcpyHostToDevice, ctx->stream));
+            WR_CUDA_TRY(cudaMemcpyAsync((void *)dv, v_rows, kv_bytes, cudaMemcpyHostToDevice, ctx->stream));
+            WR_CUDA_TRY(cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
+        }
     }
     rc = wr_append_launch(ctx, n_sess, kv, layer, positions, 1, dk, dv, dq, n_q_heads, theta_base,
-                          n_rot_pairs, flags);
+                          n_rot_pairs, flags, dq_in);
     if (rc != WR_CUDA_OK) return rc;
     rc = wr_decode_launch(ctx, n_sess, kv, layer, seq_lens, dq, dout, n_q_heads, scale_override,
                           window, 0);
     if (rc != WR_CUDA_OK) return rc;
     if (mem == WR_CUDA_MEM_HOST) {
-        WR_CUDA_TRY(cudaMemcpyAsync(out, dout, q_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        if (staged_out)
+            WR_CUDA_TRY(cudaMemcpyAsync(out, dout, q_bytes, cudaMemcpyDeviceToHost, ctx->stream));
         WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     }
     return WR_CUDA_OK;

@@ -364,13 +364,25 @@ extern "C" int wr_cuda_kv_read_rows(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
     return kv_rows_xfer(ctx, kv, layer, which, row0, n, dst, mem, 0);
 }
 
+const void *wr_host_device_alias(const void *p)
+{
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    if (attr.type != cudaMemoryTypeHost || !attr.devicePointer) return nullptr;
+    return attr.devicePointer;
+}
+
 // ------------------------------------------------- fused RoPE + KV append
 
 struct append_params {
     wr_batch_desc b;                 // b.seq_len[s] = first row (position) of session s
     const float *k_rows;
     const float *v_rows;
-    float *q_rows;
+    float *q_rows;                   // rotated Q rows are written here ...
+    const float *q_in;               // ... from these rows (the same buffer when rotating in place)
     uint32_t n_sess, n_tokens, n_kv, n_q, hd, n_rot;
     float theta;
     uint32_t rope;
@@ -459,12 +471,17 @@ __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const ap
         return;
     }
 
-    // ---- eight Q heads of this token, rotated in place
+    // ---- eight Q heads of this token: rotated in place, or from q_in into q_rows
+    // (then the pairs beyond n_rot are copied through as well)
     if (!(p.q_rows && p.rope)) return;
     const uint32_t head0 = (blockIdx.y - 1) * kAppendQHeads;
     const uint32_t n_heads = min((uint32_t)kAppendQHeads, p.n_q - head0);
-    float *qrow = p.q_rows + ((size_t)tok_idx * p.n_q + head0) * p.hd;
-    const uint32_t work = n_heads * p.n_rot;
+    const size_t qoff = ((size_t)tok_idx * p.n_q + head0) * p.hd;
+    float *qrow = p.q_rows + qoff;
+    const float *__restrict__ qsrc = p.q_in + qoff;
+    const bool in_place = (p.q_in == p.q_rows);
+    const uint32_t pairs = in_place ? p.n_rot : half;             // per head
+    const uint32_t work = n_heads * pairs;
     bool table_ready = false;
     for (uint32_t base = 0; base < work; base += kStep) {
         float x0[kAppendBatch], x1[kAppendBatch];
@@ -472,9 +489,9 @@ __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const ap
         for (int u = 0; u < kAppendBatch; ++u) {
             const uint32_t i = base + u * kAppendThreads + threadIdx.x;
             if (i < work) {
-                const uint32_t h = i / p.n_rot, j = i % p.n_rot;
-                x0[u] = qrow[h * p.hd + j];
-                x1[u] = qrow[h * p.hd + j + half];
+                const uint32_t h = i / pairs, j = i % pairs;
+                x0[u] = qsrc[h * p.hd + j];
+                x1[u] = qsrc[h * p.hd + j + half];
             }
         }
         if (!table_ready) {
@@ -485,10 +502,15 @@ __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const ap
         for (int u = 0; u < kAppendBatch; ++u) {
             const uint32_t i = base + u * kAppendThreads + threadIdx.x;
             if (i >= work) continue;
-            const uint32_t h = i / p.n_rot, j = i % p.n_rot;
-            const float cs = cs_tab[j], sn = sn_tab[j];
-            qrow[h * p.hd + j] = wrmath::sub(wrmath::mul(x0[u], cs), wrmath::mul(x1[u], sn));
-            qrow[h * p.hd + j + half] = wrmath::add(wrmath::mul(x0[u], sn), wrmath::mul(x1[u], cs));
+            const uint32_t h = i / pairs, j = i % pairs;
+            float y0 = x0[u], y1 = x1[u];
+            if (j < p.n_rot) {
+                const float cs = cs_tab[j], sn = sn_tab[j];
+                y0 = wrmath::sub(wrmath::mul(x0[u], cs), wrmath::mul(x1[u], sn));
+                y1 = wrmath::add(wrmath::mul(x0[u], sn), wrmath::mul(x1[u], cs));
+            }
+            qrow[h * p.hd + j] = y0;
+            qrow[h * p.hd + j + half] = y1;
         }
     }
 }
@@ -512,7 +534,7 @@ int wr_append_validate(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv,
 int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
                      const uint32_t *positions, uint32_t n_tokens, const float *dk,
                      const float *dv, float *dq, uint32_t n_q_heads, float theta_base,
-                     uint32_t n_rot_pairs, uint32_t flags)
+                     uint32_t n_rot_pairs, uint32_t flags, const float *dq_in)
 {
     append_params p;
     for (uint32_t s = 0; s < n_sess; ++s) {
@@ -523,6 +545,7 @@ int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
     p.k_rows = dk;
     p.v_rows = dv;
     p.q_rows = dq;
+    p.q_in = dq_in ? dq_in : dq;
     p.n_sess = n_sess;
     p.n_tokens = n_tokens;
     p.n_kv = kv[0]->n_kv;
@@ -572,7 +595,7 @@ extern "C" int wr_cuda_kv_append(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *
         }
     }
     rc = wr_append_launch(ctx, n_sess, kv, layer, positions, n_tokens, dk, dv, dq, n_q_heads,
-                          theta_base, n_rot_pairs, flags);
+                          theta_base, n_rot_pairs, flags, nullptr);
     if (rc != WR_CUDA_OK) return rc;
     if (mem == WR_CUDA_MEM_HOST) {
         if (q_rows && (flags & WR_CUDA_APPEND_ROPE))

@@ -121,7 +121,12 @@ int wr_append_validate(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv,
 int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
                      const uint32_t *positions, uint32_t n_tokens, const float *dk,
                      const float *dv, float *dq, uint32_t n_q_heads, float theta_base,
-                     uint32_t n_rot_pairs, uint32_t flags);
+                     uint32_t n_rot_pairs, uint32_t flags,
+                     const float *dq_in /* null: rotate dq in place */);
+
+// Device-side address of a page-locked host buffer (the same pointer under
+// unified addressing), or null when `p` is pageable host memory.
+const void *wr_host_device_alias(const void *p);
 
 // ---------------------------------------------------------- device helpers
 
