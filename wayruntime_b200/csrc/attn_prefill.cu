@@ -13,15 +13,19 @@
 //     keys straight from the paged cache with linear bulk copies — the page
 //     layout already is the swizzled operand image the tensor core reads;
 //   * two MMA warps (one issuing thread per head): S = Q.K^T as tcgen05.mma
-//     M128 N64 K16 x8 into TMEM, two tiles ahead of the softmax (S is
-//     double-buffered), and O += P.V as M128 N128 K16 x4 (V is the MN-major
-//     operand); completion is signalled with tcgen05.commit on mbarriers;
-//   * two softmax warpgroups (one per head), one thread per query row:
-//     tcgen05.ld the 64 scores, mask (causal / window), exponentiate against a
-//     running reference max, write P as F16 into shared memory in operand
-//     order.  O stays in TMEM; it is rescaled only when the row max has grown
-//     by more than 2^8 (exact: the final division by l uses the same reference
-//     max), and read once at the end, normalised and stored as F32.
+//     M128 N64 K16 x8 into TMEM (S is double-buffered; the scores of tile
+//     i+2 are issued as soon as the softmax has read tile i out of TMEM), and
+//     O += P.V as M128 N128 K16 x4 (V is the MN-major operand); completion is
+//     signalled with tcgen05.commit on mbarriers;
+//   * two softmax warpgroups (one per head), one thread per query row: the 64
+//     scores of the next tile are fetched from TMEM while the current tile is
+//     exponentiated; mask (causal / window), exponentiate against a running
+//     reference max, write P as F16 into shared memory in operand order.  The
+//     two heads' warps on one scheduler take turns on the special-function
+//     unit.  O stays in TMEM; it is rescaled only when the row max has grown
+//     by more than 2^8 (exact: the final division by l uses the same
+//     reference max), and read once at the end, normalised, transposed
+//     through shared memory and stored as whole F32 rows.
 // Every wait has a time limit; on expiry the kernel records an error, still
 // frees its TMEM and returns.
 #include <cuda.h>
