@@ -172,7 +172,7 @@ int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv
  * The first call on a device resolves the array's address: make it before
  * opening a stream capture.  All calls share the one array per device, so
  * calls that overlap on the GPU race; issue them one after another. */
-#define WR_CUDA_STATIC_MAX_ITEMS  2048
+#define WR_CUDA_STATIC_MAX_ITEMS  4096
 #define WR_CUDA_STATIC_MAX_GROUPS 1024
 int wr_cuda_attn_decode_static(wr_cuda_ctx *ctx, uint32_t n_sess,
                                wr_cuda_kv *const *kv, uint32_t layer,

@@ -63,14 +63,14 @@ def test_static_scratch_decode_refuses_what_does_not_fit():
     import torch
     import wayruntime_b200 as wr
     ctx = wr.Context(0, attn_max_seq=32768)
-    # 16 sessions x 16 kv heads x 16 chunks = 4096 work items > WR_CUDA_STATIC_MAX_ITEMS (2048)
-    kvs = [ctx.kv_create(1, 16, 128, 4096) for _ in range(16)]
-    q = torch.zeros((16, 16, 128), device="cuda")
+    # 16 sessions x 32 kv heads x 16 chunks = 8192 work items > WR_CUDA_STATIC_MAX_ITEMS (4096)
+    kvs = [ctx.kv_create(1, 32, 128, 4096) for _ in range(16)]
+    q = torch.zeros((16, 32, 128), device="cuda")
     out = torch.zeros_like(q)
     with pytest.raises(wr.WrCudaError) as e:
-        ctx.attn_decode_static(kvs, 0, [4096] * 16, q, out, 16)
+        ctx.attn_decode_static(kvs, 0, [4096] * 16, q, out, 32)
     assert e.value.status == -8
-    ctx.attn_decode_static(kvs, 0, [1024] * 16, q, out, 16)       # 16*16*8 = 2048 items: fits
+    ctx.attn_decode_static(kvs, 0, [1024] * 16, q, out, 32)       # 16*32*8 = 4096 items: fits
     ctx.sync()
     kv64 = ctx.kv_create(1, 2, 64, 64)
     q64 = torch.zeros((1, 2, 64), device="cuda")
@@ -78,8 +78,8 @@ def test_static_scratch_decode_refuses_what_does_not_fit():
         ctx.attn_decode_static([kv64], 0, [10], q64, torch.zeros_like(q64), 2)
     assert e.value.status == -3                                   # head_dim 128 only
     with pytest.raises(ValueError):
-        ctx.attn_decode_static(kvs[:1], 0, [10], np.zeros((1, 16, 128), np.float32),
-                               np.zeros((1, 16, 128), np.float32), 16)   # host buffers not accepted
+        ctx.attn_decode_static(kvs[:1], 0, [10], np.zeros((1, 32, 128), np.float32),
+                               np.zeros((1, 32, 128), np.float32), 32)   # host buffers not accepted
     kv64.close()
     for kv in kvs:
         kv.close()

@@ -14,7 +14,7 @@
 // Limits and rules
 //   * head_dim 128 only (the other head dims use a kernel with no scratch);
 //   * at most WR_CUDA_STATIC_MAX_ITEMS work items per call — sessions x kv
-//     heads x chunks, 16 sessions of 4096 keys with 8 kv heads are 2048 — and
+//     heads x chunks, 16 sessions of 32768 keys with 8 kv heads are 4096 — and
 //     WR_CUDA_STATIC_MAX_GROUPS (session, kv head, q subgroup) triples; a
 //     larger call is refused with WR_CUDA_ERR_LIMIT before anything runs;
 //   * q and out must be device memory (the host-buffer convenience path
