@@ -159,10 +159,25 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
         : "memory");
 }
 
+// Tiled 2-D tensor store shared -> global; rows and columns beyond the tensor's
+// extent are dropped by the hardware.  x * 4 bytes is a multiple of 16 for the caller.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src_smem)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(src_smem))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait_read()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 // ---- the kernel ------------------------------------------------------------
 
 __global__ void __launch_bounds__(kThreads, 1)
-attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefill_params p)
+attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap out_map,
+                          const prefill_params p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     smem_layout &sm = *reinterpret_cast<smem_layout *>(smem_raw);
@@ -463,35 +478,34 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             if (ok) {
                 tc_fence_after();
                 const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-                // O leaves TMEM one row per thread; a row is 512 contiguous bytes of the
-                // output.  Each warp transposes its 32 rows through shared memory (this
-                // head's Q and P tiles are no longer needed: every MMA that read them has
-                // completed) so that one store instruction writes one whole row.  The
-                // 16-byte chunks of a row are XOR-swizzled with the row number, which
-                // keeps both the row-wise writes and the chunk-wise reads conflict free.
+                // O leaves TMEM one row per thread.  Each warp lays its 32 rows out in
+                // shared memory as four tiles of 32 rows x 32 columns (128-byte rows, the
+                // eight 16-byte chunks of a row XOR-swizzled with the row number, which is
+                // both conflict free for these row-wise writes and the layout a 128-byte
+                // swizzled tensor map expects) and hands them to the TMA engine, which
+                // writes them out and drops the rows beyond the prompt.  This head's Q and
+                // P tiles serve as the staging area: every MMA that read them has completed.
                 const uint32_t wq = warp & 3u;
                 uint8_t *stage = (wq < 2) ? sm.q[h] + wq * (kQBytes / 2) : sm.p[h][wq - 2];
-                float4 *srow = reinterpret_cast<float4 *>(stage + lane * (kHd * 4));
 #pragma unroll 1
                 for (int c = 0; c < kHd; c += 32) {
                     float o[32];
                     tmem_ld32_nowait(o_addr + c, o);
                     tmem_wait_ld();
+                    float4 *trow = reinterpret_cast<float4 *>(stage + (c / 32) * 4096 + lane * 128);
 #pragma unroll
                     for (int e = 0; e < 8; ++e)
-                        srow[((c >> 2) + e) ^ lane] = make_float4(o[4 * e] * inv, o[4 * e + 1] * inv,
-                                                                 o[4 * e + 2] * inv, o[4 * e + 3] * inv);
+                        trow[e ^ (lane & 7)] = make_float4(o[4 * e] * inv, o[4 * e + 1] * inv,
+                                                            o[4 * e + 2] * inv, o[4 * e + 3] * inv);
                 }
+                fence_proxy_async();                               // generic writes -> TMA reads
                 __syncwarp();
-                const uint32_t row0 = wq * 32u;                     // first row of this warp within the tile
-                float *obase = p.out + ((size_t)(tok0 + row0) * p.n_q + head0 + h) * kHd + lane * 4;
-                const size_t row_stride = (size_t)p.n_q * kHd;
-#pragma unroll 4
-                for (uint32_t r = 0; r < 32; ++r) {
-                    if (row0 + r < rows_here) {
-                        const float4 v = reinterpret_cast<const float4 *>(stage + r * (kHd * 4))[lane ^ r];
-                        *reinterpret_cast<float4 *>(obase + r * row_stride) = v;
-                    }
+                if (lane == 0 && wq * 32u < rows_here) {
+                    const int y = (int)(tok0 + wq * 32u);
+                    const int x = (int)((head0 + h) * kHd);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) tma_store_2d(&out_map, x + 32 * c, y, stage + c * 4096);
+                    tma_store_commit_and_wait_read();              // the staging area is read before the CTA ends
                 }
             }
         }
@@ -602,6 +616,15 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return WR_CUDA_ERR_INTERNAL;
 
+    CUtensorMap out_map;                                          // F32 [n, n_q_heads * hd], boxes of 32 x 32
+    const cuuint64_t odims[2] = {(cuuint64_t)n_q_heads * kHd, (cuuint64_t)n};
+    const cuuint64_t ostrides[1] = {(cuuint64_t)n_q_heads * kHd * 4};
+    const cuuint32_t obox[2] = {32, 32};
+    if (encode(&out_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)dout, odims, ostrides, obox, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return WR_CUDA_ERR_INTERNAL;
+
     prefill_params p;
     p.pages = kv->d_pages + (size_t)layer * kv->n_pages;
     p.out = dout;
@@ -622,7 +645,7 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
         ctx->attr_flags |= 2u;
     }
     const uint32_t grid = p.n_qtiles * p.n_kv * p.n_pairs;
-    attn_prefill_hd128_kernel<<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, p);
+    attn_prefill_hd128_kernel<<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, out_map, p);
     ctx->launches++;
     WR_CUDA_TRY(cudaGetLastError());
     if (host) {
