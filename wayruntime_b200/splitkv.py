@@ -62,8 +62,17 @@ def make_exchange(ctx, max_rows, head_dim, group=None):
     x = wr.Exchange(ctx, world, rank, max_rows, head_dim)
     handles = [None] * world
     dist.all_gather_object(handles, x.handle, group=group)
-    x.connect(handles)
-    dist.barrier(group)
+    try:
+        x.connect(handles)
+        err = None
+    except wr.WrCudaError as exc:
+        err = str(exc)
+    # every rank learns whether every rank connected: nobody is left waiting in a kernel
+    errs = [None] * world
+    dist.all_gather_object(errs, err, group=group)
+    if any(e is not None for e in errs):
+        x.close()
+        raise RuntimeError(f"peer exchange unavailable: {[e for e in errs if e][0]}")
     return x
 
 
