@@ -107,6 +107,34 @@ def test_prefill_llama3_2048(ctx):
     assert np.abs(out[rows] - want).max() <= TOL
 
 
+def test_prefill_config5_8192_then_decode(ctx):
+    """BASELINE config 5 geometry: 40 Q / 8 KV heads (group of five: one lone
+    head per pair split), one session's 8192-token prompt, then a decode step
+    over the 8193 cached keys.  Prefill rows: all heads on a deterministic row
+    subset (first/last rows, 64-boundaries +-1, a stride); the decode row in full."""
+    P = port()
+    n, hq, hkv = 8192, 40, 8
+    q16 = P.f32_to_f16(_gen.normal(810, (n, hq, 128)))
+    k16 = P.f32_to_f16(_gen.normal(811, (n + 1, hkv, 128)))
+    v16 = P.f32_to_f16(_gen.normal(812, (n + 1, hkv, 128)))
+    kv = make_cache(ctx, k16, v16, max_ctx=n + 64)
+    out = np.full((n, hq, 128), np.nan, np.float32)
+    ctx.attn_prefill(kv, 0, 0, n, np.ascontiguousarray(q16), out, hq)
+    rows = np.unique(np.array([0, 1, 63, 64, 65, 127, 128, 4095, 4096, 4097, 8126, 8127, 8128, 8190, 8191] +
+                              list(range(31, n, 1021)))).astype(np.uint32)
+    rc, want = P.causal_prefill_rows(q16, k16[:n], v16[:n], rows, threads=8, max_seq=32768)
+    assert rc == 0
+    assert np.isfinite(out).all()
+    assert np.abs(out[rows] - want).max() <= TOL
+    qd = _gen.normal(813, (1, hq, 128))
+    got = np.full((1, hq, 128), np.nan, np.float32)
+    ctx.attn_decode([kv], 0, [n + 1], qd, got, hq)
+    rc, want_d = P.attention(qd, k16, v16, seq_k=n + 1, max_seq=32768)
+    assert rc == 0
+    assert np.abs(got - want_d).max() <= TOL
+    kv.close()
+
+
 def test_prefill_then_decode_consistency(ctx):
     """The last row of a prefill equals a decode step over the same cache."""
     P = port()

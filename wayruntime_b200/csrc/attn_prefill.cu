@@ -487,16 +487,17 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 // P tiles serve as the staging area: every MMA that read them has completed.
                 const uint32_t wq = warp & 3u;
                 uint8_t *stage = (wq < 2) ? sm.q[h] + wq * (kQBytes / 2) : sm.p[h][wq - 2];
-#pragma unroll 1
+                float o[kHd];                                      // the whole row: one wait for four loads
+#pragma unroll
+                for (int c = 0; c < kHd; c += 32) tmem_ld32_nowait(o_addr + c, o + c);
+                tmem_wait_ld();
+#pragma unroll
                 for (int c = 0; c < kHd; c += 32) {
-                    float o[32];
-                    tmem_ld32_nowait(o_addr + c, o);
-                    tmem_wait_ld();
                     float4 *trow = reinterpret_cast<float4 *>(stage + (c / 32) * 4096 + lane * 128);
 #pragma unroll
                     for (int e = 0; e < 8; ++e)
-                        trow[e ^ (lane & 7)] = make_float4(o[4 * e] * inv, o[4 * e + 1] * inv,
-                                                            o[4 * e + 2] * inv, o[4 * e + 3] * inv);
+                        trow[e ^ (lane & 7)] = make_float4(o[c + 4 * e] * inv, o[c + 4 * e + 1] * inv,
+                                                            o[c + 4 * e + 2] * inv, o[c + 4 * e + 3] * inv);
                 }
                 fence_proxy_async();                               // generic writes -> TMA reads
                 __syncwarp();
