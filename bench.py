@@ -286,33 +286,54 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     finite = bool(torch.isfinite(out).all().item())
-    # the same step with all-gather + merge as ONE kernel over NVLink peer memory
+    # the same step with all-gather + merge as ONE kernel over NVLink peer memory; after
+    # every phase the ranks agree on whether all of them succeeded, so that a failure on
+    # one rank can never leave another waiting in a collective
     fused = None
     if world > 1:
+        def all_ok(flag):
+            t = torch.tensor([1 if flag else 0], device="cuda", dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            return bool(t.item())
+
+        xchg, why = None, None
         try:
-            xchg = splitkv.make_exchange(ctx, rows_n, HD)
+            xchg = splitkv.make_exchange(ctx, rows_n, HD)         # raises on every rank or on none
+        except Exception as exc:
+            why = f"{type(exc).__name__}: {exc}"
+        if xchg is not None:
             out_f = torch.empty_like(q)
 
             def step_fused():
                 splitkv.decode_split_kv(ctx, batch, 0, lens, q, out_f, HQ, triples=triples, exchange=xchg)
 
-            for _ in range(3):
-                step_fused()
-            ctx.sync()
-            dist.barrier()
-            a.record(stream)
-            for _ in range(reps):
-                step_fused()
-            b.record(stream)
-            ctx.sync()
-            t = torch.tensor([a.elapsed_time(b) / reps], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            fused = {"ms_per_step": float(t.item()),
-                     "identical_to_allgather_path": bool(torch.equal(out_f, out))}
+            def run(n, end_event=None):
+                try:
+                    for _ in range(n):
+                        step_fused()
+                    if end_event is not None:
+                        end_event.record(stream)
+                    ctx.sync()                                     # a kernel that gave up waiting surfaces here
+                    return True
+                except Exception as exc:
+                    nonlocal why
+                    why = f"{type(exc).__name__}: {exc}"
+                    return False
+
+            good = all_ok(run(3))
+            if good:
+                a.record(stream)
+                good = all_ok(run(reps, b))
+                torch.cuda.synchronize()
+            if good:
+                t = torch.tensor([a.elapsed_time(b) / reps], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                fused = {"ms_per_step": float(t.item()),
+                         "identical_to_allgather_path": bool(torch.equal(out_f, out))}
             dist.barrier()
             xchg.close()
-        except Exception as exc:
-            fused = {"error": f"{type(exc).__name__}: {exc}"}
+        if fused is None:
+            fused = {"error": why or "a peer rank failed"}
     for kv in kvs:
         kv.close()
     total_bytes = N_SESS * LC_CTX * HKV * HD * 2 * 2
