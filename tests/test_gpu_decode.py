@@ -253,3 +253,41 @@ def test_split_kv_partials_and_combine(ctx):
                 kv.close()
     for kv in kvs_full:
         kv.close()
+
+
+def test_exchange_single_rank_and_refusals(ctx):
+    """The fused exchange + merge kernel with a world of one is the merge of one
+    shard: it must reproduce wr_cuda_attn_combine bit for bit, on both buffer
+    parities.  (Two ranks over NVLink: tests/test_gpu_multi.py.)"""
+    import torch
+    import wayruntime_b200 as wr
+    hq, hkv, hd = 8, 2, 128
+    lens = [300, 64, 1]
+    q, ks, vs, kvs = _ragged_batch(ctx, lens, hq, hkv, hd, 900)
+    rows = len(lens) * hq
+    qd = torch.from_numpy(q).cuda()
+    triples = torch.empty((rows, wr.TRIPLE_PAD + hd), dtype=torch.float32, device="cuda")
+    ctx.attn_decode_partial(kvs, 0, lens, qd, triples, hq)
+    want = torch.empty((rows, hd), dtype=torch.float32, device="cuda")
+    ctx.attn_combine(1, rows, hd, triples, want)
+    x = wr.Exchange(ctx, 1, 0, rows, hd)
+    for _ in range(3):
+        got = torch.full((rows, hd), float("nan"), dtype=torch.float32, device="cuda")
+        x.combine(rows, triples, got)
+        ctx.sync()
+        assert torch.equal(got, want)
+    with pytest.raises(wr.WrCudaError) as e:
+        x.combine(rows + 1, triples, got)                       # more rows than the buffers hold
+    assert e.value.status == -4
+    x.close()
+    with pytest.raises(wr.WrCudaError) as e:
+        wr.Exchange(ctx, 9, 0, rows, hd)                        # world beyond WR_CUDA_XCHG_MAX_WORLD
+    assert e.value.status == -4
+    two = wr.Exchange(ctx, 2, 1, rows, hd)
+    with pytest.raises(wr.WrCudaError) as e:
+        two.combine(rows, triples, got)                         # peers not connected yet
+    assert e.value.status == -7
+    assert len(two.handle) == 64
+    two.close()
+    for kv in kvs:
+        kv.close()
