@@ -8,13 +8,14 @@
 //   * work item = (session, kv head, q-head subgroup of <= 4*NT heads, chunk
 //     of keys).  The chunk length is a function of that session's length
 //     only, so a session's result does not depend on its batch mates.
-//   * every warp is a self-contained engine: it owns a 16 KB K slot, a 16 KB
+//   * six warps of a CTA are self-contained engines: each owns a 16 KB K slot, a 16 KB
 //     V slot and a Q slot in shared memory and refills them itself with TMA
 //     bulk copies (one 16 KB copy per K or V tile: 64 keys of one kv head are
 //     contiguous in the page and already in the swizzled order ldmatrix
 //     wants).  While it computes Q.K on tile t the V of tile t is in flight;
 //     while it computes P.V the K of tile t+1 is in flight — across item
-//     boundaries too.  No CTA-wide barrier exists.
+//     boundaries too.  No CTA-wide barrier exists.  (Lines of this comment that
+//     say "it" mean one such engine.)
 //   * items come from a global queue (the first one is static); an engine
 //     draws the index of a future item one item ahead and loads the page
 //     pointer of a future tile one tile ahead, so neither latency is exposed.
@@ -30,9 +31,9 @@
 //     (deterministic) once the last of them has arrived.  The engines only
 //     count arrivals (a fire-and-forget release increment); the merging — L2
 //     round trips during which a stream would stand still — is done by two
-//     more warps per CTA: these share out (group, head pair) jobs over the
-//     whole grid from a counter, wait for the group's arrival count, and fetch
-//     all the rows of a job in one round trip.  While they wait they keep
+//     more warps per CTA: merge warp w of the grid owns the (group, head
+//     pair) jobs w, w + W, ...; it waits for the job's arrival count and
+//     fetches all its rows in one round trip.  While they wait they keep
 //     running the merge code on nothing, so that its instructions are still
 //     cached when the last groups — the end of the kernel's critical path —
 //     arrive.
