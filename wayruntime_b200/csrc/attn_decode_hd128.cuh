@@ -12,10 +12,9 @@
 //     V slot and a Q slot in shared memory and refills them itself with TMA
 //     bulk copies (one 16 KB copy per K or V tile: 64 keys of one kv head are
 //     contiguous in the page and already in the swizzled order ldmatrix
-//     wants).  While it computes Q.K on tile t the V of tile t is in flight;
-//     while it computes P.V the K of tile t+1 is in flight — across item
-//     boundaries too.  No CTA-wide barrier exists.  (Lines of this comment that
-//     say "it" mean one such engine.)
+//     wants).  While an engine computes Q.K on tile t the V of tile t is in
+//     flight; while it computes P.V the K of tile t+1 is in flight — across
+//     item boundaries too.  No CTA-wide barrier exists.
 //   * items come from a global queue (the first one is static); an engine
 //     draws the index of a future item one item ahead and loads the page
 //     pointer of a future tile one tile ahead, so neither latency is exposed.
