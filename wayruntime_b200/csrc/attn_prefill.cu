@@ -199,7 +199,10 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
     const uint32_t t_first = key_first / kBN;
     const uint32_t n_kt = (key_end + kBN - 1) / kBN - t_first;     // >= 1
 
-    if (tid == 0) {
+    // The TMA warp sets the barriers up and starts the first copies (Q, and the first
+    // ring's worth of K and V tiles) at once: they fly while TMEM is being allocated
+    // and the other warps arrive at the barrier below.
+    if (warp == 8 && lane == 0) {
         mbar_init(&sm.bar_q, 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sm.full_k[i], 1);
@@ -225,13 +228,18 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                      ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sm.tmem_base;
-
+    // lane 0 of the TMA warp streams the K tiles, lane 1 the V tiles: separate rings,
+    // because a K tile is free again long before its V tile is.
+    auto issue_kv_tile = [&](uint32_t i) {
+        uint8_t (*ring)[kKVBlock] = lane == 0 ? sm.k : sm.v;
+        uint64_t *full = lane == 0 ? sm.full_k : sm.full_v;
+        const uint32_t st = i % kStages;
+        const char *src = (const char *)p.pages[t_first + i] + wr_block_off(kvh, lane, kHd);
+        mbar_expect_tx(&full[st], kKVBlock);
+        bulk_g2s(ring[st], src, kKVBlock, &full[st]);
+    };
     if (warp == 8) {
-        // ------------------------------------------------------------ TMA warp
+        __syncwarp();                                   // lane 1 uses barriers that lane 0 has just set up
         if (lane == 0) {
             mbar_expect_tx(&sm.bar_q, n_heads * kQBytes);
             for (uint32_t h = 0; h < n_heads; ++h) {
@@ -240,21 +248,25 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                             &sm.bar_q);
             }
         }
+        if (lane < 2)
+            for (uint32_t i = 0; i < min((uint32_t)kStages, n_kt); ++i) issue_kv_tile(i);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------ TMA warp
         if (lane < 2) {
-            // lane 0 streams the K tiles, lane 1 the V tiles: separate rings,
-            // because a K tile is free again long before its V tile is.
-            uint8_t (*ring)[kKVBlock] = lane == 0 ? sm.k : sm.v;
-            uint64_t *full = lane == 0 ? sm.full_k : sm.full_v;
             uint64_t *empty = lane == 0 ? sm.empty_k : sm.empty_v;
-            for (uint32_t i = 0; i < n_kt; ++i) {
+            for (uint32_t i = kStages; i < n_kt; ++i) {
                 const uint32_t st = i % kStages;
-                if (i >= kStages && !mbar_wait(&empty[st], ((i / kStages) - 1) & 1)) {
+                if (!mbar_wait(&empty[st], ((i / kStages) - 1) & 1)) {
                     atomicExch(p.err, 11);
                     break;
                 }
-                const char *src = (const char *)p.pages[t_first + i] + wr_block_off(kvh, lane, kHd);
-                mbar_expect_tx(&full[st], kKVBlock);
-                bulk_g2s(ring[st], src, kKVBlock, &full[st]);
+                issue_kv_tile(i);
             }
         }
     } else if (warp >= 9) {
