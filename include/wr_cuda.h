@@ -73,7 +73,8 @@ void wr_cuda_ctx_destroy(wr_cuda_ctx *ctx);
 
 /* Wait for everything enqueued on the context's stream.  Also reports (and
  * clears) a device-side error flag: a bounded wait that gave up inside a
- * kernel surfaces here as WR_CUDA_ERR_INTERNAL. */
+ * kernel surfaces here — and at the end of every call that takes
+ * WR_CUDA_MEM_HOST buffers — as WR_CUDA_ERR_INTERNAL. */
 int  wr_cuda_ctx_sync(wr_cuda_ctx *ctx);
 
 /* The context's cudaStream_t, for callers that time or order against it. */
@@ -83,6 +84,26 @@ void *wr_cuda_ctx_stream(wr_cuda_ctx *ctx);
  * reference's WR_ATTN_MAX_SEQ is a compile-time constant (internal.h:186),
  * here it is a setting so long-context shards need no rebuild. */
 int  wr_cuda_ctx_set_attn_max_seq(wr_cuda_ctx *ctx, uint32_t max_seq);
+
+/* Every device-side wait in this library (an mbarrier phase, an arrival
+ * counter, a peer's flag) gives up after this many cycles of SM clock: the
+ * kernel records an error word, unwinds and returns, and the next call that
+ * synchronises (wr_cuda_ctx_sync, or any call with WR_CUDA_MEM_HOST buffers)
+ * returns WR_CUDA_ERR_INTERNAL once and clears the word; the context stays
+ * usable.  The reference has no counterpart (its ops cannot stall); the
+ * contract kept is its "a failed step consumes nothing" (session.c:160-168,
+ * :589-592).  Default WR_CUDA_WAIT_LIMIT_DEFAULT, about two seconds. */
+#define WR_CUDA_WAIT_LIMIT_DEFAULT 4000000000LL
+int  wr_cuda_ctx_set_wait_limit(wr_cuda_ctx *ctx, int64_t cycles);
+
+/* Page-locked host memory for a caller's row buffers (Q / K / V / attention
+ * rows): with such buffers the WR_CUDA_MEM_HOST calls need no staging copy —
+ * the decode kernels read and write them in place.  The reference's session
+ * scratch comes from one arena sized at create (session.c:699-708); a host
+ * layer allocates these once per session in the same place and frees them at
+ * destroy.  64-byte aligned.  WR_CUDA_ERR_NOMEM when the host cannot pin. */
+int  wr_cuda_host_alloc(wr_cuda_ctx *ctx, uint64_t bytes, void **out);
+void wr_cuda_host_free(wr_cuda_ctx *ctx, void *p);
 
 /* Number of kernels this library has launched on the context so far. */
 uint64_t wr_cuda_ctx_launch_count(wr_cuda_ctx *ctx);
@@ -229,6 +250,14 @@ int  wr_cuda_xchg_create(wr_cuda_ctx *ctx, uint32_t world, uint32_t rank,
                          uint32_t max_rows, uint32_t head_dim, wr_cuda_xchg **out);
 int  wr_cuda_xchg_handle(wr_cuda_xchg *x, void *handle_out);
 int  wr_cuda_xchg_connect(wr_cuda_xchg *x, const void *handles /* world x 64 bytes */);
+/* The same connection for exchange objects that live in ONE process (one
+ * thread per GPU, or several contexts of a test): all[r] is rank r's object;
+ * devices other than the caller's need peer access enabled by the host. */
+int  wr_cuda_xchg_connect_local(wr_cuda_xchg *x, wr_cuda_xchg *const *all);
+/* Destroy is collective: a peer's kernel may still be storing into this
+ * rank's buffer, so every rank first synchronises its context
+ * (wr_cuda_ctx_sync, also after a step that timed out) and the ranks agree
+ * (a barrier of the host's transport) before any of them destroys. */
 void wr_cuda_xchg_destroy(wr_cuda_xchg *x);
 
 /* All-gather + merge in one kernel: stores this rank's triples (device, F32

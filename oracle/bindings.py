@@ -33,15 +33,20 @@ def _dtype_code(a):
     raise TypeError(f"unsupported dtype {a.dtype}")
 
 
-def build(ref_root: str = "/root/reference") -> None:
+def reference_root() -> str:
+    """The reference checkout: $WR_REFERENCE_ROOT, else a `reference` folder
+    beside this repository."""
+    return os.environ.get("WR_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
+def build(ref_root: str | None = None) -> None:
     """Compile liboracle.so and, when the reference checkout exists, _ref/*.so."""
-    subprocess.run(["make", "-C", _HERE, f"REF={ref_root}"], check=True,
-                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
-    cuda_lib = os.path.join(_HERE, "..", "wayruntime_b200", "lib", "libwr_cuda.so")
-    if os.path.exists(os.path.join(ref_root, "src", "core", "kernels.c")) and os.path.exists(cuda_lib):
-        # the reference with the B200 session objects linked in (the drop-in parity tests' subject)
-        subprocess.run(["make", "-C", _HERE, f"REF={ref_root}", "dropin"], check=True,
-                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    ref_root = ref_root or reference_root()
+    res = subprocess.run(["make", "-C", _HERE, f"REF={ref_root}"],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"oracle build failed:\n{res.stdout}")
 
 
 class Checker:

@@ -64,3 +64,26 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".c", ".cpp")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src, f"{f} mentions the oracle"
+
+
+def test_dropin_engine_create_refuses_a_host_without_b200():
+    """The drop-in library's wr_engine_create is the gate (reference contract:
+    include/wayruntime/wayruntime.h:181-185, probe at src/core/engine.c:130):
+    with no compute-capability-10.x device it returns WR_ERR_UNSUPPORTED, writes
+    one line to the caller's log sink, and creates nothing."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    path = os.path.join(ROOT, "wayruntime_b200", "lib", "libwayruntime_b200.so")
+    if not os.path.exists(path):
+        pytest.skip("drop-in library not built on this machine (needs the reference checkout)")
+    L = ctypes.CDLL(path)
+    L.wr_engine_create.restype = ctypes.c_int
+    engine = ctypes.c_void_p()
+    cfg = (ctypes.c_uint8 * 512)()                     # zeroed wr_engine_config: default sink (stderr)
+    assert L.wr_engine_create(cfg, ctypes.byref(engine)) == -3
+    assert not engine.value
+    assert L.wr_engine_create(None, ctypes.byref(engine)) == -3
+    assert L.wr_engine_create(cfg, None) == -4
+    # the session objects refuse as well when driven without an engine
+    assert L.wri_self_test_llm_step() == -2

@@ -1,9 +1,10 @@
 """GPU: the B200 session objects as a drop-in inside the reference library.
 
-`oracle/_ref/libwayruntime_b200.so` is the reference built WITHOUT its
+`wayruntime_b200/lib/libwayruntime_b200.so` is the reference built WITHOUT its
 session.c / batch.c, with wayruntime_b200/host/wr_b200_session.c linked in
-their place (oracle/Makefile, target `dropin`); `libwayruntime_ref.so` is the
-unmodified reference.  Both are driven through the reference's public API
+their place and the engine gate of wr_b200_engine.c in front of its
+wr_engine_create (wayruntime_b200/host/Makefile); `oracle/_ref/libwayruntime_ref*.so`
+is the unmodified reference.  Both are driven through the reference's public API
 (include/wayruntime/wayruntime.h) on the same seeded GGUF and token ids:
   * teacher-forced greedy decoding: identical argmax at every step, logits
     within tolerance (BASELINE config 1: Qwen3-0.6B shape, 64-token prompt),
@@ -28,7 +29,7 @@ import _mkgguf
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.path.join(ROOT, "oracle", "_ref", "libwayruntime_ref_tap.so")
-B200 = os.path.join(ROOT, "oracle", "_ref", "libwayruntime_b200.so")
+B200 = os.path.join(ROOT, "wayruntime_b200", "lib", "libwayruntime_b200.so")
 
 
 REF_TAP = C.CFUNCTYPE(None, C.c_void_p, C.c_uint32, C.POINTER(C.c_float), C.c_uint32)
@@ -75,7 +76,7 @@ class Lib:
 @pytest.fixture(scope="module")
 def libs():
     if not (os.path.exists(REF) and os.path.exists(B200)):
-        pytest.skip("oracle/_ref drop-in libraries not built on this machine")
+        pytest.skip("the drop-in library and the compiled reference were not built on this machine")
     return Lib(REF), Lib(B200)
 
 

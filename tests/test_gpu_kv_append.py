@@ -209,3 +209,60 @@ def test_decode_step_host_buffer_paths_agree(ctx, n_rot):
             assert np.array_equal(kv.read_rows(0, 1, ln - 1, 1), wv)
         for kv in kvs:
             kv.close()
+
+
+def test_decode_step_page_locked_views_at_odd_offsets_are_staged(ctx):
+    """Rows move as 16-byte vectors, so the kernels may touch a page-locked host
+    buffer directly only when it is 16-byte aligned.  A page-locked view that
+    starts 8 bytes into its allocation must give the same bits through the
+    staged copy path (never a launch on the misaligned address), and a device
+    row buffer at such an offset is refused."""
+    import torch
+    import wayruntime_b200 as wr
+    P = port()
+    hq, hkv, hd, theta = 32, 8, 128, 5e5
+    lens = [200, 65]
+    n = len(lens)
+    q = _gen.normal(141, (n, hq, hd))
+    k_new = _gen.normal(142, (n, hkv, hd))
+    v_new = _gen.normal(143, (n, hkv, hd))
+    hist_k = [P.f32_to_f16(_gen.normal(150 + i, (ln - 1, hkv, hd))) for i, ln in enumerate(lens)]
+    hist_v = [P.f32_to_f16(_gen.normal(160 + i, (ln - 1, hkv, hd))) for i, ln in enumerate(lens)]
+
+    def fresh():
+        kvs = [ctx.kv_create(1, hkv, hd, 256) for _ in lens]
+        for kv, hk, hv in zip(kvs, hist_k, hist_v):
+            kv.write_rows(0, 0, 0, hk)
+            kv.write_rows(0, 1, 0, hv)
+        return kvs
+
+    def odd_view(a):
+        """page-locked float32 tensor shaped like `a`, starting 8 bytes into its allocation"""
+        base = torch.empty(a.size + 2, dtype=torch.float32).pin_memory()
+        view = base[2:].view(a.shape)
+        view.copy_(torch.from_numpy(a))
+        assert view.data_ptr() % 16 == 8
+        return view
+
+    pos = [ln - 1 for ln in lens]
+    results = []
+    for odd in (False, True):
+        kvs = fresh()
+        mk = odd_view if odd else (lambda a: torch.from_numpy(a.copy()).pin_memory())
+        hq_, hk_, hv_ = mk(q), mk(k_new), mk(v_new)
+        hout = mk(np.full((n, hq, hd), np.nan, np.float32))
+        ctx.decode_step(kvs, 0, pos, hq_, hk_, hv_, hout, hq, theta=theta)
+        results.append((hout.numpy().copy(), [kv.read_rows(0, 0, ln - 1, 1) for kv, ln in zip(kvs, lens)]))
+        for kv in kvs:
+            kv.close()
+    assert np.array_equal(bits(results[0][0]), bits(results[1][0]))
+    for a, b in zip(results[0][1], results[1][1]):
+        assert np.array_equal(a, b)
+    # device rows at an 8-byte offset: refused before any launch
+    kv = ctx.kv_create(1, hkv, hd, 64)
+    dev = torch.zeros(4 * hkv * hd + 4, dtype=torch.int16, device="cuda")[4:].view(4, hkv, hd)
+    assert dev.data_ptr() % 16 == 8
+    with pytest.raises(wr.WrCudaError) as e:
+        kv.write_rows(0, 0, 0, dev)
+    assert e.value.status == -4
+    kv.close()

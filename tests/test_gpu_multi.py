@@ -61,8 +61,7 @@ def _worker(rank, world, port_no, result_q):
     ctx.sync()
     torch.cuda.synchronize()
     same = bool(np.array_equal(out2.cpu().numpy().view(np.uint32), got.view(np.uint32)))
-    dist.barrier()
-    xchg.close()
+    splitkv.close_exchange(xchg, ctx)
     rc, want = P.decode_batch(q, ks, vs, threads=4, max_seq=32768)
     result_q.put((rank, rc, float(np.abs(got - want).max()), same))
     for kv in kvs:

@@ -80,7 +80,38 @@ def test_static_scratch_decode_refuses_what_does_not_fit():
     with pytest.raises(ValueError):
         ctx.attn_decode_static(kvs[:1], 0, [10], np.zeros((1, 32, 128), np.float32),
                                np.zeros((1, 32, 128), np.float32), 32)   # host buffers not accepted
+    # straight through the C-ABI: a pageable host pointer is refused by the library
+    # itself (pointer-attribute query, no launch), not only by the Python mirror
+    import ctypes as C
+    host_q = np.zeros((1, 32, 128), np.float32)
+    host_o = np.zeros((1, 32, 128), np.float32)
+    handles = (C.c_void_p * 1)(kvs[0]._h)
+    lens = (C.c_uint32 * 1)(10)
+    rc = ctx._lib.wr_cuda_attn_decode_static(ctx._h, 1, handles, 0, lens, host_q.ctypes.data,
+                                             host_o.ctypes.data, 32, 0.0, 0)
+    assert rc == -4
     kv64.close()
     for kv in kvs:
         kv.close()
+    ctx.close()
+
+
+def test_static_scratch_is_resident_after_context_creation():
+    """The scratch array is instantiated when the context is created, so the
+    first call of the entry point takes no device memory: a caller may size its
+    KV pool from the free memory it sees after wr_cuda_ctx_create."""
+    import torch
+    import wayruntime_b200 as wr
+    ctx = wr.Context(0)
+    kv = ctx.kv_create(1, 8, 128, 256)
+    q = torch.zeros((1, 32, 128), device="cuda")
+    out = torch.zeros_like(q)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    ctx.attn_decode_static([kv], 0, [200], q, out, 32)
+    ctx.sync()
+    free_after, _ = torch.cuda.mem_get_info()
+    # (the 17 MB array would show; a first launch may still grow the driver's small per-kernel state)
+    assert free_before - free_after < 8 * 1024 * 1024
+    kv.close()
     ctx.close()

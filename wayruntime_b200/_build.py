@@ -41,3 +41,21 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         print(res.stdout)
     return LIB_PATH
+
+
+DROPIN_PATH = os.path.join(LIB_DIR, "libwayruntime_b200.so")
+
+
+def build_dropin(ref_root: str) -> str | None:
+    """Link lib/libwayruntime_b200.so: the reference library (compiled from the
+    checkout at `ref_root`, unmodified) with this package's session objects and
+    engine gate in place of its session.c / batch.c / engine entry points.
+    Returns None when there is no checkout (the GPU box uses the prebuilt file)."""
+    if not os.path.exists(os.path.join(ref_root, "src", "core", "kernels.c")):
+        return None
+    build()
+    res = subprocess.run(["make", "-C", os.path.join(PKG, "host"), f"REF={ref_root}"],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"drop-in link failed:\n{res.stdout}")
+    return DROPIN_PATH

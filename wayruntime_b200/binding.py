@@ -29,12 +29,14 @@ _STATUS = {
 
 EXPORTS = [
     "wr_cuda_device_check", "wr_cuda_ctx_create", "wr_cuda_ctx_destroy", "wr_cuda_ctx_sync",
-    "wr_cuda_ctx_stream", "wr_cuda_ctx_set_attn_max_seq", "wr_cuda_ctx_launch_count",
+    "wr_cuda_ctx_stream", "wr_cuda_ctx_set_attn_max_seq", "wr_cuda_ctx_set_wait_limit",
+    "wr_cuda_ctx_launch_count", "wr_cuda_host_alloc", "wr_cuda_host_free",
     "wr_cuda_kv_create", "wr_cuda_kv_destroy", "wr_cuda_kv_max_ctx", "wr_cuda_kv_write_rows",
     "wr_cuda_kv_read_rows", "wr_cuda_kv_append", "wr_cuda_attn_decode", "wr_cuda_attn_prefill",
     "wr_cuda_attn_decode_partial", "wr_cuda_attn_combine", "wr_cuda_decode_step",
     "wr_cuda_attn_decode_static",
-    "wr_cuda_xchg_create", "wr_cuda_xchg_handle", "wr_cuda_xchg_connect", "wr_cuda_xchg_destroy",
+    "wr_cuda_xchg_create", "wr_cuda_xchg_handle", "wr_cuda_xchg_connect", "wr_cuda_xchg_connect_local",
+    "wr_cuda_xchg_destroy",
     "wr_cuda_attn_exchange_combine",
 ]
 
@@ -70,7 +72,10 @@ def load_library():
         "wr_cuda_ctx_sync": (i32, [vp]),
         "wr_cuda_ctx_stream": (vp, [vp]),
         "wr_cuda_ctx_set_attn_max_seq": (i32, [vp, u32]),
+        "wr_cuda_ctx_set_wait_limit": (i32, [vp, C.c_int64]),
         "wr_cuda_ctx_launch_count": (C.c_uint64, [vp]),
+        "wr_cuda_host_alloc": (i32, [vp, C.c_uint64, C.POINTER(vp)]),
+        "wr_cuda_host_free": (None, [vp, vp]),
         "wr_cuda_kv_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
         "wr_cuda_kv_destroy": (None, [vp]),
         "wr_cuda_kv_max_ctx": (u32, [vp]),
@@ -91,6 +96,7 @@ def load_library():
         "wr_cuda_xchg_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
         "wr_cuda_xchg_handle": (i32, [vp, vp]),
         "wr_cuda_xchg_connect": (i32, [vp, vp]),
+        "wr_cuda_xchg_connect_local": (i32, [vp, C.POINTER(vp)]),
         "wr_cuda_xchg_destroy": (None, [vp]),
         "wr_cuda_attn_exchange_combine": (i32, [vp, vp, u32, vp, vp]),
     }
@@ -170,6 +176,10 @@ class Context:
 
     def set_attn_max_seq(self, n: int):
         _check(self._lib.wr_cuda_ctx_set_attn_max_seq(self._h, n), "wr_cuda_ctx_set_attn_max_seq")
+
+    def set_wait_limit(self, cycles: int):
+        """SM clock cycles after which a device-side wait gives up (default about 2 s)."""
+        _check(self._lib.wr_cuda_ctx_set_wait_limit(self._h, int(cycles)), "wr_cuda_ctx_set_wait_limit")
 
     def kv_create(self, n_layers, n_kv_heads, head_dim, max_ctx) -> "KVCache":
         return KVCache(self, n_layers, n_kv_heads, head_dim, max_ctx)
@@ -291,6 +301,13 @@ class Exchange:
         if len(blob) != self.world * XCHG_HANDLE_BYTES:
             raise ValueError("one 64-byte handle per rank, in rank order")
         _check(self._lib.wr_cuda_xchg_connect(self._h, C.c_char_p(blob)), "wr_cuda_xchg_connect")
+
+    @staticmethod
+    def connect_local(objs) -> None:
+        """Connect exchange objects that live in this process (rank order)."""
+        arr = (C.c_void_p * len(objs))(*[o._h for o in objs])
+        for o in objs:
+            _check(o._lib.wr_cuda_xchg_connect_local(o._h, arr), "wr_cuda_xchg_connect_local")
 
     def combine(self, n_rows: int, triples, out) -> None:
         tp, tm, _t = _buf(triples)

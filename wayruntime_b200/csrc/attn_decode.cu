@@ -159,6 +159,59 @@ int wr_decode_validate(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv,
     return WR_CUDA_OK;
 }
 
+// Work decomposition of one head_dim-128 decode launch: sessions sorted by
+// descending length (their larger chunks are drawn from the work queue first,
+// which evens out the finish), per-session chunking (a function of that
+// session alone), item numbering.  Shared by every entry point that launches
+// the kernel, so that they all give the same bits.  Fills everything of `p`
+// that depends on the batch; the caller adds buffers, scale and flags.
+void wr_decode_plan(uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer, const uint32_t *seq_lens,
+                    uint32_t n_q, uint32_t window, wr_decode::params &p, uint32_t &nt, uint32_t &items)
+{
+    using namespace wr_decode;
+    const uint32_t n_kv = kv[0]->n_kv, hd = kv[0]->hd;
+    const uint32_t group = n_q / n_kv;
+    nt = group <= 4 ? 1u : 2u;
+    const uint32_t qsubs = (group + 4 * nt - 1) / (4 * nt);
+    uint32_t order[WR_CUDA_BATCH_MAX];
+    for (uint32_t s = 0; s < n_sess; ++s) order[s] = s;
+    std::stable_sort(order, order + n_sess,
+                     [&](uint32_t a, uint32_t b) { return seq_lens[a] > seq_lens[b]; });
+    items = 0;
+    for (uint32_t i = 0; i < n_sess; ++i) {
+        const uint32_t s = order[i];
+        const uint32_t len = seq_lens[s];
+        const uint32_t key_lo = (window > 0 && len > window) ? len - window : 0;  // kernels.c:1463
+        const uint32_t n_tiles = (len + kTile - 1) / kTile;
+        const uint32_t tile_lo = key_lo / kTile;
+        const uint32_t span = n_tiles - tile_lo;
+        const uint32_t ct = chunk_tiles_for(span);             // chunk length: this session alone
+        const uint32_t nc = (span + ct - 1) / ct;              // 0 for an empty shard
+        p.b.pages[i] = kv[s]->d_pages + (size_t)layer * kv[s]->n_pages;
+        p.b.seq_len[i] = len;
+        p.page_base[i] = kv[s]->contig[layer]
+                             ? (const char *)kv[s]->pages[(size_t)layer * kv[s]->n_pages]
+                             : nullptr;
+        p.row[i] = s;
+        p.key_lo[i] = key_lo;
+        p.tile_lo[i] = tile_lo;
+        p.n_tiles[i] = n_tiles;
+        p.chunk_tiles[i] = ct;
+        p.n_chunks[i] = nc;
+        p.item_base[i] = items;
+        items += n_kv * qsubs * nc;
+    }
+    for (uint32_t s = n_sess; s <= WR_CUDA_BATCH_MAX; ++s) p.item_base[s] = items;
+    for (uint32_t i = n_sess; i < WR_CUDA_BATCH_MAX; ++i) p.page_base[i] = nullptr;
+    p.page_bytes = wr_page_bytes(n_kv, hd);
+    p.n_groups = n_sess * n_kv * qsubs;
+    p.n_sess = n_sess;
+    p.n_q = n_q;
+    p.n_kv = n_kv;
+    p.group = group;
+    p.qsubs = qsubs;
+}
+
 // Enqueue the decode kernel on device-resident q / out.  Caller holds
 // ctx->lock and has validated the arguments.
 int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
@@ -172,43 +225,8 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
     if (hd == wr_decode::kHd) {
         using namespace wr_decode;
         params p;
-        const uint32_t nt = group <= 4 ? 1u : 2u;
-        const uint32_t qsubs = (group + 4 * nt - 1) / (4 * nt);
-        // Longest sessions first: their (largest) chunks are drawn from the
-        // work queue before the small ones, which evens out the finish.
-        uint32_t order[WR_CUDA_BATCH_MAX];
-        for (uint32_t s = 0; s < n_sess; ++s) order[s] = s;
-        std::stable_sort(order, order + n_sess,
-                         [&](uint32_t a, uint32_t b) { return seq_lens[a] > seq_lens[b]; });
-        uint32_t items = 0;
-        for (uint32_t i = 0; i < n_sess; ++i) {
-            const uint32_t s = order[i];
-            const uint32_t len = seq_lens[s];
-            const uint32_t key_lo = (window > 0 && len > window) ? len - window : 0;  // kernels.c:1463
-            const uint32_t n_tiles = (len + kTile - 1) / kTile;
-            const uint32_t tile_lo = key_lo / kTile;
-            const uint32_t span = n_tiles - tile_lo;
-            // Chunk length is a function of this session alone.
-            const uint32_t ct = chunk_tiles_for(span);
-            const uint32_t nc = (span + ct - 1) / ct;          // 0 for an empty shard
-            p.b.pages[i] = kv[s]->d_pages + (size_t)layer * kv[s]->n_pages;
-            p.b.seq_len[i] = len;
-            p.page_base[i] = kv[s]->contig[layer]
-                                 ? (const char *)kv[s]->pages[(size_t)layer * kv[s]->n_pages]
-                                 : nullptr;
-            p.row[i] = s;
-            p.key_lo[i] = key_lo;
-            p.tile_lo[i] = tile_lo;
-            p.n_tiles[i] = n_tiles;
-            p.chunk_tiles[i] = ct;
-            p.n_chunks[i] = nc;
-            p.item_base[i] = items;
-            items += n_kv * qsubs * nc;
-        }
-        for (uint32_t s = n_sess; s <= WR_CUDA_BATCH_MAX; ++s) p.item_base[s] = items;
-        for (uint32_t i = n_sess; i < WR_CUDA_BATCH_MAX; ++i) p.page_base[i] = nullptr;
-        p.page_bytes = wr_page_bytes(n_kv, hd);
-        p.n_groups = n_sess * n_kv * qsubs;
+        uint32_t nt = 1, items = 0;
+        wr_decode_plan(n_sess, kv, layer, seq_lens, n_q, window, p, nt, items);
         int rc = wr_ctx_reserve_ws(ctx, (size_t)std::max(items, 1u) * 8 * kTripleStride * sizeof(float),
                                    (size_t)p.n_groups * kTicketsPerGroup + kTicketExtra);
         if (rc != WR_CUDA_OK) return rc;
@@ -217,11 +235,7 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
         p.ws = ctx->ws;
         p.tickets = ctx->tickets;
         p.err = ctx->dev_err;
-        p.n_sess = n_sess;
-        p.n_q = n_q;
-        p.n_kv = n_kv;
-        p.group = group;
-        p.qsubs = qsubs;
+        p.wait_limit = ctx->wait_limit;
         p.emit_triples = (uint32_t)emit_triples;
         p.scale = scale;
         if (!(ctx->attr_flags & 1u)) {
@@ -290,7 +304,7 @@ static int decode_common(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *k
     if (rc != WR_CUDA_OK) return rc;
     if (mem == WR_CUDA_MEM_HOST) {
         WR_CUDA_TRY(cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+        return wr_ctx_sync_checked(ctx);
     }
     return WR_CUDA_OK;
 }
@@ -330,7 +344,9 @@ extern "C" int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv
         // rows stay as they are.  Pageable buffers take the staged path.
         const void *dev_k = wr_host_device_alias(k_rows), *dev_v = wr_host_device_alias(v_rows);
         const void *dev_q = wr_host_device_alias(q), *dev_o = wr_host_device_alias(out);
-        const bool zero_copy = dev_k && dev_v && dev_q && dev_o && (flags & WR_CUDA_APPEND_ROPE);
+        // (rows move as 16-byte vectors: a page-locked buffer at an odd offset is staged instead)
+        const bool aligned = ((((uintptr_t)dev_k | (uintptr_t)dev_v | (uintptr_t)dev_q | (uintptr_t)dev_o) & 15u) == 0);
+        const bool zero_copy = dev_k && dev_v && dev_q && dev_o && aligned && (flags & WR_CUDA_APPEND_ROPE);
         rc = wr_ctx_reserve_stage(ctx, 2 * kv_bytes + 2 * q_bytes, 0);
         if (rc != WR_CUDA_OK) return rc;
         char *d = (char *)ctx->stage_dev;
@@ -359,7 +375,7 @@ extern "C" int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv
     if (mem == WR_CUDA_MEM_HOST) {
         if (staged_out)
             WR_CUDA_TRY(cudaMemcpyAsync(out, dout, q_bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+        return wr_ctx_sync_checked(ctx);
     }
     return WR_CUDA_OK;
 }
@@ -410,7 +426,7 @@ extern "C" int wr_cuda_attn_combine(wr_cuda_ctx *ctx, uint32_t n_shards, uint32_
     WR_CUDA_TRY(cudaGetLastError());
     if (mem == WR_CUDA_MEM_HOST) {
         WR_CUDA_TRY(cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+        return wr_ctx_sync_checked(ctx);
     }
     return WR_CUDA_OK;
 }

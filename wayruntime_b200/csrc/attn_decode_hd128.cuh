@@ -87,7 +87,16 @@ struct params {
     int *err;
     uint32_t n_sess, n_q, n_kv, group, qsubs, emit_triples, n_groups;
     float scale;
+    long long wait_limit;   // SM clock cycles a device-side wait may last
 };
+
+}  // namespace wr_decode
+
+// Host side (attn_decode.cu): the batch-dependent part of `params`.
+void wr_decode_plan(uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer, const uint32_t *seq_lens,
+                    uint32_t n_q, uint32_t window, wr_decode::params &p, uint32_t &nt, uint32_t &items);
+
+namespace wr_decode {
 
 struct warp_smem {
     alignas(128) uint8_t k[kBlockBytes];
@@ -268,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
                 if (lane == 0) {
                     ready = ((uint32_t)ld_relaxed(ticket) == nc);
                     if (ready) fence_acq_rel_gpu();
-                    else if (clock64() - t_start > 8000000000LL) {
+                    else if (clock64() - t_start > 2 * p.wait_limit) {
                         atomicExch(p.err, 4);
                         ready = -1;
                     }
@@ -407,8 +416,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         const uint32_t heads_here = min(kHeadsMax, p.group - d0.qs * kHeadsMax);
 
         // ---------------- K tile (and, on the item's first tile, its Q rows)
-        if (!mbar_wait(bar_k, uses & 1)) {
+        if (!mbar_wait(bar_k, uses & 1, p.wait_limit)) {
             if (lane == 0) atomicExch(p.err, 2);
+            (void)mbar_wait(bar_v, uses & 1, p.wait_limit);    // this tile's V copy may still be landing
             return;
         }
         if (d0.flags & 2u) {
@@ -516,8 +526,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         }
 
         // ---------------- V tile
-        if (!mbar_wait(bar_v, uses & 1)) {
+        if (!mbar_wait(bar_v, uses & 1, p.wait_limit)) {
             if (lane == 0) atomicExch(p.err, 3);
+            if (d1.flags & 1u) (void)mbar_wait(bar_k, (uses + 1) & 1, p.wait_limit);   // the next K copy is in flight
             return;
         }
         ++uses;

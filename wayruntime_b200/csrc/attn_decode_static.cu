@@ -9,7 +9,11 @@
 // synchronises the whole device), or a host that has frozen its memory map
 // after start-up.  For them this file offers the same kernel over a scratch
 // area that is part of the library image itself: a file-scope __device__
-// array, present on every device that loads the library from load to exit.
+// array.  The CUDA runtime instantiates a module's device arrays when the
+// module is first used on a device, so wr_cuda_ctx_create touches this one
+// (wr_static_setup): from context creation to process exit the array occupies
+// its 17 MB on that device, and its cost lands at start-up, before the caller
+// sizes a KV pool, not at the first step.
 //
 // Limits and rules
 //   * head_dim 128 only (the other head dims use a kernel with no scratch);
@@ -18,10 +22,13 @@
 //     WR_CUDA_STATIC_MAX_GROUPS (session, kv head, q subgroup) triples; a
 //     larger call is refused with WR_CUDA_ERR_LIMIT before anything runs;
 //   * q and out must be device memory (the host-buffer convenience path
-//     needs staging, which is an allocation);
-//   * the first call on a device looks the array's device address up
-//     (cudaGetSymbolAddress); make that first call before opening any stream
-//     capture;
+//     needs staging, which is an allocation); anything else is refused with
+//     WR_CUDA_ERR_INVAL after a pointer-attribute query, which allocates
+//     nothing;
+//   * the array's device address is looked up (cudaGetSymbolAddress) once per
+//     device, when the first context on that device is created; a call on a
+//     device that somehow skipped that does it itself, so make the first call
+//     on a device before opening any stream capture;
 //   * every call uses the same array: the tickets and the queue are cleared
 //     on the stream before each launch, the partial results are always
 //     written before they are read; two calls that overlap on the GPU (two
@@ -79,7 +86,24 @@ int static_setup(int device, static_ptrs **out)
     return WR_CUDA_OK;
 }
 
+// true when `p` is memory the device can address as its own or a peer's allocation
+bool is_device_pointer(const void *p)
+{
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
 }  // namespace
+
+int wr_static_setup(int device)
+{
+    static_ptrs *sp = nullptr;
+    return static_setup(device, &sp);
+}
 
 extern "C" int wr_cuda_attn_decode_static(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv,
                                           uint32_t layer, const uint32_t *seq_lens, const float *q,
@@ -105,42 +129,12 @@ extern "C" int wr_cuda_attn_decode_static(wr_cuda_ctx *ctx, uint32_t n_sess, wr_
     rc = static_setup(ctx->device, &sp);
     if (rc != WR_CUDA_OK) return rc;
 
-    // Same work decomposition as wr_cuda_attn_decode, so the result is the same.
+    if (!is_device_pointer(q) || !is_device_pointer(out)) return WR_CUDA_ERR_INVAL;
+
+    // The work decomposition is wr_cuda_attn_decode's own, so the result is the same.
     params p;
-    const uint32_t group = n_q_heads / n_kv;
-    const uint32_t nt = group <= 4 ? 1u : 2u;
-    const uint32_t qsubs = (group + 4 * nt - 1) / (4 * nt);
-    uint32_t order[WR_CUDA_BATCH_MAX];
-    for (uint32_t s = 0; s < n_sess; ++s) order[s] = s;
-    std::stable_sort(order, order + n_sess,
-                     [&](uint32_t a, uint32_t b) { return seq_lens[a] > seq_lens[b]; });
-    uint32_t items = 0;
-    for (uint32_t i = 0; i < n_sess; ++i) {
-        const uint32_t s = order[i];
-        const uint32_t len = seq_lens[s];
-        const uint32_t key_lo = (window > 0 && len > window) ? len - window : 0;
-        const uint32_t n_tiles = (len + kTile - 1) / kTile;
-        const uint32_t tile_lo = key_lo / kTile;
-        const uint32_t span = n_tiles - tile_lo;
-        const uint32_t ct = chunk_tiles_for(span);
-        const uint32_t nc = (span + ct - 1) / ct;
-        p.b.pages[i] = kv[s]->d_pages + (size_t)layer * kv[s]->n_pages;
-        p.b.seq_len[i] = len;
-        p.page_base[i] = kv[s]->contig[layer] ? (const char *)kv[s]->pages[(size_t)layer * kv[s]->n_pages]
-                                              : nullptr;
-        p.row[i] = s;
-        p.key_lo[i] = key_lo;
-        p.tile_lo[i] = tile_lo;
-        p.n_tiles[i] = n_tiles;
-        p.chunk_tiles[i] = ct;
-        p.n_chunks[i] = nc;
-        p.item_base[i] = items;
-        items += n_kv * qsubs * nc;
-    }
-    for (uint32_t s = n_sess; s <= WR_CUDA_BATCH_MAX; ++s) p.item_base[s] = items;
-    for (uint32_t i = n_sess; i < WR_CUDA_BATCH_MAX; ++i) p.page_base[i] = nullptr;
-    p.page_bytes = wr_page_bytes(n_kv, hd);
-    p.n_groups = n_sess * n_kv * qsubs;
+    uint32_t nt = 1, items = 0;
+    wr_decode_plan(n_sess, kv, layer, seq_lens, n_q_heads, window, p, nt, items);
     if (items > WR_CUDA_STATIC_MAX_ITEMS || p.n_groups > WR_CUDA_STATIC_MAX_GROUPS)
         return WR_CUDA_ERR_LIMIT;           // the fixed scratch area cannot hold this call
     p.q = q;
@@ -148,11 +142,7 @@ extern "C" int wr_cuda_attn_decode_static(wr_cuda_ctx *ctx, uint32_t n_sess, wr_
     p.ws = sp->ws;
     p.tickets = sp->tickets;
     p.err = ctx->dev_err;
-    p.n_sess = n_sess;
-    p.n_q = n_q_heads;
-    p.n_kv = n_kv;
-    p.group = group;
-    p.qsubs = qsubs;
+    p.wait_limit = ctx->wait_limit;
     p.emit_triples = 0;
     p.scale = (scale_override > 0.0f) ? scale_override : 1.0f / sqrtf((float)hd);
     // The array keeps whatever the previous call (or an aborted one) left:

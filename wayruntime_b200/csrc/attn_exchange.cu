@@ -44,6 +44,7 @@ struct xchg_params {
     int *done;
     int *err;
     uint32_t world, rank, max_rows, hd, n_rows, step, parity;
+    long long wait_limit;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *addr, uint32_t v)
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(256) attn_exchange_combine_kernel(const xchg_p
         const uint32_t *flag = slot_flag(p.peer[p.rank], p.parity, threadIdx.x, p);
         const long long t0 = clock64();
         while (ld_acquire_sys(flag) != p.step) {
-            if (clock64() - t0 > 4000000000LL) {          // about two seconds
+            if (clock64() - t0 > p.wait_limit) {          // the context's wait limit
                 atomicExch(p.err, 21);
                 s_ok = 0;
                 break;
@@ -191,8 +192,8 @@ extern "C" int wr_cuda_xchg_handle(wr_cuda_xchg *x, void *handle_out)
 extern "C" int wr_cuda_xchg_connect(wr_cuda_xchg *x, const void *handles)
 {
     if (!x || !handles) return WR_CUDA_ERR_INVAL;
-    if (x->connected) return WR_CUDA_ERR_STATE;
     std::lock_guard<std::mutex> g(x->ctx->lock);
+    if (x->connected) return WR_CUDA_ERR_STATE;
     WR_CUDA_TRY(cudaSetDevice(x->ctx->device));
     for (uint32_t r = 0; r < x->world; ++r) {
         if (r == x->rank) continue;
@@ -206,6 +207,22 @@ extern "C" int wr_cuda_xchg_connect(wr_cuda_xchg *x, const void *handles)
         x->peer[r] = (char *)ptr;
         x->opened[r] = true;
     }
+    x->connected = true;
+    return WR_CUDA_OK;
+}
+
+extern "C" int wr_cuda_xchg_connect_local(wr_cuda_xchg *x, wr_cuda_xchg *const *all)
+{
+    if (!x || !all) return WR_CUDA_ERR_INVAL;
+    std::lock_guard<std::mutex> g(x->ctx->lock);
+    if (x->connected) return WR_CUDA_ERR_STATE;
+    for (uint32_t r = 0; r < x->world; ++r) {
+        const wr_cuda_xchg *o = all[r];
+        if (!o || o->world != x->world || o->rank != r || o->max_rows != x->max_rows || o->hd != x->hd)
+            return WR_CUDA_ERR_INVAL;
+        if (r == x->rank && o != x) return WR_CUDA_ERR_INVAL;
+    }
+    for (uint32_t r = 0; r < x->world; ++r) x->peer[r] = all[r]->local;   // same address space: no IPC mapping
     x->connected = true;
     return WR_CUDA_OK;
 }
@@ -246,6 +263,7 @@ extern "C" int wr_cuda_attn_exchange_combine(wr_cuda_ctx *ctx, wr_cuda_xchg *x, 
     p.max_rows = x->max_rows;
     p.hd = x->hd;
     p.n_rows = n_rows;
+    p.wait_limit = ctx->wait_limit;
     p.step = ++x->step;
     p.parity = x->step & 1u;
     // few CTAs: every one of them has to be resident while it waits for the peers

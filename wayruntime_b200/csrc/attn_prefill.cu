@@ -58,6 +58,7 @@ struct prefill_params {
     int *err;
     uint32_t n, p0, n_q, n_kv, group, n_pairs, window, n_qtiles;
     float scale_log2;           // score scale * log2(e)
+    long long wait_limit;       // SM clock cycles a device-side wait may last
 };
 
 struct smem_layout {
@@ -262,7 +263,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             uint64_t *empty = lane == 0 ? sm.empty_k : sm.empty_v;
             for (uint32_t i = kStages; i < n_kt; ++i) {
                 const uint32_t st = i % kStages;
-                if (!mbar_wait(&empty[st], ((i / kStages) - 1) & 1)) {
+                if (!mbar_wait(&empty[st], ((i / kStages) - 1) & 1, p.wait_limit)) {
                     atomicExch(p.err, 11);
                     break;
                 }
@@ -276,7 +277,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         if (lane == 0 && h < n_heads) {
             const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
             const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
-            bool ok = mbar_wait(&sm.bar_q, 0);
+            bool ok = mbar_wait(&sm.bar_q, 0, p.wait_limit);
             // This one thread feeds the tensor core, so its instruction count
             // per tile matters: descriptors are built once and an operand is
             // selected by adding its byte offset (>>4) to the address field.
@@ -299,7 +300,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             // Scores run two tiles ahead of the softmax that consumes them (S is
             // double-buffered in TMEM), so a softmax does not wait for its S.
             for (uint32_t i = 0; ok && i < min(2u, n_kt); ++i) {
-                ok = mbar_wait(&sm.full_k[i], 0);
+                ok = mbar_wait(&sm.full_k[i], 0, p.wait_limit);
                 if (!ok) break;
                 tc_fence_after();
                 issue_s(h, i);
@@ -309,16 +310,16 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 if (i + 2 < n_kt) {
                     // the softmax of tile i has its scores in registers: S[i&1] can take
                     // tile i+2 while that softmax is still exponentiating
-                    ok = mbar_wait(&sm.s_free[h][i & 1], (i >> 1) & 1);
-                    if (ok) ok = mbar_wait(&sm.full_k[(i + 2) % kStages], ((i + 2) / kStages) & 1);
+                    ok = mbar_wait(&sm.s_free[h][i & 1], (i >> 1) & 1, p.wait_limit);
+                    if (ok) ok = mbar_wait(&sm.full_k[(i + 2) % kStages], ((i + 2) / kStages) & 1, p.wait_limit);
                     if (!ok) break;
                     tc_fence_after();
                     issue_s(h, i + 2);
                     umma_commit(&sm.empty_k[(i + 2) % kStages]);
                 }
                 // softmax of (head h, tile i) has written P[i&1]
-                ok = mbar_wait(&sm.p_ready[h][i & 1], (i >> 1) & 1);
-                if (ok) ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1);
+                ok = mbar_wait(&sm.p_ready[h][i & 1], (i >> 1) & 1, p.wait_limit);
+                if (ok) ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1, p.wait_limit);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t vd = v_desc0 + (uint64_t)((i % kStages) * (kKVBlock >> 4));
@@ -350,7 +351,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         // The scores of the current tile live in s[]; the next tile's are fetched
         // from TMEM while this tile is still being exponentiated.
         float s[kBN];
-        bool ok = mbar_wait(&sm.s_full[h][0], 0);
+        bool ok = mbar_wait(&sm.s_full[h][0], 0, p.wait_limit);
         if (ok) {
             tc_fence_after();
             tmem_ld32_nowait(s_base, s);
@@ -389,7 +390,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             if (__any_sync(0xffffffffu, grow)) {
                 const float a = grow ? ex2_approx(m_ref - tm2) : 1.0f;
                 // O must hold every earlier tile (tile i-1 was the last one issued)
-                ok = mbar_wait(&sm.pv_done[h][(i - 1) & 1], ((i - 1) >> 1) & 1);
+                ok = mbar_wait(&sm.pv_done[h][(i - 1) & 1], ((i - 1) >> 1) & 1, p.wait_limit);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll 1
@@ -410,7 +411,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             // P = 2^(s*c2 - m_ref) as F16 in operand order: row `row`, 8 chunks of 8 keys;
             // P[i&1] is free once the P.V of tile i-2 has read it
             if (i >= 2) {
-                ok = mbar_wait(&sm.pv_done[h][i & 1], ((i >> 1) - 1) & 1);
+                ok = mbar_wait(&sm.pv_done[h][i & 1], ((i >> 1) - 1) & 1, p.wait_limit);
                 if (!ok) break;
             }
             // The exponentials saturate the special-function unit, which this warp
@@ -418,7 +419,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             // turns, so that one's loads, max and hand-offs run under the other's
             // exponentials instead of both queueing for the unit at once.
             if (two && (h == 1 || i > 0)) {
-                ok = mbar_wait(&sm.xu_turn[quad][h], (h == 1 ? i : i - 1) & 1);
+                ok = mbar_wait(&sm.xu_turn[quad][h], (h == 1 ? i : i - 1) & 1, p.wait_limit);
                 if (!ok) break;
             }
             uint8_t *prow = sm.p[h][i & 1] + row * 128;
@@ -445,7 +446,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             if (more) {
                 // columns 0..31 are spent: refill them with the next tile's (its scores
                 // were issued two tiles ahead, so this wait normally falls through)
-                ok = mbar_wait(&sm.s_full[h][(i + 1) & 1], ((i + 1) >> 1) & 1);
+                ok = mbar_wait(&sm.s_full[h][(i + 1) & 1], ((i + 1) >> 1) & 1, p.wait_limit);
                 if (!ok) break;
                 tc_fence_after();
                 tmem_ld32_nowait(s_next, s);
@@ -461,7 +462,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 // prompt (or belong to a rolled-back step): clear them in the
                 // staged V tile so that 0 * garbage cannot make a NaN (each head's
                 // group does it before releasing its own P.V; the writes are equal).
-                ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1);
+                ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1, p.wait_limit);
                 if (!ok) break;
                 if (row < kBN && key0 + row >= key_end) {
                     uint8_t *vrow = sm.v[i % kStages] + row * 128;
@@ -486,7 +487,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             // The last P.V completes after every earlier one (one issuing thread,
             // in order); this group has already observed the previous phase of that
             // barrier (tile n_kt-3), so the parity wait is one completion behind at most.
-            ok = mbar_wait(&sm.pv_done[h][(n_kt - 1) & 1], ((n_kt - 1) >> 1) & 1);
+            ok = mbar_wait(&sm.pv_done[h][(n_kt - 1) & 1], ((n_kt - 1) >> 1) & 1, p.wait_limit);
             if (ok) {
                 tc_fence_after();
                 const float inv = (l > 0.f) ? 1.0f / l : 0.f;
@@ -642,6 +643,7 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
     p.pages = kv->d_pages + (size_t)layer * kv->n_pages;
     p.out = dout;
     p.err = ctx->dev_err;
+    p.wait_limit = ctx->wait_limit;
     p.n = n;
     p.p0 = p0;
     p.n_q = n_q_heads;
@@ -663,7 +665,7 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
     WR_CUDA_TRY(cudaGetLastError());
     if (host) {
         WR_CUDA_TRY(cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+        return wr_ctx_sync_checked(ctx);
     }
     return WR_CUDA_OK;
 }

@@ -51,6 +51,14 @@ extern "C" int wr_cuda_ctx_create(int device, wr_cuda_ctx **out)
         return e == cudaErrorMemoryAllocation ? WR_CUDA_ERR_NOMEM : WR_CUDA_ERR_INTERNAL;
     }
     *ctx->host_err = 0;
+    // The allocation-free decode entry point keeps its scratch in a __device__
+    // array of this library: instantiate it (and its kernels) now, so that its
+    // memory is taken at start-up, before the caller sizes the KV pool.
+    rc = wr_static_setup(device);
+    if (rc != WR_CUDA_OK) {
+        wr_cuda_ctx_destroy(ctx);
+        return rc;
+    }
     *out = ctx;
     return WR_CUDA_OK;
 }
@@ -73,11 +81,8 @@ extern "C" void wr_cuda_ctx_destroy(wr_cuda_ctx *ctx)
     delete ctx;
 }
 
-extern "C" int wr_cuda_ctx_sync(wr_cuda_ctx *ctx)
+int wr_ctx_sync_checked(wr_cuda_ctx *ctx)
 {
-    if (!ctx) return WR_CUDA_ERR_INVAL;
-    std::lock_guard<std::mutex> g(ctx->lock);
-    WR_CUDA_TRY(cudaSetDevice(ctx->device));
     WR_CUDA_TRY(cudaMemcpyAsync(ctx->host_err, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost,
                                 ctx->stream));
     WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
@@ -93,6 +98,22 @@ extern "C" int wr_cuda_ctx_sync(wr_cuda_ctx *ctx)
     return WR_CUDA_OK;
 }
 
+extern "C" int wr_cuda_ctx_sync(wr_cuda_ctx *ctx)
+{
+    if (!ctx) return WR_CUDA_ERR_INVAL;
+    std::lock_guard<std::mutex> g(ctx->lock);
+    WR_CUDA_TRY(cudaSetDevice(ctx->device));
+    return wr_ctx_sync_checked(ctx);
+}
+
+extern "C" int wr_cuda_ctx_set_wait_limit(wr_cuda_ctx *ctx, int64_t cycles)
+{
+    if (!ctx || cycles <= 0) return WR_CUDA_ERR_INVAL;
+    std::lock_guard<std::mutex> g(ctx->lock);
+    ctx->wait_limit = (long long)cycles;
+    return WR_CUDA_OK;
+}
+
 extern "C" void *wr_cuda_ctx_stream(wr_cuda_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 
 extern "C" int wr_cuda_ctx_set_attn_max_seq(wr_cuda_ctx *ctx, uint32_t max_seq)
@@ -102,6 +123,31 @@ extern "C" int wr_cuda_ctx_set_attn_max_seq(wr_cuda_ctx *ctx, uint32_t max_seq)
     std::lock_guard<std::mutex> g(ctx->lock);
     ctx->attn_max_seq = max_seq;
     return WR_CUDA_OK;
+}
+
+extern "C" int wr_cuda_host_alloc(wr_cuda_ctx *ctx, uint64_t bytes, void **out)
+{
+    if (!ctx || !out || bytes == 0) return WR_CUDA_ERR_INVAL;
+    *out = nullptr;
+    std::lock_guard<std::mutex> g(ctx->lock);
+    WR_CUDA_TRY(cudaSetDevice(ctx->device));
+    void *p = nullptr;
+    if (cudaHostAlloc(&p, (size_t)bytes, cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return WR_CUDA_ERR_NOMEM;
+    }
+    *out = p;
+    return WR_CUDA_OK;
+}
+
+extern "C" void wr_cuda_host_free(wr_cuda_ctx *ctx, void *p)
+{
+    if (!ctx || !p) return;
+    std::lock_guard<std::mutex> g(ctx->lock);
+    (void)cudaSetDevice(ctx->device);
+    (void)cudaStreamSynchronize(ctx->stream);      // a kernel may still be reading the rows in place
+    (void)cudaFreeHost(p);
+    (void)cudaGetLastError();
 }
 
 extern "C" uint64_t wr_cuda_ctx_launch_count(wr_cuda_ctx *ctx)
@@ -326,6 +372,9 @@ static int kv_rows_xfer(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t layer, int wh
     if (layer >= kv->n_layers || (which != 0 && which != 1)) return WR_CUDA_ERR_INVAL;
     if (n == 0) return WR_CUDA_OK;
     if ((uint64_t)row0 + n > kv->max_ctx) return WR_CUDA_ERR_CTX_FULL;
+    if (mem != WR_CUDA_MEM_HOST && mem != WR_CUDA_MEM_DEVICE) return WR_CUDA_ERR_INVAL;
+    // device rows move as 16-byte vectors when head_dim allows it
+    if (mem == WR_CUDA_MEM_DEVICE && (kv->hd & 7u) == 0 && ((uintptr_t)buf & 15u)) return WR_CUDA_ERR_INVAL;
     std::lock_guard<std::mutex> g(ctx->lock);
     WR_CUDA_TRY(cudaSetDevice(ctx->device));
     size_t bytes = (size_t)n * kv->n_kv * kv->hd * 2u;
@@ -347,7 +396,7 @@ static int kv_rows_xfer(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t layer, int wh
     if (mem == WR_CUDA_MEM_HOST) {
         if (!to_cache)
             WR_CUDA_TRY(cudaMemcpyAsync(buf, dbuf, bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+        return wr_ctx_sync_checked(ctx);
     }
     return WR_CUDA_OK;
 }
@@ -600,7 +649,7 @@ extern "C" int wr_cuda_kv_append(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *
     if (mem == WR_CUDA_MEM_HOST) {
         if (q_rows && (flags & WR_CUDA_APPEND_ROPE))
             WR_CUDA_TRY(cudaMemcpyAsync(q_rows, dq, q_bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+        return wr_ctx_sync_checked(ctx);
     }
     return WR_CUDA_OK;
 }

@@ -83,6 +83,9 @@ struct wr_cuda_ctx {
     size_t stage_host_bytes = 0;
     int live_kv = 0;
     uint32_t attr_flags = 0;         // per-device kernel attributes already set
+    // SM clock cycles a device-side wait may last before the kernel gives up
+    // (wr_cuda_ctx_set_wait_limit); every kernel of the context gets this value.
+    long long wait_limit = WR_CUDA_WAIT_LIMIT_DEFAULT;
 };
 
 struct wr_cuda_kv {
@@ -113,6 +116,10 @@ struct wr_batch_desc {
     } while (0)
 
 int wr_ctx_reserve_stage(wr_cuda_ctx *ctx, size_t dev_bytes, size_t host_bytes);
+// Wait for the context's stream and report (and clear) the device-side error
+// word: WR_CUDA_ERR_INTERNAL when a kernel gave up on a bounded wait.  Every
+// call that synchronises ends with this.  Caller holds ctx->lock.
+int wr_ctx_sync_checked(wr_cuda_ctx *ctx);
 int wr_ctx_reserve_ws(wr_cuda_ctx *ctx, size_t ws_bytes, size_t tickets);
 int wr_kv_batch_check(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer);
 int wr_append_validate(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
@@ -123,6 +130,10 @@ int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
                      const float *dv, float *dq, uint32_t n_q_heads, float theta_base,
                      uint32_t n_rot_pairs, uint32_t flags,
                      const float *dq_in /* null: rotate dq in place */);
+
+// Resolve the device addresses of the allocation-free decode path's scratch
+// arrays and set its kernels' attributes, once per device (that device current).
+int wr_static_setup(int device);
 
 // Device-side address of a page-locked host buffer (the same pointer under
 // unified addressing), or null when `p` is pageable host memory.
@@ -154,10 +165,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait: returns false when the phase did not complete within about
-// two seconds of SM clock (the caller records an error and unwinds; nothing
-// in this library spins without a limit).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+// Bounded wait: returns false when the phase did not complete within `limit`
+// cycles of SM clock (the context's wait limit; the caller records an error
+// and unwinds; nothing in this library spins without a limit).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, long long limit)
 {
     const uint32_t addr = smem_u32(bar);
     long long t0 = 0;                       // the clock is read only once a poll has failed
@@ -172,7 +183,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
             : "memory");
         if (done) return true;
         if (first) t0 = clock64();
-        else if (clock64() - t0 > 4000000000LL) return false;
+        else if (clock64() - t0 > limit) return false;
     }
 }
 __device__ __forceinline__ void fence_barrier_init()

@@ -10,7 +10,9 @@
  * wri_self_test_llm_step, wri_self_test_batch_step), so that linking these
  * objects before the reference archive leaves session.o and batch.o unused.
  * It is compiled against the reference's own headers (include/, src/) at
- * integration time; nothing of the reference is copied here.
+ * integration time.  The public entry points restate the reference's argument
+ * checks, locking order and cursor rules (they are the contract a drop-in has
+ * to reproduce); everything behind them is new.
  *
  * What stays on the host, through the reference's own ops and therefore with
  * the reference's own numerics: embedding, RMSNorm, the Q/K/V/O and FFN
@@ -27,6 +29,15 @@
  * mis-run): Gemma-class models (sandwich norms, per-layer head_dim, shared-KV
  * layers, per-layer-input embeddings, sliding-window layers).
  *
+ * All row scratch (Q / K / V / attention / residual rows for a whole batch or
+ * a prefill chunk) is page-locked host memory taken once at wr_session_create
+ * and freed at destroy — "no reallocation during decode"
+ * (include/wayruntime/wayruntime.h:388-392) holds for it as for the KV pages —
+ * so the device calls read and write the rows in place instead of staging
+ * them.  A prompt longer than WR_B200_ROWS_MAX tokens is prefilled in chunks of
+ * that many rows; rows are independent and key tiles sit at absolute
+ * positions, so chunking does not change any row's result.
+ *
  * Environment: WR_CUDA_DEVICE selects the device (default 0);
  * WR_B200_PREFILL=decode makes wr_prefill run token by token through the
  * decode kernel (F32-exact queries) instead of the tensor-core prefill kernel
@@ -42,26 +53,16 @@
 
 /* ------------------------------------------------------------- device side */
 
-static wr_cuda_ctx *g_cuda;            /* one per process, like the engine */
-static int          g_cuda_rc;
-static volatile int g_cuda_guard;
+#include "wr_b200_host.h"
 
 static wr_cuda_ctx *cuda_ctx(int *rc_out)
 {
-    while (__atomic_exchange_n(&g_cuda_guard, 1, __ATOMIC_ACQUIRE)) { }
-    if (!g_cuda && g_cuda_rc == 0) {
-        const char *dev = getenv("WR_CUDA_DEVICE");
-        int d = dev ? atoi(dev) : 0;
-        g_cuda_rc = wr_cuda_ctx_create(d, &g_cuda);
-        if (g_cuda_rc == 0)
-            g_cuda_rc = wr_cuda_ctx_set_attn_max_seq(g_cuda, WR_ATTN_MAX_SEQ);
-        if (g_cuda_rc != 0)
-            wri_log_msg(0, "b200 session: no usable sm_100 device (rc=%d); there is no CPU "
-                           "fallback for attention", g_cuda_rc);
-    }
-    wr_cuda_ctx *c = g_cuda;
-    if (rc_out) *rc_out = g_cuda_rc;
-    __atomic_store_n(&g_cuda_guard, 0, __ATOMIC_RELEASE);
+    int rc = 0;
+    wr_cuda_ctx *c = wr_b200_cuda_ctx(&rc);
+    if (!c)
+        wri_log_msg(0, "b200 session: no usable sm_100 device (rc=%d); there is no CPU "
+                       "fallback for attention", rc);
+    if (rc_out) *rc_out = rc;
     return c;
 }
 
@@ -80,10 +81,25 @@ void wr_b200_set_attn_tap(wr_b200_attn_tap_fn fn, void *user)
 
 /* ------------------------------------------------------------------ session */
 
+/* Rows a session's scratch holds: a whole batch (WR_BATCH_MAX) or one prefill chunk. */
+#define WR_B200_ROWS_MAX 256u
+
+typedef struct row_buffers {
+    uint32_t rows;             /* capacity */
+    float *resid;   /* [rows][hidden]  */
+    float *q;       /* [rows][n_q*hd]  */
+    float *k, *v;   /* [rows][n_kv*hd] */
+    float *attn;    /* [rows][n_q*hd]  */
+    float *normed, *proj, *gate, *up;   /* one row each */
+    void  *block;              /* page-locked (wr_cuda_host_alloc) */
+} row_buffers;
+
 typedef struct b200_session {
     struct wr_session pub;     /* first member: generate.c reads s->model through it */
     wr_cuda_kv *kv;
+    wr_cuda_ctx *cuda;
     float      *host;          /* one aligned block holding the scratch tensors */
+    row_buffers rb;            /* taken once at create */
 } b200_session;
 
 static b200_session *priv(wr_session *s) { return (b200_session *)s; }
@@ -113,6 +129,29 @@ static uint32_t max_ffn(const wr_model *m)
 }
 
 static size_t pad16(size_t n) { return (n + 15u) & ~(size_t)15u; }
+
+static int rows_alloc(row_buffers *rb, wr_cuda_ctx *cuda, const wr_model *m, uint32_t rows)
+{
+    const size_t hid = m->hidden_dim, nq = (size_t)m->n_q_heads * m->head_dim,
+                 nkv = (size_t)m->n_kv_heads * m->head_dim, ffn = max_ffn(m);
+    const size_t total = rows * (pad16(hid) + 2 * pad16(nq) + 2 * pad16(nkv)) + 2 * pad16(hid) +
+                         2 * pad16(ffn);
+    memset(rb, 0, sizeof(*rb));
+    int rc = wr_cuda_host_alloc(cuda, total * sizeof(float), &rb->block);
+    if (rc != 0) return rc;
+    float *p = rb->block;
+    rb->rows = rows;
+    rb->resid = p;  p += rows * pad16(hid);
+    rb->q = p;      p += rows * pad16(nq);
+    rb->attn = p;   p += rows * pad16(nq);
+    rb->k = p;      p += rows * pad16(nkv);
+    rb->v = p;      p += rows * pad16(nkv);
+    rb->normed = p; p += pad16(hid);
+    rb->proj = p;   p += pad16(hid);
+    rb->gate = p;   p += pad16(ffn);
+    rb->up = p;
+    return WR_OK;
+}
 
 wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_session **out)
 {
@@ -166,9 +205,16 @@ wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_ses
     f32_tensor(&s->ffn_up, p, 1, ffn, 0, 0);                   p += pad16(ffn);
     f32_tensor(&s->logits, p, 1, m->vocab_size, 0, 0);
 
+    bs->cuda = cuda;
     int rc = wr_cuda_kv_create(cuda, m->n_layers, m->n_kv_heads, hd, max_ctx, &bs->kv);
+    if (rc == 0) {
+        uint32_t rows = max_ctx < WR_B200_ROWS_MAX ? max_ctx : WR_B200_ROWS_MAX;
+        if (rows < WR_BATCH_MAX) rows = WR_BATCH_MAX;
+        rc = rows_alloc(&bs->rb, cuda, m, rows);
+        if (rc != 0) { wr_cuda_kv_destroy(bs->kv); bs->kv = NULL; }
+    }
     if (rc != 0) {
-        wri_log_msg(0, "b200 session: device KV allocation failed (rc=%d)", rc);
+        wri_log_msg(0, "b200 session: device KV / row scratch allocation failed (rc=%d)", rc);
         free(bs->host);
         wr_mutex_destroy(s->lock);
         free(bs);
@@ -192,6 +238,7 @@ void wr_session_destroy(wr_session *s)
         wr_mutex_unlock(m->lock);
     }
     if (bs->kv) wr_cuda_kv_destroy(bs->kv);
+    if (bs->rb.block) wr_cuda_host_free(bs->cuda, bs->rb.block);
     free(bs->host);
     if (s->lock) wr_mutex_destroy(s->lock);
     free(bs);
@@ -214,39 +261,6 @@ wr_status wr_session_status(const wr_session *s)
 
 /* --------------------------------------------------------- forward over rows */
 
-typedef struct row_buffers {
-    uint32_t rows;
-    float *resid;   /* [rows][hidden]  */
-    float *q;       /* [rows][n_q*hd]  */
-    float *k, *v;   /* [rows][n_kv*hd] */
-    float *attn;    /* [rows][n_q*hd]  */
-    float *normed, *proj, *gate, *up;   /* one row each */
-    void  *block;
-} row_buffers;
-
-static int rows_alloc(row_buffers *rb, const wr_model *m, uint32_t rows)
-{
-    const size_t hid = m->hidden_dim, nq = (size_t)m->n_q_heads * m->head_dim,
-                 nkv = (size_t)m->n_kv_heads * m->head_dim, ffn = max_ffn(m);
-    const size_t total = rows * (pad16(hid) + 2 * pad16(nq) + 2 * pad16(nkv)) + 2 * pad16(hid) +
-                         2 * pad16(ffn);
-    memset(rb, 0, sizeof(*rb));
-    rb->block = aligned_alloc(64, total * sizeof(float));
-    if (!rb->block) return WR_ERR_NOMEM;
-    float *p = rb->block;
-    rb->rows = rows;
-    rb->resid = p;  p += rows * pad16(hid);
-    rb->q = p;      p += rows * pad16(nq);
-    rb->attn = p;   p += rows * pad16(nq);
-    rb->k = p;      p += rows * pad16(nkv);
-    rb->v = p;      p += rows * pad16(nkv);
-    rb->normed = p; p += pad16(hid);
-    rb->proj = p;   p += pad16(hid);
-    rb->gate = p;   p += pad16(ffn);
-    rb->up = p;
-    return WR_OK;
-}
-
 static wr_status fail(const char *what, uint32_t layer, int rc)
 {
     wri_log_msg(0, "b200 session: %s failed at layer %u (rc=%d)", what, layer, rc);
@@ -259,10 +273,11 @@ enum { ATTN_DECODE = 0, ATTN_PREFILL = 1 };
  *   ATTN_DECODE : row r is the new token of session kvs[r] at position pos[r];
  *   ATTN_PREFILL: rows are consecutive tokens of session kvs[0] from pos[0].
  * On success rb->resid holds the pre-final-norm hidden rows. */
-static wr_status forward_rows(const wr_model *m, row_buffers *rb, const uint32_t *tokens,
+static wr_status forward_rows(const wr_model *m, row_buffers *rb, uint32_t R, const uint32_t *tokens,
                               wr_cuda_kv *const *kvs, const uint32_t *pos, int mode)
 {
-    const uint32_t R = rb->rows, hid = m->hidden_dim, hd = m->head_dim;
+    if (R == 0 || R > rb->rows) return WR_ERR_INTERNAL;
+    const uint32_t hid = m->hidden_dim, hd = m->head_dim;
     const uint32_t nq = m->n_q_heads * hd, nkv = m->n_kv_heads * hd;
     const size_t s_hid = pad16(hid), s_q = pad16(nq), s_kv = pad16(nkv);
     const float eps = m->rms_eps;
@@ -387,14 +402,11 @@ static wr_status finish_row(wr_session *s, const float *resid_row, int compute_l
  * Kept as an external symbol because the reference exports it. */
 wr_status wri_session_decode_body(wr_session *s, uint32_t token)
 {
-    row_buffers rb;
-    int rc = rows_alloc(&rb, s->model, 1);
-    if (rc != WR_OK) return (wr_status)rc;
+    row_buffers *rb = &priv(s)->rb;
     wr_cuda_kv *kv = priv(s)->kv;
     uint32_t pos = s->pos;
-    wr_status st = forward_rows(s->model, &rb, &token, &kv, &pos, ATTN_DECODE);
-    if (st == WR_OK) st = finish_row(s, rb.resid, 0);
-    free(rb.block);
+    wr_status st = forward_rows(s->model, rb, 1, &token, &kv, &pos, ATTN_DECODE);
+    if (st == WR_OK) st = finish_row(s, rb->resid, 0);
     return st;
 }
 
@@ -406,15 +418,11 @@ wr_status wri_session_step(wr_session *s, uint32_t token, int compute_logits)
     if (s->pos >= s->max_context) {
         st = WR_ERR_CTX_FULL;                       /* consumed nothing */
     } else {
-        row_buffers rb;
-        st = (wr_status)rows_alloc(&rb, s->model, 1);
-        if (st == WR_OK) {
-            wr_cuda_kv *kv = priv(s)->kv;
-            uint32_t pos = s->pos;
-            st = forward_rows(s->model, &rb, &token, &kv, &pos, ATTN_DECODE);
-            if (st == WR_OK) st = finish_row(s, rb.resid, compute_logits);
-            free(rb.block);
-        }
+        row_buffers *rb = &priv(s)->rb;
+        wr_cuda_kv *kv = priv(s)->kv;
+        uint32_t pos = s->pos;
+        st = forward_rows(s->model, rb, 1, &token, &kv, &pos, ATTN_DECODE);
+        if (st == WR_OK) st = finish_row(s, rb->resid, compute_logits);
         if (st == WR_OK) __atomic_store_n(&s->pos, s->pos + 1, __ATOMIC_RELEASE);
     }
     __atomic_store_n(&s->last_status, st, __ATOMIC_RELEASE);
@@ -437,24 +445,23 @@ int wri_session_prefill(wr_session *s, const uint32_t *ids, uint32_t n)
         const char *mode = getenv("WR_B200_PREFILL");
         const int by_token = (mode && strcmp(mode, "decode") == 0) || s->model->head_dim != 128;
         wr_cuda_kv *kv = priv(s)->kv;
+        row_buffers *rb = &priv(s)->rb;
         if (by_token) {
-            row_buffers rb;
-            st = (wr_status)rows_alloc(&rb, s->model, 1);
             uint32_t pos = s->pos;
             for (uint32_t i = 0; st == WR_OK && i < n; i++, pos++)
-                st = forward_rows(s->model, &rb, &ids[i], &kv, &pos, ATTN_DECODE);
-            if (st == WR_OK) st = finish_row(s, rb.resid, 0);
-            if (rb.block) free(rb.block);
+                st = forward_rows(s->model, rb, 1, &ids[i], &kv, &pos, ATTN_DECODE);
+            if (st == WR_OK) st = finish_row(s, rb->resid, 0);
         } else {
-            row_buffers rb;
-            st = (wr_status)rows_alloc(&rb, s->model, n);
-            if (st == WR_OK) {
-                uint32_t pos = s->pos;
-                st = forward_rows(s->model, &rb, ids, &kv, &pos, ATTN_PREFILL);
-                if (st == WR_OK)
-                    st = finish_row(s, rb.resid + (size_t)(n - 1) * pad16(s->model->hidden_dim), 0);
-                free(rb.block);
+            /* chunks of at most rb->rows tokens: rows are independent, key tiles absolute */
+            uint32_t done = 0, last = 0;
+            while (st == WR_OK && done < n) {
+                last = (n - done < rb->rows) ? n - done : rb->rows;
+                uint32_t pos = s->pos + done;
+                st = forward_rows(s->model, rb, last, ids + done, &kv, &pos, ATTN_PREFILL);
+                done += last;
             }
+            if (st == WR_OK)
+                st = finish_row(s, rb->resid + (size_t)(last - 1) * pad16(s->model->hidden_dim), 0);
         }
         if (st == WR_OK) __atomic_store_n(&s->pos, s->pos + n, __ATOMIC_RELEASE);
     }
@@ -498,17 +505,14 @@ int wri_batch_decode_step(wr_session *const *sessions, const uint32_t *tokens, u
     for (uint32_t i = 0; i < n && st == WR_OK; i++)
         if (sessions[i]->pos >= sessions[i]->max_context) st = WR_ERR_CTX_FULL;
     if (st == WR_OK) {
-        row_buffers rb;
-        st = (wr_status)rows_alloc(&rb, m, n);
-        if (st == WR_OK) {
-            wr_cuda_kv *kvs[WR_BATCH_MAX];
-            uint32_t pos[WR_BATCH_MAX];
-            for (uint32_t i = 0; i < n; i++) { kvs[i] = priv(sessions[i])->kv; pos[i] = sessions[i]->pos; }
-            st = forward_rows(m, &rb, tokens, kvs, pos, ATTN_DECODE);    /* all sessions, one grid per layer */
-            for (uint32_t i = 0; i < n && st == WR_OK; i++)
-                st = finish_row(sessions[i], rb.resid + (size_t)i * pad16(m->hidden_dim), 1);
-            free(rb.block);
-        }
+        /* the rows of the whole batch live in the scratch of one of its (locked) sessions */
+        row_buffers *rb = &priv(order[0])->rb;
+        wr_cuda_kv *kvs[WR_BATCH_MAX];
+        uint32_t pos[WR_BATCH_MAX];
+        for (uint32_t i = 0; i < n; i++) { kvs[i] = priv(sessions[i])->kv; pos[i] = sessions[i]->pos; }
+        st = forward_rows(m, rb, n, tokens, kvs, pos, ATTN_DECODE);    /* all sessions, one grid per layer */
+        for (uint32_t i = 0; i < n && st == WR_OK; i++)
+            st = finish_row(sessions[i], rb->resid + (size_t)i * pad16(m->hidden_dim), 1);
     }
     if (st == WR_OK)
         for (uint32_t i = 0; i < n; i++)

@@ -69,11 +69,25 @@ def make_exchange(ctx, max_rows, head_dim, group=None):
         err = str(exc)
     # every rank learns whether every rank connected: nobody is left waiting in a kernel
     errs = [None] * world
-    dist.all_gather_object(errs, err, group=group)
+    dist.all_gather_object(errs, err, group=group)         # (also a barrier: nobody closes early)
     if any(e is not None for e in errs):
         x.close()
         raise RuntimeError(f"peer exchange unavailable: {[e for e in errs if e][0]}")
     return x
+
+
+def close_exchange(x, ctx, group=None):
+    """Collective destroy of an `Exchange`: a peer's kernel may still be storing
+    into this rank's buffer, so every rank drains its own stream (a step that
+    timed out is reported here and does not stop the close), the ranks meet,
+    and only then is the buffer freed."""
+    import torch.distributed as dist
+    try:
+        ctx.sync()
+    except Exception:
+        pass
+    dist.barrier(group=group)
+    x.close()
 
 
 def decode_split_kv(ctx, kvs, layer, local_lens, q, out, n_q_heads, scale=0.0, group=None,
