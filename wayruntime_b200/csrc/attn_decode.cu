@@ -185,7 +185,7 @@ void wr_decode_plan(uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer, cons
         const uint32_t n_tiles = (len + kTile - 1) / kTile;
         const uint32_t tile_lo = key_lo / kTile;
         const uint32_t span = n_tiles - tile_lo;
-        const uint32_t ct = chunk_tiles_for(span);             // chunk length: this session alone
+        const uint32_t ct = chunk_tiles_for(span, n_kv, qsubs); // chunk length: this session and the cache geometry alone
         const uint32_t nc = (span + ct - 1) / ct;              // 0 for an empty shard
         p.b.pages[i] = kv[s]->d_pages + (size_t)layer * kv[s]->n_pages;
         p.b.seq_len[i] = len;

@@ -52,17 +52,27 @@ constexpr int kTicketsPerGroup = 4;                    // arrival counters reser
 constexpr int kTicketExtra = 2;                        // after the tickets: work queue, engine exits
 constexpr uint32_t kBlockBytes = kTile * kHd * 2;      // one K or V tile of one head
 constexpr int kTripleStride = WR_CUDA_TRIPLE_PAD + kHd;  // m, l, 0, 0, o[128]
-constexpr int kMaxChunks = 32;                         // per session (lane c of a merge warp holds chunk c)
+constexpr int kMaxChunks = 128;                        // per session (lane c of a merge warp holds chunks c, c+32, c+64, c+96)
+constexpr int kChunkSlots = kMaxChunks / 32;
 constexpr int kChunkBatch = 16;                        // chunk rows a merge keeps in flight per head
 constexpr int kMinChunkTiles = 2;
+constexpr int kItemsPerSessionTarget = 128;            // work items one session should offer the engines
 
-// Tiles per chunk: a function of the session's own span only (batch
-// invariance).  Up to 16 chunks for sessions of at most 64 tiles; longer ones
-// may use up to 32, which keeps items short enough to balance a small batch of
-// long sessions over all engines.
-__host__ __device__ inline uint32_t chunk_tiles_for(uint32_t span_tiles)
+// Tiles per chunk: a function of the session's own span and of the cache
+// geometry only — never of its batch mates (batch invariance).  A session
+// is cut so that it offers about kItemsPerSessionTarget items (kv heads x
+// q subgroups x chunks): with eight kv heads that is 16 chunks, with one kv
+// head (a KV-head-sharded cache) up to 128, so that a small batch still
+// reaches every engine of the machine.  Sessions longer than 64 tiles use at
+// least 32 chunks, which keeps items short enough to balance a few long
+// sessions.  A chunk is never shorter than kMinChunkTiles.
+__host__ __device__ inline uint32_t chunk_tiles_for(uint32_t span_tiles, uint32_t n_kv, uint32_t qsubs)
 {
-    const uint32_t max_chunks = span_tiles > 64u ? (uint32_t)kMaxChunks : 16u;
+    const uint32_t per_chunk = n_kv * qsubs;
+    uint32_t max_chunks = ((uint32_t)kItemsPerSessionTarget + per_chunk - 1) / per_chunk;
+    if (max_chunks < 16u) max_chunks = 16u;
+    if (span_tiles > 64u && max_chunks < 32u) max_chunks = 32u;
+    if (max_chunks > (uint32_t)kMaxChunks) max_chunks = (uint32_t)kMaxChunks;
     const uint32_t ct = (span_tiles + max_chunks - 1) / max_chunks;
     return ct < (uint32_t)kMinChunkTiles ? (uint32_t)kMinChunkTiles : ct;
 }
@@ -148,20 +158,25 @@ __device__ __forceinline__ int atom_add_relaxed(int *addr, int v)
 __device__ __forceinline__ void merge_head_pair(const params &p, size_t row0, size_t first_item, uint32_t nc,
                                              uint32_t hs0, uint32_t heads_here, uint32_t lane, bool dry_run)
 {
-    float mc[2], lc[2];
+    // lane c holds (m, l) of chunks c, c + 32, c + 64, c + 96
+    float mc[2][kChunkSlots], lc[2][kChunkSlots];
 #pragma unroll
     for (uint32_t e = 0; e < 2; ++e) {
         const uint32_t hs = hs0 + e;
-        mc[e] = WR_NEG_SENTINEL;
-        lc[e] = 0.f;
-        if (lane < nc && hs < heads_here) {
-            const float *tr = p.ws + ((first_item + lane) * 8 + hs) * kTripleStride;
-            mc[e] = __ldcg(tr);
-            lc[e] = __ldcg(tr + 1);
+#pragma unroll
+        for (int q = 0; q < kChunkSlots; ++q) {
+            mc[e][q] = WR_NEG_SENTINEL;
+            lc[e][q] = 0.f;
+            const uint32_t c = q * 32 + lane;
+            if (c < nc && hs < heads_here) {
+                const float *tr = p.ws + ((first_item + c) * 8 + hs) * kTripleStride;
+                mc[e][q] = __ldcg(tr);
+                lc[e][q] = __ldcg(tr + 1);
+            }
         }
     }
     float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
-    float mstar[2], wgt[2], L[2] = {0.f, 0.f};
+    float mstar[2], wgt[2][kChunkSlots], L[2] = {0.f, 0.f};
     // chunk rows in batches of kChunkBatch (one batch unless the session is long)
 #pragma unroll 1
     for (uint32_t c0 = 0; c0 == 0 || c0 < nc; c0 += kChunkBatch) {
@@ -179,19 +194,29 @@ __device__ __forceinline__ void merge_head_pair(const params &p, size_t row0, si
         if (c0 == 0) {
 #pragma unroll
             for (uint32_t e = 0; e < 2; ++e) {
-                mstar[e] = mc[e];
+                float mx = mc[e][0];
+#pragma unroll
+                for (int q = 1; q < kChunkSlots; ++q) mx = fmaxf(mx, mc[e][q]);
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1)
-                    mstar[e] = fmaxf(mstar[e], __shfl_xor_sync(0xffffffffu, mstar[e], off));
-                wgt[e] = (mc[e] == WR_NEG_SENTINEL) ? 0.f : __expf(mc[e] - mstar[e]);
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+                mstar[e] = mx;
+#pragma unroll
+                for (int q = 0; q < kChunkSlots; ++q)
+                    wgt[e][q] = (mc[e][q] == WR_NEG_SENTINEL) ? 0.f : __expf(mc[e][q] - mx);
             }
         }
+        const uint32_t slot = c0 >> 5;             // the whole batch lies in one group of 32 chunks
 #pragma unroll
         for (uint32_t e = 0; e < 2; ++e) {
-            const float wl = wgt[e] * lc[e];
+            float wsel = wgt[e][0], lsel = lc[e][0];
+#pragma unroll
+            for (int q = 1; q < kChunkSlots; ++q)
+                if (slot == (uint32_t)q) { wsel = wgt[e][q]; lsel = lc[e][q]; }
+            const float wl = wsel * lsel;
 #pragma unroll
             for (int j = 0; j < kChunkBatch; ++j) {
-                const float wj = __shfl_sync(0xffffffffu, wgt[e], (c0 + j) & 31);
+                const float wj = __shfl_sync(0xffffffffu, wsel, (c0 + j) & 31);
                 L[e] += __shfl_sync(0xffffffffu, wl, (c0 + j) & 31);
                 acc[e].x += wj * ov[e][j].x; acc[e].y += wj * ov[e][j].y;
                 acc[e].z += wj * ov[e][j].z; acc[e].w += wj * ov[e][j].w;

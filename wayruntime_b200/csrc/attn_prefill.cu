@@ -5,27 +5,35 @@
 // rows [0, p0+i] through wri_op_gqa_attention (src/core/kernels.c:1414-1527).
 // This kernel computes the same rows all at once as a dense contraction.
 //
-// One CTA = one 128-token query tile of TWO q heads of the same GQA group (a
-// lone head when the group size is odd), so every K|V tile staged in shared
-// memory feeds both.  Data flow:
-//   * TMA warp: the two Q tiles through a 2-D tensor map (cp.async.bulk.tensor,
-//     128-byte swizzle, out-of-range rows zero-filled), then K|V tiles of 64
-//     keys straight from the paged cache with linear bulk copies — the page
-//     layout already is the swizzled operand image the tensor core reads;
-//   * two MMA warps (one issuing thread per head): S = Q.K^T as tcgen05.mma
-//     M128 N64 K16 x8 into TMEM (S is double-buffered; the scores of tile
-//     i+2 are issued as soon as the softmax has read tile i out of TMEM), and
-//     O += P.V as M128 N128 K16 x4 (V is the MN-major operand); completion is
-//     signalled with tcgen05.commit on mbarriers;
-//   * two softmax warpgroups (one per head), one thread per query row: the 64
-//     scores of the next tile are fetched from TMEM while the current tile is
-//     exponentiated; mask (causal / window), exponentiate against a running
-//     reference max, write P as F16 into shared memory in operand order.  The
-//     two heads' warps on one scheduler take turns on the special-function
-//     unit.  O stays in TMEM; it is rescaled only when the row max has grown
-//     by more than 2^8 (exact: the final division by l uses the same
-//     reference max), and read once at the end, normalised, transposed
-//     through shared memory and stored as whole F32 rows.
+// Work is cut into BLOCKS of 128 query rows of one q head.  A CTA always holds
+// two blocks that read the same K/V tiles: two q heads of one GQA group over
+// the same 128 tokens, or — for the odd head of a group — the same head over
+// two consecutive 128-token ranges.  CTAs are persistent (one per SM): they
+// draw work tiles, longest first, from a counter in global memory, and the
+// next tile's queries and first scores are in flight while the previous
+// tile's output leaves.
+//
+// Per CTA, per step of 128 keys:
+//   * producer warp: K and V tiles of 128 keys (two cache pages) come straight
+//     from the paged cache with linear bulk copies — the page layout already is
+//     the swizzled operand image the tensor core reads; Q tiles come through a
+//     2-D tensor map (cp.async.bulk.tensor, 128-byte swizzle, rows past the
+//     prompt zero-filled);
+//   * one MMA thread: S_b = Q_b.K^T as eight tcgen05.mma M128 N128 K16 into the
+//     block's 128 score columns of TMEM, and O_b += P_b.V as eight more with P
+//     read from TMEM (the A operand) and V as the MN-major B operand.  The two
+//     blocks alternate — the tensor core works on one block's tiles while the
+//     other block's scores are being exponentiated — so neither S nor P needs a
+//     second buffer: P overwrites the first 64 columns of its own S;
+//   * two softmax warpgroups (one per block, one thread per query row): fetch
+//     the 128 scores from TMEM, mask (causal / window), row maximum,
+//     exponentiate against a running reference maximum (a share of the
+//     exponentials runs as a polynomial on the FMA pipe, because the special-
+//     function unit is as loaded as the tensor core here), write P as F16 back
+//     into TMEM.  O stays in TMEM; it is rescaled only when the row maximum has
+//     grown by more than 2^8 (exact: the final division by l uses the same
+//     reference maximum), read once at the end, normalised, and stored by TMA
+//     through a small swizzled staging tile per warp.
 // Every wait has a time limit; on expiry the kernel records an error, still
 // frees its TMEM and returns.
 #include <cuda.h>
@@ -37,45 +45,79 @@
 namespace {
 
 constexpr int kHd = 128;
-constexpr int kBM = 128;                 // query rows per head per CTA
-constexpr int kBN = 64;                  // keys per tile = page tokens
-constexpr int kStages = 3;               // per ring (K and V tiles are staged separately)
+constexpr int kBM = 128;                 // query rows per block
+constexpr int kBN = 128;                 // keys per step = two cache pages
+constexpr int kStages = 2;               // per ring (K and V tiles are staged separately)
 constexpr int kGroupThreads = 128;       // one softmax warpgroup
-constexpr int kThreads = 2 * kGroupThreads + 96;     // + TMA warp + one MMA warp per head
+constexpr int kThreads = 2 * kGroupThreads + 64;     // + producer warp + MMA warp
 constexpr uint32_t kQHalfBytes = kBM * 128;      // 64 dims of 128 rows
-constexpr uint32_t kQBytes = 2 * kQHalfBytes;    // 32 KB per head
-constexpr uint32_t kKVBlock = kBN * kHd * 2;     // 16 KB: one K or V tile
-constexpr uint32_t kPBytes = kBM * kBN * 2;      // 16 KB
+constexpr uint32_t kQBytes = 2 * kQHalfBytes;    // 32 KB per block
+constexpr uint32_t kPageBlock = 64 * kHd * 2;    // 16 KB: K or V of one head in one page
+constexpr uint32_t kKVTile = 2 * kPageBlock;     // 32 KB: 128 keys
+constexpr uint32_t kOutStage = 32 * 32 * 4;      // 4 KB per warp: 32 rows x 32 F32 columns
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0;                   // S of (head h, tile parity b) at columns 64*(2h+b)
-constexpr uint32_t kTmemO = 256;                 // O of head h at columns 256 + 128*h
+constexpr uint32_t kTmemS = 0;                   // S (then P) of block b at columns 128*b
+constexpr uint32_t kTmemO = 256;                 // O of block b at columns 256 + 128*b
 constexpr float kRescaleLog2 = 8.0f;             // move the reference max when it is 2^8 behind
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kTileSlots = 4;                    // ring of published work tiles
+// Of every kPolyPeriod exponentials one is evaluated on the FMA pipe (0: none; else even).
+#ifndef WR_PREFILL_POLY_PERIOD
+#define WR_PREFILL_POLY_PERIOD 4
+#endif
+constexpr int kPolyPeriod = WR_PREFILL_POLY_PERIOD;
+
+// Development aid, off by default: built with -DWR_PREFILL_TIMELINE the kernel's CTA 0
+// writes clock64() stamps of its hand-offs into a device buffer (kTlRoles rows of
+// kTlEvents stamps: row 0/1 = softmax group of block 0/1, row 2 = MMA thread), which
+// wr_cuda_debug_prefill_timeline copies out.
+#ifdef WR_PREFILL_TIMELINE
+// Rows 3 (softmax group of block 0) and 4 (MMA warp) hold tile-level stamps as clock * 16 + tag.
+constexpr int kTlRoles = 5, kTlEvents = 512;
+#define TL_DECL uint32_t tl_n = 0, tl_m = 0; const bool tl_on = (blockIdx.x == 0) && p.tl != nullptr
+#define TL(role) do { if (tl_on && tl_n < kTlEvents) p.tl[(role) * kTlEvents + tl_n++] = clock64(); } while (0)
+#define TLT(role, tag) do { if (tl_on && tl_m < kTlEvents) p.tl[(role) * kTlEvents + tl_m++] = clock64() * 16 + (tag); } while (0)
+#else
+#define TL_DECL
+#define TL(role)
+#define TLT(role, tag)
+#endif
 
 struct prefill_params {
+#ifdef WR_PREFILL_TIMELINE
+    long long *tl;
+#endif
     const uint64_t *pages;      // page table of (session, layer)
-    float *out;                 // [n, n_q, hd] F32
+    const char *page_base;      // non-null: page t = page_base + t * page_bytes
+    uint64_t page_bytes;
     int *err;
-    uint32_t n, p0, n_q, n_kv, group, n_pairs, window, n_qtiles;
+    int *sched;                 // [0] next work tile, [1] CTAs that have left
+    uint32_t n, p0, n_q, n_kv, group, window, n_qtiles, n_tiles;
     float scale_log2;           // score scale * log2(e)
     long long wait_limit;       // SM clock cycles a device-side wait may last
 };
 
+// A published work tile: up to two blocks over the same KV head.
+struct tile_info {
+    uint32_t valid, nblk, kvh, pad;
+    uint32_t head[2], qt[2];
+};
+
 struct smem_layout {
-    alignas(1024) uint8_t q[2][kQBytes];                 // per head
-    alignas(1024) uint8_t k[kStages][kKVBlock];          // K ring (freed after the scores)
-    alignas(1024) uint8_t v[kStages][kKVBlock];          // V ring (freed after P.V)
-    alignas(1024) uint8_t p[2][2][kPBytes];              // [head][tile parity]
-    alignas(8) uint64_t bar_q;
-    uint64_t full_k[kStages];
-    uint64_t empty_k[kStages];
-    uint64_t full_v[kStages];
-    uint64_t empty_v[kStages];
-    uint64_t s_full[2][2];                               // [head][tile parity]
-    uint64_t s_free[2][2];                               // softmax has read S out of TMEM
-    uint64_t p_ready[2][2];
-    uint64_t pv_done[2][2];                              // P.V of the tile using P[parity] has completed
-    uint64_t xu_turn[4][2];                              // [scheduler][head]: that head's warp may exponentiate
+    alignas(1024) uint8_t q[2][kQBytes];                 // per block
+    alignas(1024) uint8_t k[kStages][kKVTile];           // [64-dim half][128 keys][128 B]
+    alignas(1024) uint8_t v[kStages][kKVTile];           // [page][64-dim half][64 keys][128 B]
+    alignas(1024) uint8_t ostage[8][kOutStage];          // per softmax warp
+    alignas(8) uint64_t q_full;
+    uint64_t q_free;
+    uint64_t k_full[kStages], k_free[kStages];
+    uint64_t v_full[kStages], v_free[kStages];
+    uint64_t s_full[2];                                  // per block: scores are in TMEM
+    uint64_t p_full[2];                                  // per block: P is in TMEM (one arrival per warp)
+    uint64_t o_done[2];                                  // per block: the tile's last P.V has completed
+    uint64_t o_free[2];                                  // per block: O has been read out (one arrival per warp)
+    uint64_t tile_ready[kTileSlots];
+    tile_info tile[kTileSlots];
     uint32_t tmem_base;
 };
 
@@ -95,14 +137,36 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t m, uint32_t n, bool b
 {
     return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate)
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+// D[tmem] (+)= A[smem] . B[smem]; descriptors as (low, high) words
+__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                        uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] . B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                        uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar)
@@ -142,11 +206,34 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float *v)
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// 16 consecutive 32-bit columns of this thread's TMEM lane: 32 F16 probabilities, two per column.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ float ex2_approx(float x)
 {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// 2^x on the FMA pipe: x = r + f with r the nearest integer, a degree-3
+// polynomial for 2^f on [-0.5, 0.5] (relative error 7.6e-5, well inside the
+// F16 rounding of P), r added to the exponent field.  x <= -126 gives ~1e-38.
+__device__ __forceinline__ float ex2_poly(float x)
+{
+    x = fmaxf(x, -126.0f);
+    const float t = x + 12582912.0f;                 // 1.5 * 2^23: the integer lands in the low mantissa bits
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(0.05516839f, f, 0.24260326f);
+    p = fmaf(p, f, 0.69326085f);
+    p = fmaf(p, f, 0.99992865f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 // Tiled 2-D tensor copy global -> shared (no multicast).  The inner coordinate
 // x is in elements; x * 2 bytes is a multiple of 16 for every caller.
@@ -159,7 +246,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
         ::"r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
-
 // Tiled 2-D tensor store shared -> global; rows and columns beyond the tensor's
 // extent are dropped by the hardware.  x * 4 bytes is a multiple of 16 for the caller.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src_smem)
@@ -168,10 +254,72 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int 
                  ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(src_smem))
                  : "memory");
 }
-__device__ __forceinline__ void tma_store_commit_and_wait_read()
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// ---- work tiles -------------------------------------------------------------
+//
+// Tiles are numbered longest first.  Query tiles are taken from the end of the
+// prompt in pairs (r1, r0 = r1 - 1); pair k contributes, in this order,
+//   n_kv tiles of the odd head of each group over (r0, r1)      [only if group is odd]
+//   n_kv * (group / 2) head-pair tiles over r1
+//   n_kv * (group / 2) head-pair tiles over r0                  [only if r0 >= 0]
+__host__ __device__ inline uint32_t tiles_per_qpair(uint32_t n_kv, uint32_t group)
 {
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    return n_kv * ((group & 1u) + 2u * (group / 2u));
+}
+__host__ __device__ inline uint32_t prefill_tile_count(uint32_t n_qtiles, uint32_t n_kv, uint32_t group)
+{
+    uint32_t n = (n_qtiles / 2u) * tiles_per_qpair(n_kv, group);
+    if (n_qtiles & 1u) n += n_kv * ((group & 1u) + group / 2u);      // the first query tile on its own
+    return n;
+}
+__device__ inline tile_info decode_tile(const prefill_params &p, uint32_t idx)
+{
+    tile_info t;
+    t.valid = 0; t.nblk = 0; t.kvh = 0; t.pad = 0;
+    t.head[0] = t.head[1] = 0; t.qt[0] = t.qt[1] = 0;
+    if (idx >= p.n_tiles) return t;
+    t.valid = 1;
+    const uint32_t per = tiles_per_qpair(p.n_kv, p.group), pairs = p.group / 2u, odd = p.group & 1u;
+    const uint32_t k = idx / per;                    // query-tile pair, counted from the end of the prompt
+    uint32_t r = idx % per;
+    const int r1 = (int)p.n_qtiles - 1 - 2 * (int)k, r0 = r1 - 1;
+    if (odd && r < p.n_kv) {                         // the odd head of group r over both query tiles
+        t.kvh = r;
+        t.head[0] = t.head[1] = r * p.group + p.group - 1;
+        if (r0 >= 0) { t.nblk = 2; t.qt[0] = (uint32_t)r0; t.qt[1] = (uint32_t)r1; }
+        else { t.nblk = 1; t.qt[0] = (uint32_t)r1; }
+        return t;
+    }
+    r -= odd * p.n_kv;
+    // (a lone first query tile has only the "r1" half of the list)
+    const uint32_t qt = (r < p.n_kv * pairs || r0 < 0) ? (uint32_t)r1 : (uint32_t)r0;
+    r %= p.n_kv * pairs;
+    t.kvh = r / pairs;
+    t.nblk = 2;
+    t.head[0] = t.kvh * p.group + 2u * (r % pairs);
+    t.head[1] = t.head[0] + 1;
+    t.qt[0] = t.qt[1] = qt;
+    return t;
+}
+
+// Key-step range [lo, hi) of a block, in steps of kBN keys.
+struct block_range {
+    uint32_t tok0, rows, key_end, lo, hi;
+};
+__device__ __forceinline__ block_range range_of(const prefill_params &p, uint32_t qt)
+{
+    block_range b;
+    b.tok0 = qt * kBM;
+    b.rows = min((uint32_t)kBM, p.n - b.tok0);
+    b.key_end = p.p0 + b.tok0 + b.rows;
+    uint32_t key_first = 0;
+    if (p.window > 0 && p.p0 + b.tok0 + 1 > p.window) key_first = p.p0 + b.tok0 + 1 - p.window;
+    b.lo = key_first / kBN;
+    b.hi = (b.key_end + kBN - 1) / kBN;
+    return b;
 }
 
 // ---- the kernel ------------------------------------------------------------
@@ -184,44 +332,22 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
     smem_layout &sm = *reinterpret_cast<smem_layout *>(smem_raw);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // Heaviest tiles first: the last query tile of the prompt has the most keys.
-    const uint32_t per_tile = p.n_kv * p.n_pairs;
-    const uint32_t qt = p.n_qtiles - 1 - blockIdx.x / per_tile;
-    const uint32_t kvh = (blockIdx.x % per_tile) / p.n_pairs;
-    const uint32_t pair = blockIdx.x % p.n_pairs;
-    const uint32_t head0 = kvh * p.group + 2 * pair;
-    const uint32_t n_heads = min(2u, p.group - 2 * pair);          // 1 for the odd head of a group
-    const uint32_t tok0 = qt * kBM;
-    const uint32_t rows_here = min((uint32_t)kBM, p.n - tok0);
-    // keys visible to this tile: [key_first, key_end)
-    const uint32_t key_end = p.p0 + tok0 + rows_here;
-    uint32_t key_first = 0;
-    if (p.window > 0 && p.p0 + tok0 + 1 > p.window) key_first = p.p0 + tok0 + 1 - p.window;
-    const uint32_t t_first = key_first / kBN;
-    const uint32_t n_kt = (key_end + kBN - 1) / kBN - t_first;     // >= 1
-
-    // The TMA warp sets the barriers up and starts the first copies (Q, and the first
-    // ring's worth of K and V tiles) at once: they fly while TMEM is being allocated
-    // and the other warps arrive at the barrier below.
     if (warp == 8 && lane == 0) {
-        mbar_init(&sm.bar_q, 1);
+        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.q_free, 1);
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(&sm.full_k[i], 1);
-            mbar_init(&sm.empty_k[i], n_heads);      // one tcgen05.commit per head
-            mbar_init(&sm.full_v[i], 1);
-            mbar_init(&sm.empty_v[i], n_heads);
+            mbar_init(&sm.k_full[i], 1);
+            mbar_init(&sm.k_free[i], 1);
+            mbar_init(&sm.v_full[i], 1);
+            mbar_init(&sm.v_free[i], 1);
         }
-        for (int h = 0; h < 2; ++h) {
-            mbar_init(&sm.s_full[h][0], 1);
-            mbar_init(&sm.s_full[h][1], 1);
-            mbar_init(&sm.s_free[h][0], kGroupThreads);
-            mbar_init(&sm.s_free[h][1], kGroupThreads);
-            mbar_init(&sm.p_ready[h][0], kGroupThreads);
-            mbar_init(&sm.p_ready[h][1], kGroupThreads);
-            mbar_init(&sm.pv_done[h][0], 1);
-            mbar_init(&sm.pv_done[h][1], 1);
-            for (int q = 0; q < 4; ++q) mbar_init(&sm.xu_turn[q][h], 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&sm.s_full[b], 1);
+            mbar_init(&sm.p_full[b], 4);
+            mbar_init(&sm.o_done[b], 1);
+            mbar_init(&sm.o_free[b], 4);
         }
+        for (int i = 0; i < kTileSlots; ++i) mbar_init(&sm.tile_ready[i], 1);
         fence_barrier_init();
     }
     if (warp == 0) {
@@ -229,300 +355,397 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                      ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // lane 0 of the TMA warp streams the K tiles, lane 1 the V tiles: separate rings,
-    // because a K tile is free again long before its V tile is.
-    auto issue_kv_tile = [&](uint32_t i) {
-        uint8_t (*ring)[kKVBlock] = lane == 0 ? sm.k : sm.v;
-        uint64_t *full = lane == 0 ? sm.full_k : sm.full_v;
-        const uint32_t st = i % kStages;
-        const char *src = (const char *)p.pages[t_first + i] + wr_block_off(kvh, lane, kHd);
-        mbar_expect_tx(&full[st], kKVBlock);
-        bulk_g2s(ring[st], src, kKVBlock, &full[st]);
-    };
-    if (warp == 8) {
-        __syncwarp();                                   // lane 1 uses barriers that lane 0 has just set up
-        if (lane == 0) {
-            mbar_expect_tx(&sm.bar_q, n_heads * kQBytes);
-            for (uint32_t h = 0; h < n_heads; ++h) {
-                tma_load_2d(sm.q[h], &q_map, (int)((head0 + h) * kHd), (int)tok0, &sm.bar_q);
-                tma_load_2d(sm.q[h] + kQHalfBytes, &q_map, (int)((head0 + h) * kHd + 64), (int)tok0,
-                            &sm.bar_q);
-            }
-        }
-        if (lane < 2)
-            for (uint32_t i = 0; i < min((uint32_t)kStages, n_kt); ++i) issue_kv_tile(i);
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
+    const long long limit = p.wait_limit;
+    const uint32_t n_pages_total = (p.p0 + p.n + 63u) / 64u;     // pages that hold rows of this prompt
+
+    auto page_ptr = [&](uint32_t t) -> const char * {
+        return p.page_base ? p.page_base + (uint64_t)t * p.page_bytes : (const char *)p.pages[t];
+    };
 
     if (warp == 8) {
-        // ------------------------------------------------------------ TMA warp
-        if (lane < 2) {
-            uint64_t *empty = lane == 0 ? sm.empty_k : sm.empty_v;
-            for (uint32_t i = kStages; i < n_kt; ++i) {
-                const uint32_t st = i % kStages;
-                if (!mbar_wait(&empty[st], ((i / kStages) - 1) & 1, p.wait_limit)) {
-                    atomicExch(p.err, 11);
-                    break;
-                }
-                issue_kv_tile(i);
-            }
-        }
-    } else if (warp >= 9) {
-        // ------------------------------------- MMA warps: one issuing thread per head
-        // (while one of them waits on a barrier the other keeps the tensor core fed)
-        const uint32_t h = warp - 9;
-        if (lane == 0 && h < n_heads) {
-            const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
-            const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
-            bool ok = mbar_wait(&sm.bar_q, 0, p.wait_limit);
-            // This one thread feeds the tensor core, so its instruction count
-            // per tile matters: descriptors are built once and an operand is
-            // selected by adding its byte offset (>>4) to the address field.
-            const uint64_t qd = umma_desc(smem_u32(sm.q[h]), 16, 1024);
-            const uint64_t k_desc0 = umma_desc(smem_u32(sm.k[0]), 16, 1024);
-            const uint64_t v_desc0 = umma_desc(smem_u32(sm.v[0]), 8192, 1024);
-            const uint64_t p_desc0 = umma_desc(smem_u32(sm.p[0][0]), 16, 1024);
-            auto issue_s = [&](uint32_t h, uint32_t i) {
-
-                const uint64_t kd = k_desc0 + (uint64_t)((i % kStages) * (kKVBlock >> 4));
-                const uint32_t d = tmem + kTmemS + 64 * (2 * h + (i & 1));
-#pragma unroll
-                for (int kk = 0; kk < kHd / 16; ++kk) {
-                    const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-                    umma_f16(d, qd + ((half * kQHalfBytes + off) >> 4),
-                             kd + ((half * (kBN * 128) + off) >> 4), idesc_s, kk > 0);
-                }
-                umma_commit(&sm.s_full[h][i & 1]);
-            };
-            // Scores run two tiles ahead of the softmax that consumes them (S is
-            // double-buffered in TMEM), so a softmax does not wait for its S.
-            for (uint32_t i = 0; ok && i < min(2u, n_kt); ++i) {
-                ok = mbar_wait(&sm.full_k[i], 0, p.wait_limit);
-                if (!ok) break;
-                tc_fence_after();
-                issue_s(h, i);
-                umma_commit(&sm.empty_k[i]);                     // this head is done with K tile i
-            }
-            for (uint32_t i = 0; ok && i < n_kt; ++i) {
-                if (i + 2 < n_kt) {
-                    // the softmax of tile i has its scores in registers: S[i&1] can take
-                    // tile i+2 while that softmax is still exponentiating
-                    ok = mbar_wait(&sm.s_free[h][i & 1], (i >> 1) & 1, p.wait_limit);
-                    if (ok) ok = mbar_wait(&sm.full_k[(i + 2) % kStages], ((i + 2) / kStages) & 1, p.wait_limit);
+        // ---------------------------------------------------------- producer warp
+        // lane 0: work tiles, Q and K tiles; lane 1: V tiles (a K tile is free
+        // again long before its V tile is, so the two rings run independently).
+        if (lane == 0) {
+            uint32_t tile = blockIdx.x, kcount = 0;
+            bool ok = true;
+            for (uint32_t it = 0; ok; ++it) {
+                const uint32_t slot = it % kTileSlots;
+                const tile_info ti = decode_tile(p, tile);
+                sm.tile[slot] = ti;
+                mbar_arrive(&sm.tile_ready[slot]);               // (release: the tile is visible to the waiters)
+                if (!ti.valid) break;
+                const uint32_t next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
+                if (it > 0) {                                    // the previous tile's scores have all been issued
+                    ok = mbar_wait(&sm.q_free, (it - 1) & 1, limit);
                     if (!ok) break;
-                    tc_fence_after();
-                    issue_s(h, i + 2);
-                    umma_commit(&sm.empty_k[(i + 2) % kStages]);
                 }
-                // softmax of (head h, tile i) has written P[i&1]
-                ok = mbar_wait(&sm.p_ready[h][i & 1], (i >> 1) & 1, p.wait_limit);
-                if (ok) ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1, p.wait_limit);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t vd = v_desc0 + (uint64_t)((i % kStages) * (kKVBlock >> 4));
-                const uint64_t pd = p_desc0 + (uint64_t)((2 * h + (i & 1)) * (kPBytes >> 4));
-                const uint32_t d = tmem + kTmemO + 128 * h;
-#pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk)
-                    umma_f16(d, pd + ((kk * 32) >> 4), vd + ((kk * 2048) >> 4), idesc_o, (i > 0) || (kk > 0));
-                umma_commit(&sm.pv_done[h][i & 1]);              // O_h holds tiles 0..i, P[i&1] is free
-                umma_commit(&sm.empty_v[i % kStages]);           // this head is done with V tile i
-            }
-            if (!ok) atomicExch(p.err, 12);
-        }
-    } else if (warp < 4 * n_heads) {
-        // ----------------------------- softmax warpgroup h: one thread per query row
-        const uint32_t h = warp >> 2;
-        const uint32_t row = tid & (kGroupThreads - 1);     // TMEM lane
-        const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
-        const uint32_t s_base = tmem + lane_base + kTmemS + 128 * h;
-        const uint32_t o_addr = tmem + lane_base + kTmemO + 128 * h;
-        const uint32_t qpos = p.p0 + tok0 + row;            // absolute position of this query
-        uint32_t lo_key = 0;
-        if (p.window > 0 && qpos + 1 > p.window) lo_key = qpos + 1 - p.window;
-        const float c2 = p.scale_log2;
-        float m_ref = WR_NEG_SENTINEL;                      // reference max, log2 domain
-        float l = 0.f;
-        const uint32_t quad = warp & 3u;                    // scheduler this warp and its twin of the other head share
-        const bool two = (n_heads == 2);
-        // The scores of the current tile live in s[]; the next tile's are fetched
-        // from TMEM while this tile is still being exponentiated.
-        float s[kBN];
-        bool ok = mbar_wait(&sm.s_full[h][0], 0, p.wait_limit);
-        if (ok) {
-            tc_fence_after();
-            tmem_ld32_nowait(s_base, s);
-            tmem_ld32_nowait(s_base + 32, s + 32);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(&sm.s_free[h][0]);                      // S[0] may take tile 2
-        }
-        for (uint32_t i = 0; ok && i < n_kt; ++i) {
-            const uint32_t key0 = (t_first + i) * kBN;
-            // tiles that no row's causal or window limit cuts through need no masking
-            const bool edge = (key0 + kBN - 1 > p.p0 + tok0) || (p.window > 0);
-            if (edge) {
-#pragma unroll
-                for (int j = 0; j < kBN; ++j) {
-                    const uint32_t key = key0 + j;
-                    if (key > qpos || key < lo_key) s[j] = WR_NEG_SENTINEL;
+                mbar_expect_tx(&sm.q_full, ti.nblk * kQBytes);
+                for (uint32_t b = 0; b < ti.nblk; ++b) {
+                    tma_load_2d(sm.q[b], &q_map, (int)(ti.head[b] * kHd), (int)(ti.qt[b] * kBM), &sm.q_full);
+                    tma_load_2d(sm.q[b] + kQHalfBytes, &q_map, (int)(ti.head[b] * kHd + 64), (int)(ti.qt[b] * kBM),
+                                &sm.q_full);
                 }
-            }
-            // four independent max chains instead of one 64-deep dependency
-            float mx[4] = {s[0], s[1], s[2], s[3]};
-#pragma unroll
-            for (int j = 4; j < kBN; j += 4) {
-                mx[0] = fmaxf(mx[0], s[j]);
-                mx[1] = fmaxf(mx[1], s[j + 1]);
-                mx[2] = fmaxf(mx[2], s[j + 2]);
-                mx[3] = fmaxf(mx[3], s[j + 3]);
-            }
-            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            // Move the reference max (and rescale O) only when it is far behind.
-            // The rescale uses warp-wide TMEM instructions, so the warp decides
-            // together; rows that do not need it multiply by one.
-            const float tm2 = tmax * c2;
-            const bool grow = (tmax > WR_NEG_SENTINEL) && (m_ref != WR_NEG_SENTINEL) && (tm2 > m_ref + kRescaleLog2);
-            if (tmax > WR_NEG_SENTINEL && m_ref == WR_NEG_SENTINEL) m_ref = tm2;
-            if (__any_sync(0xffffffffu, grow)) {
-                const float a = grow ? ex2_approx(m_ref - tm2) : 1.0f;
-                // O must hold every earlier tile (tile i-1 was the last one issued)
-                ok = mbar_wait(&sm.pv_done[h][(i - 1) & 1], ((i - 1) >> 1) & 1, p.wait_limit);
-                if (!ok) break;
-                tc_fence_after();
-#pragma unroll 1
-                for (int c = 0; c < kHd; c += 32) {
-                    float o[32];
-                    tmem_ld32_nowait(o_addr + c, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] *= a;
-                    tmem_st32(o_addr + c, o);
-                }
-                tmem_wait_st();
-                if (grow) {
-                    l *= a;
-                    m_ref = tm2;
-                }
-            }
-            // P = 2^(s*c2 - m_ref) as F16 in operand order: row `row`, 8 chunks of 8 keys;
-            // P[i&1] is free once the P.V of tile i-2 has read it
-            if (i >= 2) {
-                ok = mbar_wait(&sm.pv_done[h][i & 1], ((i >> 1) - 1) & 1, p.wait_limit);
-                if (!ok) break;
-            }
-            // The exponentials saturate the special-function unit, which this warp
-            // shares with the same-numbered warp of the other head: the two take
-            // turns, so that one's loads, max and hand-offs run under the other's
-            // exponentials instead of both queueing for the unit at once.
-            if (two && (h == 1 || i > 0)) {
-                ok = mbar_wait(&sm.xu_turn[quad][h], (h == 1 ? i : i - 1) & 1, p.wait_limit);
-                if (!ok) break;
-            }
-            uint8_t *prow = sm.p[h][i & 1] + row * 128;
-            // (no visible key yet for this row: every score is the sentinel and must give 0)
-            const float neg_m = (m_ref == WR_NEG_SENTINEL) ? 0.f : -m_ref;
-            float psum[4] = {0.f, 0.f, 0.f, 0.f};
-            auto exp_chunk = [&](int c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    // a masked score is -1e30: the fused multiply-add stays hugely negative, 2^x gives 0
-                    const float p0 = ex2_approx(fmaf(s[c * 8 + 2 * e], c2, neg_m));
-                    const float p1 = ex2_approx(fmaf(s[c * 8 + 2 * e + 1], c2, neg_m));
-                    psum[e] += p0 + p1;
-                    const __half2 hh = __floats2half2_rn(p0, p1);
-                    w[e] = *reinterpret_cast<const uint32_t *>(&hh);
-                }
-                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-            };
-            const bool more = i + 1 < n_kt;
-            const uint32_t s_next = s_base + 64 * ((i + 1) & 1);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) exp_chunk(c);
-            if (more) {
-                // columns 0..31 are spent: refill them with the next tile's (its scores
-                // were issued two tiles ahead, so this wait normally falls through)
-                ok = mbar_wait(&sm.s_full[h][(i + 1) & 1], ((i + 1) >> 1) & 1, p.wait_limit);
-                if (!ok) break;
-                tc_fence_after();
-                tmem_ld32_nowait(s_next, s);
-            }
-#pragma unroll
-            for (int c = 4; c < 7; ++c) exp_chunk(c);
-            if (two && lane == 0) mbar_arrive(&sm.xu_turn[quad][h ^ 1]);   // a little early: hides the hand-off
-            exp_chunk(7);
-            if (more) tmem_ld32_nowait(s_next + 32, s + 32);
-            l += (psum[0] + psum[1]) + (psum[2] + psum[3]);
-            if (i == n_kt - 1 && (key_end % kBN) != 0) {
-                // Cache rows past the last key were never written for this
-                // prompt (or belong to a rolled-back step): clear them in the
-                // staged V tile so that 0 * garbage cannot make a NaN (each head's
-                // group does it before releasing its own P.V; the writes are equal).
-                ok = mbar_wait(&sm.full_v[i % kStages], (i / kStages) & 1, p.wait_limit);
-                if (!ok) break;
-                if (row < kBN && key0 + row >= key_end) {
-                    uint8_t *vrow = sm.v[i % kStages] + row * 128;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        *reinterpret_cast<uint4 *>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
-                        *reinterpret_cast<uint4 *>(vrow + 8192 + c * 16) = make_uint4(0, 0, 0, 0);
+                const block_range r0 = range_of(p, ti.qt[0]), r1 = range_of(p, ti.qt[ti.nblk - 1]);
+                const uint32_t lo = min(r0.lo, r1.lo), hi = max(r0.hi, r1.hi);
+                for (uint32_t j = lo; j < hi && ok; ++j, ++kcount) {
+                    const uint32_t st = kcount % kStages;
+                    if (kcount >= kStages) {
+                        ok = mbar_wait(&sm.k_free[st], ((kcount / kStages) - 1) & 1, limit);
+                        if (!ok) break;
+                    }
+                    // [64-dim half][128 keys][128 B]: each page contributes 64 keys to each half
+                    const uint32_t n_pg = (2 * j + 1 < n_pages_total) ? 2u : 1u;
+                    mbar_expect_tx(&sm.k_full[st], n_pg * kPageBlock);
+                    for (uint32_t pg = 0; pg < n_pg; ++pg) {
+                        const char *src = page_ptr(2 * j + pg) + wr_block_off(ti.kvh, 0, kHd);
+                        bulk_g2s(sm.k[st] + pg * 8192, src, 8192, &sm.k_full[st]);
+                        bulk_g2s(sm.k[st] + kQHalfBytes + pg * 8192, src + 8192, 8192, &sm.k_full[st]);
                     }
                 }
+                tile = next_tile;
             }
-            fence_proxy_async();          // P (generic writes) is read by the tensor core
-            tc_fence_before();
-            mbar_arrive(&sm.p_ready[h][i & 1]);
-            if (more) {
-                tmem_wait_ld();
-                tc_fence_before();
-                mbar_arrive(&sm.s_free[h][(i + 1) & 1]);        // S[(i+1)&1] may take tile i+3
+            if (!ok) atomicExch(p.err, 11);
+        } else if (lane == 1) {
+            uint32_t vcount = 0;
+            bool ok = true;
+            for (uint32_t it = 0; ok; ++it) {
+                const uint32_t slot = it % kTileSlots;
+                ok = mbar_wait(&sm.tile_ready[slot], (it / kTileSlots) & 1, limit);
+                if (!ok) break;
+                const tile_info ti = sm.tile[slot];
+                if (!ti.valid) break;
+                const block_range r0 = range_of(p, ti.qt[0]), r1 = range_of(p, ti.qt[ti.nblk - 1]);
+                const uint32_t lo = min(r0.lo, r1.lo), hi = max(r0.hi, r1.hi);
+                for (uint32_t j = lo; j < hi && ok; ++j, ++vcount) {
+                    const uint32_t st = vcount % kStages;
+                    if (vcount >= kStages) {
+                        ok = mbar_wait(&sm.v_free[st], ((vcount / kStages) - 1) & 1, limit);
+                        if (!ok) break;
+                    }
+                    const uint32_t n_pg = (2 * j + 1 < n_pages_total) ? 2u : 1u;
+                    mbar_expect_tx(&sm.v_full[st], n_pg * kPageBlock);
+                    for (uint32_t pg = 0; pg < n_pg; ++pg)
+                        bulk_g2s(sm.v[st] + pg * kPageBlock, page_ptr(2 * j + pg) + wr_block_off(ti.kvh, 1, kHd),
+                                 kPageBlock, &sm.v_full[st]);
+                }
+            }
+            if (!ok) atomicExch(p.err, 14);
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------ MMA warp
+        // The whole warp runs this control flow; one elected lane issues the
+        // tensor-core instructions.  (Issued from a branch that only one lane
+        // takes, every operand has to be moved out of that lane's registers one
+        // instruction at a time, in competition with the softmax warps for issue
+        // slots: measured 100-220 clk per instruction against 64 this way.)
+        const bool lead = elect_one();
+        const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
+        const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
+        // descriptor words: the high word is fixed per operand kind, an operand is
+        // selected by adding its byte offset (>>4) to the address field of the low word
+        const uint64_t kmaj0 = umma_desc(0, 16, 1024), mnmaj0 = umma_desc(0, 8192, 1024);
+        const uint32_t kmaj_hi = (uint32_t)(kmaj0 >> 32), kmaj_lo = (uint32_t)kmaj0;
+        const uint32_t mnmaj_hi = (uint32_t)(mnmaj0 >> 32), mnmaj_lo = (uint32_t)mnmaj0;
+        const uint32_t q_lo0 = kmaj_lo | ((smem_u32(sm.q[0]) & 0x3FFFFu) >> 4);
+        const uint32_t k_lo0 = kmaj_lo | ((smem_u32(sm.k[0]) & 0x3FFFFu) >> 4);
+        const uint32_t v_lo0 = mnmaj_lo | ((smem_u32(sm.v[0]) & 0x3FFFFu) >> 4);
+        uint32_t kc = 0, vc = 0;                 // K / V tiles consumed so far
+        uint32_t p_uses0 = 0, p_uses1 = 0;       // P hand-offs seen per block
+        uint32_t o_uses0 = 0, o_uses1 = 0;       // work tiles finished per block
+        bool ok = true;
+        TL_DECL;
+        if (lane == 0) TLT(4, 0);                                // role started
+        // S_b = Q_b . K^T for the K tile in stage st
+        auto issue_s = [&](uint32_t b, uint32_t st) {
+            const uint32_t q_lo = q_lo0 + b * (kQBytes >> 4), k_lo = k_lo0 + st * (kKVTile >> 4);
+            const uint32_t d = tmem + kTmemS + 128 * b;
+            if (lead) {
+#pragma unroll
+                for (int kk = 0; kk < kHd / 16; ++kk) {
+                    const uint32_t off = ((kk >> 2) * kQHalfBytes + (kk & 3) * 32) >> 4;
+                    umma_ss(d, q_lo + off, kmaj_hi, k_lo + off, kmaj_hi, idesc_s, kk > 0);
+                }
+                umma_commit(&sm.s_full[b]);
+            }
+        };
+        // O_b (+)= P_b . V for the V tile in stage st, n_kk steps of 16 keys
+        auto issue_pv = [&](uint32_t b, uint32_t st, uint32_t n_kk, bool accumulate) {
+            const uint32_t v_lo = v_lo0 + st * (kKVTile >> 4);
+            const uint32_t d = tmem + kTmemO + 128 * b, a = tmem + kTmemS + 128 * b;
+            if (lead) {
+                if (n_kk == kBN / 16) {
+#pragma unroll
+                    for (int kk = 0; kk < kBN / 16; ++kk)
+                        umma_ts(d, a + 8 * kk, v_lo + (((kk >> 2) * kPageBlock + (kk & 3) * 2048) >> 4), mnmaj_hi,
+                                idesc_o, accumulate || kk > 0);
+                } else {
+                    for (uint32_t kk = 0; kk < n_kk; ++kk)
+                        umma_ts(d, a + 8 * kk, v_lo + (((kk >> 2) * kPageBlock + (kk & 3) * 2048) >> 4), mnmaj_hi,
+                                idesc_o, accumulate || kk > 0);
+                }
+            }
+        };
+        for (uint32_t it = 0; ok; ++it) {
+            const uint32_t slot = it % kTileSlots;
+            ok = mbar_wait(&sm.tile_ready[slot], (it / kTileSlots) & 1, limit);
+            if (!ok) break;
+            const tile_info ti = sm.tile[slot];
+            if (!ti.valid) break;
+            const block_range rg0 = range_of(p, ti.qt[0]), rg1 = range_of(p, ti.qt[ti.nblk - 1]);
+            const uint32_t lo = min(rg0.lo, rg1.lo), hi = max(rg0.hi, rg1.hi);
+            const bool two = ti.nblk > 1;
+            if (lane == 0) TLT(4, 1);                            // tile known
+
+            ok = mbar_wait(&sm.q_full, it & 1, limit);
+            if (lane == 0) TLT(4, 2);                            // Q landed
+            if (ok) ok = mbar_wait(&sm.k_full[kc % kStages], (kc / kStages) & 1, limit);
+            if (!ok) break;
+            if (lane == 0) TLT(4, 3);                            // first K landed
+            tc_fence_after();
+            if (lo >= rg0.lo && lo < rg0.hi) issue_s(0, kc % kStages);
+            if (two && lo >= rg1.lo && lo < rg1.hi) issue_s(1, kc % kStages);
+            if (lead) umma_commit(&sm.k_free[kc % kStages]);
+            ++kc;
+            if (lo + 1 == hi && lead) umma_commit(&sm.q_free);       // Q is no longer read
+            for (uint32_t j = lo; j < hi && ok; ++j) {
+                const bool more = j + 1 < hi;
+                const uint32_t vst = vc % kStages, kst = kc % kStages;
+                ok = mbar_wait(&sm.v_full[vst], (vc / kStages) & 1, limit);
+                if (ok && more) ok = mbar_wait(&sm.k_full[kst], (kc / kStages) & 1, limit);
+                if (!ok) break;
+                // one block: wait for its P, issue its P.V, then its next scores
+                auto step_block = [&](uint32_t b, const block_range &rg, uint32_t &p_uses, uint32_t &o_uses) -> bool {
+                    if (j >= rg.lo && j < rg.hi) {
+                        bool good = mbar_wait(&sm.p_full[b], p_uses & 1, limit);
+                        ++p_uses;
+                        // the first P.V of a tile overwrites O: the previous tile's rows must have left TMEM
+                        if (good && j == rg.lo && o_uses > 0) good = mbar_wait(&sm.o_free[b], (o_uses - 1) & 1, limit);
+                        if (!good) return false;
+                        if (lane == 0) TL(2);                    // P of block b seen
+                        tc_fence_after();
+                        const bool last = (j + 1 == rg.hi);
+                        // steps of 16 keys; the last tile stops at the block's last key
+                        const uint32_t n_kk = last ? (rg.key_end - j * kBN + 15u) / 16u : (uint32_t)(kBN / 16);
+                        issue_pv(b, vst, n_kk, j > rg.lo);
+                        if (last) {
+                            if (lead) umma_commit(&sm.o_done[b]);
+                            ++o_uses;
+                        }
+                    }
+                    if (lane == 0) TL(2);                        // P.V issued
+                    if (more && j + 1 >= rg.lo && j + 1 < rg.hi) issue_s(b, kst);    // (P_b of step j was consumed just above)
+                    if (lane == 0) TL(2);                        // next scores issued
+                    return true;
+                };
+                ok = step_block(0, rg0, p_uses0, o_uses0);
+                if (ok && two) ok = step_block(1, rg1, p_uses1, o_uses1);
+                if (!ok) break;
+                if (lead) umma_commit(&sm.v_free[vst]);
+                ++vc;
+                if (more) {
+                    if (lead) umma_commit(&sm.k_free[kst]);
+                    ++kc;
+                    if (j + 2 == hi && lead) umma_commit(&sm.q_free);
+                }
             }
         }
-        tmem_wait_ld();                   // (an early exit may leave a fetch in flight)
-        if (ok) {
-            // The last P.V completes after every earlier one (one issuing thread,
-            // in order); this group has already observed the previous phase of that
-            // barrier (tile n_kt-3), so the parity wait is one completion behind at most.
-            ok = mbar_wait(&sm.pv_done[h][(n_kt - 1) & 1], ((n_kt - 1) >> 1) & 1, p.wait_limit);
-            if (ok) {
+        if (!ok && lane == 0) atomicExch(p.err, 12);
+    } else {
+        // ----------------------------- softmax warpgroup b: one thread per query row
+        const uint32_t b = warp >> 2;
+        const uint32_t row = tid & (kGroupThreads - 1);     // TMEM lane
+        const uint32_t wq = warp & 3u;
+        const uint32_t lane_base = (wq * 32u) << 16;
+        const uint32_t s_addr = tmem + lane_base + kTmemS + 128 * b;
+        const uint32_t o_addr = tmem + lane_base + kTmemO + 128 * b;
+        const float c2 = p.scale_log2;
+        uint8_t *stage = sm.ostage[warp];
+        uint32_t s_uses = 0, o_uses = 0, vc = 0;
+        bool ok = true;
+        TL_DECL;
+#ifdef WR_PREFILL_TIMELINE
+        const bool tl_me = (lane == 0 && wq == 0);
+#define TLS() do { if (tl_me) TL(b); } while (0)
+#define TLST(tag) do { if (tl_me && b == 0) TLT(3, tag); } while (0)
+#else
+#define TLS()
+#define TLST(tag)
+#endif
+        TLST(0);                                             // role started
+        bool store_pending = false;                          // lane 0: a TMA store may still read the staging tile
+        for (uint32_t it = 0; ok; ++it) {
+            const uint32_t slot = it % kTileSlots;
+            ok = mbar_wait(&sm.tile_ready[slot], (it / kTileSlots) & 1, limit);
+            if (!ok) break;
+            const tile_info ti = sm.tile[slot];
+            if (!ti.valid) break;
+            const block_range rg0 = range_of(p, ti.qt[0]), rg1 = range_of(p, ti.qt[ti.nblk - 1]);
+            const uint32_t lo = min(rg0.lo, rg1.lo), hi = max(rg0.hi, rg1.hi);
+            if (b >= ti.nblk) {                              // a lone block: this group sits the tile out
+                vc += hi - lo;
+                continue;
+            }
+            const block_range me = (b == 0) ? rg0 : rg1;
+            TLST(1);                                         // tile known
+            const uint32_t qpos = p.p0 + me.tok0 + row;      // absolute position of this query
+            uint32_t lo_key = 0;
+            if (p.window > 0 && qpos + 1 > p.window) lo_key = qpos + 1 - p.window;
+            float m_ref = WR_NEG_SENTINEL;                   // reference max, log2 domain
+            float l = 0.f;
+            for (uint32_t j = me.lo; j < me.hi && ok; ++j) {
+                ok = mbar_wait(&sm.s_full[b], s_uses & 1, limit);
+                ++s_uses;
+                if (!ok) break;
+                TLS();                                           // 0: scores ready
                 tc_fence_after();
-                const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-                // O leaves TMEM one row per thread.  Each warp lays its 32 rows out in
-                // shared memory as four tiles of 32 rows x 32 columns (128-byte rows, the
-                // eight 16-byte chunks of a row XOR-swizzled with the row number, which is
-                // both conflict free for these row-wise writes and the layout a 128-byte
-                // swizzled tensor map expects) and hands them to the TMA engine, which
-                // writes them out and drops the rows beyond the prompt.  This head's Q and
-                // P tiles serve as the staging area: every MMA that read them has completed.
-                const uint32_t wq = warp & 3u;
-                uint8_t *stage = (wq < 2) ? sm.q[h] + wq * (kQBytes / 2) : sm.p[h][wq - 2];
-                float o[kHd];                                      // the whole row: one wait for four loads
+                float s[kBN];
 #pragma unroll
-                for (int c = 0; c < kHd; c += 32) tmem_ld32_nowait(o_addr + c, o + c);
+                for (int c = 0; c < kBN; c += 32) tmem_ld32_nowait(s_addr + c, s + c);
                 tmem_wait_ld();
+                TLS();                                           // 1: scores in registers
+                const uint32_t key0 = j * kBN;
+                // steps that no row's causal or window limit cuts through need no masking
+                const bool edge = (key0 + kBN - 1 > p.p0 + me.tok0) || (p.window > 0);
+                if (edge) {
 #pragma unroll
-                for (int c = 0; c < kHd; c += 32) {
-                    float4 *trow = reinterpret_cast<float4 *>(stage + (c / 32) * 4096 + lane * 128);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e)
-                        trow[e ^ (lane & 7)] = make_float4(o[c + 4 * e] * inv, o[c + 4 * e + 1] * inv,
-                                                            o[c + 4 * e + 2] * inv, o[c + 4 * e + 3] * inv);
+                    for (int i = 0; i < kBN; ++i) {
+                        const uint32_t key = key0 + i;
+                        if (key > qpos || key < lo_key) s[i] = WR_NEG_SENTINEL;
+                    }
                 }
-                fence_proxy_async();                               // generic writes -> TMA reads
-                __syncwarp();
-                if (lane == 0 && wq * 32u < rows_here) {
-                    const int y = (int)(tok0 + wq * 32u);
-                    const int x = (int)((head0 + h) * kHd);
+                float mx[8];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) tma_store_2d(&out_map, x + 32 * c, y, stage + c * 4096);
-                    tma_store_commit_and_wait_read();              // the staging area is read before the CTA ends
+                for (int i = 0; i < 8; ++i) mx[i] = s[i];
+#pragma unroll
+                for (int i = 8; i < kBN; i += 8)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) mx[e] = fmaxf(mx[e], s[i + e]);
+                const float tmax = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                         fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+                // Move the reference max (and rescale O) only when it is far behind.
+                // The rescale uses warp-wide TMEM instructions, so the warp decides
+                // together; rows that do not need it multiply by one.  O is quiet here:
+                // this step's scores were issued after the previous step's P.V, so that
+                // P.V has completed, and the next one waits for the P written below.
+                const float tm2 = tmax * c2;
+                const bool grow = (tmax > WR_NEG_SENTINEL) && (m_ref != WR_NEG_SENTINEL) && (tm2 > m_ref + kRescaleLog2);
+                if (tmax > WR_NEG_SENTINEL && m_ref == WR_NEG_SENTINEL) m_ref = tm2;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float a = grow ? ex2_approx(m_ref - tm2) : 1.0f;
+#pragma unroll 1
+                    for (int c = 0; c < kHd; c += 32) {
+                        float o[32];
+                        tmem_ld32_nowait(o_addr + c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] *= a;
+                        tmem_st32(o_addr + c, o);
+                    }
+                    if (grow) {
+                        l *= a;
+                        m_ref = tm2;
+                    }
+                }
+                // P = 2^(s*c2 - m_ref) as F16, two keys per TMEM column, over the first 64 columns of S
+                // (no visible key yet for this row: every score is the sentinel and must give 0)
+                const float neg_m = (m_ref == WR_NEG_SENTINEL) ? 0.f : -m_ref;
+                TLS();                                           // 2: maximum known
+                float psum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < kBN / 32; ++c) {
+                    uint32_t w[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        // a masked score is -1e30: the fused multiply-add stays hugely negative, 2^x gives 0
+                        const float x0 = fmaf(s[c * 32 + 2 * e], c2, neg_m);
+                        const float x1 = fmaf(s[c * 32 + 2 * e + 1], c2, neg_m);
+                        const float p0 = ex2_approx(x0);
+                        const bool poly = kPolyPeriod > 0 && (e % (kPolyPeriod > 1 ? kPolyPeriod / 2 : 1)) == 0;
+                        const float p1 = poly ? ex2_poly(x1) : ex2_approx(x1);
+                        psum[e & 3] += p0 + p1;
+                        const __half2 hh = __floats2half2_rn(p0, p1);
+                        w[e] = *reinterpret_cast<const uint32_t *>(&hh);
+                    }
+                    tmem_st16(s_addr + 16 * c, w);
+                }
+                l += (psum[0] + psum[1]) + (psum[2] + psum[3]);
+                TLS();                                           // 3: P stores issued
+                if (key0 + kBN > p.p0 + p.n) {
+                    // Cache rows past the prompt's last key were never written for it
+                    // (or belong to a rolled-back step): clear them in the staged V
+                    // tile so that 0 * garbage cannot make a NaN (both groups do it
+                    // before releasing their own P.V; the writes are equal).
+                    const uint32_t vst = (vc + (j - lo)) % kStages;
+                    ok = mbar_wait(&sm.v_full[vst], ((vc + (j - lo)) / kStages) & 1, limit);
+                    if (!ok) break;
+                    const uint32_t first_bad = p.p0 + p.n - key0;
+                    if (row >= first_bad) {
+                        uint8_t *vrow = sm.v[vst] + (row >> 6) * kPageBlock + (row & 63u) * 128;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            *reinterpret_cast<uint4 *>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
+                            *reinterpret_cast<uint4 *>(vrow + 8192 + c * 16) = make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                    fence_proxy_async();          // generic writes -> tensor-core reads
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.p_full[b]);
+                TLS();                                           // 4: P handed over
+            }
+            vc += hi - lo;
+            if (!ok) break;
+            TLST(2);                                         // last P handed over
+            // ---- the tile's last P.V has completed: O leaves TMEM, normalised
+            ok = mbar_wait(&sm.o_done[b], o_uses & 1, limit);
+            ++o_uses;
+            if (!ok) break;
+            TLST(3);                                         // O complete
+            tc_fence_after();
+            float o[kHd];
+#pragma unroll
+            for (int c = 0; c < kHd; c += 32) tmem_ld32_nowait(o_addr + c, o + c);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.o_free[b]);       // the next tile may overwrite O
+            TLST(4);                                         // O in registers
+            const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+            // Each warp hands its 32 rows to the TMA engine as four tiles of 32 rows x 32
+            // columns (128-byte rows, the eight 16-byte chunks of a row XOR-swizzled with
+            // the row number: conflict free for these row-wise writes and the layout a
+            // 128-byte-swizzled tensor map expects); rows beyond the prompt are dropped
+            // by the hardware.
+            const bool rows_live = wq * 32u < me.rows;
+            const int y = (int)(me.tok0 + wq * 32u);
+            const int x = (int)((b == 0 ? ti.head[0] : ti.head[1]) * kHd);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (lane == 0 && store_pending) tma_store_wait_read();
+                __syncwarp();
+                float4 *trow = reinterpret_cast<float4 *>(stage + lane * 128);
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    trow[e ^ (lane & 7)] = make_float4(o[32 * c + 4 * e] * inv, o[32 * c + 4 * e + 1] * inv,
+                                                        o[32 * c + 4 * e + 2] * inv, o[32 * c + 4 * e + 3] * inv);
+                fence_proxy_async();                           // generic writes -> TMA reads
+                __syncwarp();
+                if (lane == 0 && rows_live) {
+                    tma_store_2d(&out_map, x + 32 * c, y, stage);
+                    tma_store_commit();
+                    store_pending = true;
                 }
             }
+            TLST(5);                                         // stores issued
         }
+        if (lane == 0 && store_pending) tma_store_wait_all();   // the staging tile is read, the rows are written
         if (!ok) atomicExch(p.err, 13);
     }
 
@@ -531,6 +754,15 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
                      : "memory");
+    }
+    // The last CTA to leave rewinds the work counter for the next launch.
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+            p.sched[0] = 0;
+            p.sched[1] = 0;
+            __threadfence();
+        }
     }
 }
 
@@ -595,6 +827,10 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
         int rc = wr_ctx_reserve_stage(ctx, need, 0);
         if (rc != WR_CUDA_OK) return rc;
     }
+    if (!ctx->prefill_sched) {
+        WR_CUDA_TRY(cudaMalloc((void **)&ctx->prefill_sched, 2 * sizeof(int)));
+        WR_CUDA_TRY(cudaMemsetAsync(ctx->prefill_sched, 0, 2 * sizeof(int), ctx->stream));
+    }
     char *stage = (char *)ctx->stage_dev;
     size_t off = 0;
     __half *q16 = nullptr;
@@ -641,17 +877,26 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
 
     prefill_params p;
     p.pages = kv->d_pages + (size_t)layer * kv->n_pages;
-    p.out = dout;
+    p.page_base = kv->contig[layer] ? (const char *)kv->pages[(size_t)layer * kv->n_pages] : nullptr;
+    p.page_bytes = wr_page_bytes(kv->n_kv, kHd);
+#ifdef WR_PREFILL_TIMELINE
+    if (!ctx->debug_buf) {
+        WR_CUDA_TRY(cudaMalloc(&ctx->debug_buf, kTlRoles * kTlEvents * sizeof(long long)));
+    }
+    WR_CUDA_TRY(cudaMemsetAsync(ctx->debug_buf, 0, kTlRoles * kTlEvents * sizeof(long long), ctx->stream));
+    p.tl = (long long *)ctx->debug_buf;
+#endif
     p.err = ctx->dev_err;
+    p.sched = ctx->prefill_sched;
     p.wait_limit = ctx->wait_limit;
     p.n = n;
     p.p0 = p0;
     p.n_q = n_q_heads;
     p.n_kv = kv->n_kv;
     p.group = n_q_heads / kv->n_kv;
-    p.n_pairs = (p.group + 1) / 2;
     p.window = window;
     p.n_qtiles = (n + kBM - 1) / kBM;
+    p.n_tiles = prefill_tile_count(p.n_qtiles, p.n_kv, p.group);
     const float scale = (scale_override > 0.0f) ? scale_override : 1.0f / sqrtf((float)kHd);   // kernels.c:1457-1459
     p.scale_log2 = scale * kLog2e;
     if (!(ctx->attr_flags & 2u)) {
@@ -659,7 +904,7 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
                                          (int)sizeof(smem_layout)));
         ctx->attr_flags |= 2u;
     }
-    const uint32_t grid = p.n_qtiles * p.n_kv * p.n_pairs;
+    const uint32_t grid = std::min<uint32_t>(p.n_tiles, (uint32_t)ctx->sm_count);
     attn_prefill_hd128_kernel<<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, out_map, p);
     ctx->launches++;
     WR_CUDA_TRY(cudaGetLastError());
@@ -669,3 +914,16 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
     }
     return WR_CUDA_OK;
 }
+
+#ifdef WR_PREFILL_TIMELINE
+// Copies the last launch's stamps out: kTlRoles x kTlEvents int64 values (0 = unused).
+extern "C" int wr_cuda_debug_prefill_timeline(wr_cuda_ctx *ctx, long long *host_out, uint32_t n)
+{
+    if (!ctx || !host_out || !ctx->debug_buf) return WR_CUDA_ERR_INVAL;
+    std::lock_guard<std::mutex> g(ctx->lock);
+    WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    const size_t want = std::min<size_t>(n, (size_t)kTlRoles * kTlEvents) * sizeof(long long);
+    WR_CUDA_TRY(cudaMemcpy(host_out, ctx->debug_buf, want, cudaMemcpyDeviceToHost));
+    return WR_CUDA_OK;
+}
+#endif

@@ -72,6 +72,8 @@ extern "C" void wr_cuda_ctx_destroy(wr_cuda_ctx *ctx)
         for (void *slab : pool.slabs) (void)cudaFree(slab);
     if (ctx->ws) (void)cudaFree(ctx->ws);
     if (ctx->tickets) (void)cudaFree(ctx->tickets);
+    if (ctx->prefill_sched) (void)cudaFree(ctx->prefill_sched);
+    if (ctx->debug_buf) (void)cudaFree(ctx->debug_buf);
     if (ctx->dev_err) (void)cudaFree(ctx->dev_err);
     if (ctx->host_err) (void)cudaFreeHost(ctx->host_err);
     if (ctx->stage_dev) (void)cudaFree(ctx->stage_dev);
@@ -92,6 +94,8 @@ int wr_ctx_sync_checked(wr_cuda_ctx *ctx)
         // A kernel that gave up left its arrival tickets and work queue mid-count.
         if (ctx->tickets)
             WR_CUDA_TRY(cudaMemsetAsync(ctx->tickets, 0, ctx->ticket_count * sizeof(int), ctx->stream));
+        if (ctx->prefill_sched)
+            WR_CUDA_TRY(cudaMemsetAsync(ctx->prefill_sched, 0, 2 * sizeof(int), ctx->stream));
         WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
         return WR_CUDA_ERR_INTERNAL;
     }

@@ -74,6 +74,8 @@ struct wr_cuda_ctx {
     size_t ws_bytes = 0;
     int *tickets = nullptr;
     size_t ticket_count = 0;
+    int *prefill_sched = nullptr;    // prefill kernel: next work tile, CTAs that have left
+    void *debug_buf = nullptr;       // development builds only (kernel timelines)
     int *dev_err = nullptr;          // device-side error flag
     int *host_err = nullptr;         // pinned mirror
     // staging for WR_CUDA_MEM_HOST calls
