@@ -13,27 +13,30 @@
 // next tile's queries and first scores are in flight while the previous
 // tile's output leaves.
 //
-// Per CTA, per step of 128 keys:
-//   * producer warp: K and V tiles of 128 keys (two cache pages) come straight
-//     from the paged cache with linear bulk copies — the page layout already is
-//     the swizzled operand image the tensor core reads; Q tiles come through a
-//     2-D tensor map (cp.async.bulk.tensor, 128-byte swizzle, rows past the
-//     prompt zero-filled);
-//   * one MMA thread: S_b = Q_b.K^T as eight tcgen05.mma M128 N128 K16 into the
-//     block's 128 score columns of TMEM, and O_b += P_b.V as eight more with P
-//     read from TMEM (the A operand) and V as the MN-major B operand.  The two
-//     blocks alternate — the tensor core works on one block's tiles while the
-//     other block's scores are being exponentiated — so neither S nor P needs a
-//     second buffer: P overwrites the first 64 columns of its own S;
+// Per CTA, per step of 64 keys (one cache page):
+//   * producer warp: K and V tiles come straight from the paged cache with one
+//     linear 16 KB bulk copy each — the page layout already is the swizzled
+//     operand image the tensor core reads; Q tiles come through a 2-D tensor map
+//     (cp.async.bulk.tensor, 128-byte swizzle, rows past the prompt zero-filled);
+//   * MMA warp (the whole warp runs the control flow, one elected lane issues):
+//     S_b = Q_b.K^T as eight tcgen05.mma M128 N64 K16 into one of the block's two
+//     64-column score buffers in TMEM, and O_b += P_b.V as four M128 N128 K16
+//     with P read from TMEM (the A operand) and V as the MN-major B operand.
+//     Scores run two steps ahead of the softmax that consumes them, so a softmax
+//     group goes from one step to the next without waiting for the tensor core;
+//     P overwrites the first 32 columns of the score buffer it came from, and
+//     the scores of step j+2 are issued into that buffer right behind P.V of
+//     step j (the tensor core executes in issue order);
 //   * two softmax warpgroups (one per block, one thread per query row): fetch
-//     the 128 scores from TMEM, mask (causal / window), row maximum,
-//     exponentiate against a running reference maximum (a share of the
-//     exponentials runs as a polynomial on the FMA pipe, because the special-
-//     function unit is as loaded as the tensor core here), write P as F16 back
-//     into TMEM.  O stays in TMEM; it is rescaled only when the row maximum has
-//     grown by more than 2^8 (exact: the final division by l uses the same
-//     reference maximum), read once at the end, normalised, and stored by TMA
-//     through a small swizzled staging tile per warp.
+//     the 64 scores from TMEM (the next step's are fetched while this step's are
+//     exponentiated), mask (causal / window), row maximum, exponentiate against
+//     a running reference maximum (a share of the exponentials runs as a
+//     polynomial on the FMA pipe, because the special-function unit is as
+//     loaded as the tensor core here), write P as F16 back into TMEM.  O stays
+//     in TMEM; it is rescaled only when the row maximum has grown by more than
+//     2^8 (exact: the final division by l uses the same reference maximum),
+//     read once at the end, normalised, and stored by TMA through two small
+//     swizzled staging tiles per warp.
 // Every wait has a time limit; on expiry the kernel records an error, still
 // frees its TMEM and returns.
 #include <cuda.h>
@@ -46,17 +49,17 @@ namespace {
 
 constexpr int kHd = 128;
 constexpr int kBM = 128;                 // query rows per block
-constexpr int kBN = 128;                 // keys per step = two cache pages
-constexpr int kStages = 2;               // per ring (K and V tiles are staged separately)
+constexpr int kBN = 64;                  // keys per step = one cache page
+constexpr int kStages = 3;               // per ring (K and V tiles are staged separately)
 constexpr int kGroupThreads = 128;       // one softmax warpgroup
-constexpr int kThreads = 2 * kGroupThreads + 64;     // + producer warp + MMA warp
+constexpr int kThreads = 2 * kGroupThreads + 96;     // + producer warp + one MMA warp per block
 constexpr uint32_t kQHalfBytes = kBM * 128;      // 64 dims of 128 rows
 constexpr uint32_t kQBytes = 2 * kQHalfBytes;    // 32 KB per block
-constexpr uint32_t kPageBlock = 64 * kHd * 2;    // 16 KB: K or V of one head in one page
-constexpr uint32_t kKVTile = 2 * kPageBlock;     // 32 KB: 128 keys
-constexpr uint32_t kOutStage = 32 * 32 * 4;      // 4 KB per warp: 32 rows x 32 F32 columns
+constexpr uint32_t kKVTile = kBN * kHd * 2;      // 16 KB: K or V of one head in one page
+constexpr uint32_t kKHalfBytes = kBN * 128;      // 64 dims of 64 keys
+constexpr uint32_t kOutStage = 32 * 32 * 4;      // 4 KB: 32 rows x 32 F32 columns
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0;                   // S (then P) of block b at columns 128*b
+constexpr uint32_t kTmemS = 0;                   // S (then P) of block b, buffer x at columns 128*b + 64*x
 constexpr uint32_t kTmemO = 256;                 // O of block b at columns 256 + 128*b
 constexpr float kRescaleLog2 = 8.0f;             // move the reference max when it is 2^8 behind
 constexpr float kLog2e = 1.4426950408889634f;
@@ -66,6 +69,12 @@ constexpr int kTileSlots = 4;                    // ring of published work tiles
 #define WR_PREFILL_POLY_PERIOD 4
 #endif
 constexpr int kPolyPeriod = WR_PREFILL_POLY_PERIOD;
+// Block 1's softmax group starts each work tile this many clocks late, so that the two
+// blocks ask the tensor core for their next scores at different times (see the kernel).
+#ifndef WR_PREFILL_STAGGER
+#define WR_PREFILL_STAGGER 600
+#endif
+constexpr long long kStaggerClk = WR_PREFILL_STAGGER;
 
 // Development aid, off by default: built with -DWR_PREFILL_TIMELINE the kernel's CTA 0
 // writes clock64() stamps of its hand-offs into a device buffer (kTlRoles rows of
@@ -104,16 +113,17 @@ struct tile_info {
 };
 
 struct smem_layout {
-    alignas(1024) uint8_t q[2][kQBytes];                 // per block
-    alignas(1024) uint8_t k[kStages][kKVTile];           // [64-dim half][128 keys][128 B]
-    alignas(1024) uint8_t v[kStages][kKVTile];           // [page][64-dim half][64 keys][128 B]
-    alignas(1024) uint8_t ostage[8][kOutStage];          // per softmax warp
-    alignas(8) uint64_t q_full;
+    alignas(1024) uint8_t q[2][kQBytes];                 // per block: [64-dim half][128 rows][128 B]
+    alignas(1024) uint8_t k[kStages][kKVTile];           // [64-dim half][64 keys][128 B]
+    alignas(1024) uint8_t v[kStages][kKVTile];
+    alignas(1024) uint8_t ostage[8][2][kOutStage];       // per softmax warp, two tiles in flight
+    alignas(8) uint64_t q_full[2];                       // per block
     uint64_t q_free;
     uint64_t k_full[kStages], k_free[kStages];
     uint64_t v_full[kStages], v_free[kStages];
-    uint64_t s_full[2];                                  // per block: scores are in TMEM
+    uint64_t s_full[2][2];                               // [block][buffer]: scores are in TMEM
     uint64_t p_full[2];                                  // per block: P is in TMEM (one arrival per warp)
+    uint64_t pv_pen[2];                                  // per block: the tile's last-but-one P.V has completed
     uint64_t o_done[2];                                  // per block: the tile's last P.V has completed
     uint64_t o_free[2];                                  // per block: O has been read out (one arrival per warp)
     uint64_t tile_ready[kTileSlots];
@@ -255,7 +265,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int 
                  : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- work tiles -------------------------------------------------------------
@@ -333,17 +343,20 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (warp == 8 && lane == 0) {
-        mbar_init(&sm.q_full, 1);
-        mbar_init(&sm.q_free, 1);
+        mbar_init(&sm.q_full[0], 1);
+        mbar_init(&sm.q_full[1], 1);
+        mbar_init(&sm.q_free, 2);                        // one arrival per MMA warp
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sm.k_full[i], 1);
-            mbar_init(&sm.k_free[i], 1);
+            mbar_init(&sm.k_free[i], 2);
             mbar_init(&sm.v_full[i], 1);
-            mbar_init(&sm.v_free[i], 1);
+            mbar_init(&sm.v_free[i], 2);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&sm.s_full[b], 1);
+            mbar_init(&sm.s_full[b][0], 1);
+            mbar_init(&sm.s_full[b][1], 1);
             mbar_init(&sm.p_full[b], 4);
+            mbar_init(&sm.pv_pen[b], 1);
             mbar_init(&sm.o_done[b], 1);
             mbar_init(&sm.o_free[b], 4);
         }
@@ -360,10 +373,18 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
     const long long limit = p.wait_limit;
-    const uint32_t n_pages_total = (p.p0 + p.n + 63u) / 64u;     // pages that hold rows of this prompt
 
     auto page_ptr = [&](uint32_t t) -> const char * {
         return p.page_base ? p.page_base + (uint64_t)t * p.page_bytes : (const char *)p.pages[t];
+    };
+    // Work tile number `it` of this CTA: the first one is the CTA's own number (every
+    // role works it out for itself, nobody waits), later ones are published by the producer.
+    auto tile_of = [&](uint32_t it, bool &ok) -> tile_info {
+        if (it == 0) return decode_tile(p, blockIdx.x);
+        const uint32_t slot = it % kTileSlots;
+        ok = mbar_wait(&sm.tile_ready[slot], ((it - 1) / kTileSlots) & 1, limit);
+        if (!ok) return decode_tile(p, p.n_tiles);                   // (invalid)
+        return sm.tile[slot];
     };
 
     if (warp == 8) {
@@ -371,54 +392,49 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         // lane 0: work tiles, Q and K tiles; lane 1: V tiles (a K tile is free
         // again long before its V tile is, so the two rings run independently).
         if (lane == 0) {
-            uint32_t tile = blockIdx.x, kcount = 0;
+            uint32_t kcount = 0;
+            tile_info ti = decode_tile(p, blockIdx.x);
             bool ok = true;
-            for (uint32_t it = 0; ok; ++it) {
-                const uint32_t slot = it % kTileSlots;
-                const tile_info ti = decode_tile(p, tile);
-                sm.tile[slot] = ti;
-                mbar_arrive(&sm.tile_ready[slot]);               // (release: the tile is visible to the waiters)
-                if (!ti.valid) break;
+            for (uint32_t it = 0; ok && ti.valid; ++it) {
+                // the next tile's number is on its way while this tile's loads are issued
                 const uint32_t next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
                 if (it > 0) {                                    // the previous tile's scores have all been issued
                     ok = mbar_wait(&sm.q_free, (it - 1) & 1, limit);
                     if (!ok) break;
                 }
-                mbar_expect_tx(&sm.q_full, ti.nblk * kQBytes);
-                for (uint32_t b = 0; b < ti.nblk; ++b) {
-                    tma_load_2d(sm.q[b], &q_map, (int)(ti.head[b] * kHd), (int)(ti.qt[b] * kBM), &sm.q_full);
-                    tma_load_2d(sm.q[b] + kQHalfBytes, &q_map, (int)(ti.head[b] * kHd + 64), (int)(ti.qt[b] * kBM),
-                                &sm.q_full);
-                }
                 const block_range r0 = range_of(p, ti.qt[0]), r1 = range_of(p, ti.qt[ti.nblk - 1]);
                 const uint32_t lo = min(r0.lo, r1.lo), hi = max(r0.hi, r1.hi);
-                for (uint32_t j = lo; j < hi && ok; ++j, ++kcount) {
+                auto load_q = [&](uint32_t b, uint32_t head, uint32_t qt) {
+                    mbar_expect_tx(&sm.q_full[b], kQBytes);
+                    tma_load_2d(sm.q[b], &q_map, (int)(head * kHd), (int)(qt * kBM), &sm.q_full[b]);
+                    tma_load_2d(sm.q[b] + kQHalfBytes, &q_map, (int)(head * kHd + 64), (int)(qt * kBM), &sm.q_full[b]);
+                };
+                auto load_k = [&](uint32_t j) -> bool {
                     const uint32_t st = kcount % kStages;
-                    if (kcount >= kStages) {
-                        ok = mbar_wait(&sm.k_free[st], ((kcount / kStages) - 1) & 1, limit);
-                        if (!ok) break;
-                    }
-                    // [64-dim half][128 keys][128 B]: each page contributes 64 keys to each half
-                    const uint32_t n_pg = (2 * j + 1 < n_pages_total) ? 2u : 1u;
-                    mbar_expect_tx(&sm.k_full[st], n_pg * kPageBlock);
-                    for (uint32_t pg = 0; pg < n_pg; ++pg) {
-                        const char *src = page_ptr(2 * j + pg) + wr_block_off(ti.kvh, 0, kHd);
-                        bulk_g2s(sm.k[st] + pg * 8192, src, 8192, &sm.k_full[st]);
-                        bulk_g2s(sm.k[st] + kQHalfBytes + pg * 8192, src + 8192, 8192, &sm.k_full[st]);
-                    }
-                }
-                tile = next_tile;
+                    if (kcount >= kStages && !mbar_wait(&sm.k_free[st], ((kcount / kStages) - 1) & 1, limit)) return false;
+                    mbar_expect_tx(&sm.k_full[st], kKVTile);
+                    bulk_g2s(sm.k[st], page_ptr(j) + wr_block_off(ti.kvh, 0, kHd), kKVTile, &sm.k_full[st]);
+                    ++kcount;
+                    return true;
+                };
+                // what the first scores need goes first: Q of block 0, the first K tile, Q of block 1
+                load_q(0, ti.head[0], ti.qt[0]);
+                ok = load_k(lo);
+                if (ti.nblk > 1) load_q(1, ti.head[1], ti.qt[1]);
+                for (uint32_t j = lo + 1; j < hi && ok; ++j) ok = load_k(j);
+                if (!ok) break;
+                ti = decode_tile(p, next_tile);
+                const uint32_t slot = (it + 1) % kTileSlots;
+                sm.tile[slot] = ti;
+                mbar_arrive(&sm.tile_ready[slot]);               // (release: the tile is visible to the waiters)
             }
             if (!ok) atomicExch(p.err, 11);
         } else if (lane == 1) {
             uint32_t vcount = 0;
             bool ok = true;
             for (uint32_t it = 0; ok; ++it) {
-                const uint32_t slot = it % kTileSlots;
-                ok = mbar_wait(&sm.tile_ready[slot], (it / kTileSlots) & 1, limit);
-                if (!ok) break;
-                const tile_info ti = sm.tile[slot];
-                if (!ti.valid) break;
+                const tile_info ti = tile_of(it, ok);
+                if (!ok || !ti.valid) break;
                 const block_range r0 = range_of(p, ti.qt[0]), r1 = range_of(p, ti.qt[ti.nblk - 1]);
                 const uint32_t lo = min(r0.lo, r1.lo), hi = max(r0.hi, r1.hi);
                 for (uint32_t j = lo; j < hi && ok; ++j, ++vcount) {
@@ -427,22 +443,24 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                         ok = mbar_wait(&sm.v_free[st], ((vcount / kStages) - 1) & 1, limit);
                         if (!ok) break;
                     }
-                    const uint32_t n_pg = (2 * j + 1 < n_pages_total) ? 2u : 1u;
-                    mbar_expect_tx(&sm.v_full[st], n_pg * kPageBlock);
-                    for (uint32_t pg = 0; pg < n_pg; ++pg)
-                        bulk_g2s(sm.v[st] + pg * kPageBlock, page_ptr(2 * j + pg) + wr_block_off(ti.kvh, 1, kHd),
-                                 kPageBlock, &sm.v_full[st]);
+                    mbar_expect_tx(&sm.v_full[st], kKVTile);
+                    bulk_g2s(sm.v[st], page_ptr(j) + wr_block_off(ti.kvh, 1, kHd), kKVTile, &sm.v_full[st]);
                 }
             }
             if (!ok) atomicExch(p.err, 14);
         }
-    } else if (warp == 9) {
-        // ------------------------------------------------ MMA warp
+    } else if (warp >= 9) {
+        // ------------------------------------------------ MMA warps, one per block
         // The whole warp runs this control flow; one elected lane issues the
         // tensor-core instructions.  (Issued from a branch that only one lane
         // takes, every operand has to be moved out of that lane's registers one
         // instruction at a time, in competition with the softmax warps for issue
         // slots: measured 100-220 clk per instruction against 64 this way.)
+        // Each block has its own warp so that the two blocks' hand-offs are served
+        // independently: one block's P.V never waits for the other block's softmax.
+        // Both warps walk every step of every work tile, also the steps their block
+        // takes no part in, because a K or V stage is free when BOTH have let it go.
+        const uint32_t b = warp - 9;
         const bool lead = elect_one();
         const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
         const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
@@ -451,107 +469,121 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         const uint64_t kmaj0 = umma_desc(0, 16, 1024), mnmaj0 = umma_desc(0, 8192, 1024);
         const uint32_t kmaj_hi = (uint32_t)(kmaj0 >> 32), kmaj_lo = (uint32_t)kmaj0;
         const uint32_t mnmaj_hi = (uint32_t)(mnmaj0 >> 32), mnmaj_lo = (uint32_t)mnmaj0;
-        const uint32_t q_lo0 = kmaj_lo | ((smem_u32(sm.q[0]) & 0x3FFFFu) >> 4);
+        const uint32_t q_lo = (kmaj_lo | ((smem_u32(sm.q[0]) & 0x3FFFFu) >> 4)) + b * (kQBytes >> 4);
         const uint32_t k_lo0 = kmaj_lo | ((smem_u32(sm.k[0]) & 0x3FFFFu) >> 4);
         const uint32_t v_lo0 = mnmaj_lo | ((smem_u32(sm.v[0]) & 0x3FFFFu) >> 4);
-        uint32_t kc = 0, vc = 0;                 // K / V tiles consumed so far
-        uint32_t p_uses0 = 0, p_uses1 = 0;       // P hand-offs seen per block
-        uint32_t o_uses0 = 0, o_uses1 = 0;       // work tiles finished per block
+        const uint32_t s_tmem = tmem + kTmemS + 128 * b, o_tmem = tmem + kTmemO + 128 * b;
+        // ring positions advance by one per step; parity flips when a ring wraps
+        uint32_t k_st = 0, k_par = 0;            // K stage / parity of the next step to score
+        uint32_t v_st = 0, v_par = 0;            // V stage / parity of the next step to multiply
+        uint32_t seq = 0;                        // score tiles issued (buffer = seq & 1)
+        uint32_t p_uses = 0, o_uses = 0, q_uses = 0;   // P hand-offs, finished tiles, Q tiles of this block
         bool ok = true;
         TL_DECL;
-        if (lane == 0) TLT(4, 0);                                // role started
-        // S_b = Q_b . K^T for the K tile in stage st
-        auto issue_s = [&](uint32_t b, uint32_t st) {
-            const uint32_t q_lo = q_lo0 + b * (kQBytes >> 4), k_lo = k_lo0 + st * (kKVTile >> 4);
-            const uint32_t d = tmem + kTmemS + 128 * b;
-            if (lead) {
-#pragma unroll
-                for (int kk = 0; kk < kHd / 16; ++kk) {
-                    const uint32_t off = ((kk >> 2) * kQHalfBytes + (kk & 3) * 32) >> 4;
-                    umma_ss(d, q_lo + off, kmaj_hi, k_lo + off, kmaj_hi, idesc_s, kk > 0);
-                }
-                umma_commit(&sm.s_full[b]);
-            }
-        };
-        // O_b (+)= P_b . V for the V tile in stage st, n_kk steps of 16 keys
-        auto issue_pv = [&](uint32_t b, uint32_t st, uint32_t n_kk, bool accumulate) {
-            const uint32_t v_lo = v_lo0 + st * (kKVTile >> 4);
-            const uint32_t d = tmem + kTmemO + 128 * b, a = tmem + kTmemS + 128 * b;
-            if (lead) {
-                if (n_kk == kBN / 16) {
-#pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk)
-                        umma_ts(d, a + 8 * kk, v_lo + (((kk >> 2) * kPageBlock + (kk & 3) * 2048) >> 4), mnmaj_hi,
-                                idesc_o, accumulate || kk > 0);
-                } else {
-                    for (uint32_t kk = 0; kk < n_kk; ++kk)
-                        umma_ts(d, a + 8 * kk, v_lo + (((kk >> 2) * kPageBlock + (kk & 3) * 2048) >> 4), mnmaj_hi,
-                                idesc_o, accumulate || kk > 0);
-                }
-            }
-        };
+#ifdef WR_PREFILL_TIMELINE
+        const bool tl_mma = (lane == 0 && b == 0);
+#else
+        const bool tl_mma = false;
+#endif
+        (void)tl_mma;
+        if (tl_mma) TLT(4, 0);                                   // role started
         for (uint32_t it = 0; ok; ++it) {
-            const uint32_t slot = it % kTileSlots;
-            ok = mbar_wait(&sm.tile_ready[slot], (it / kTileSlots) & 1, limit);
-            if (!ok) break;
-            const tile_info ti = sm.tile[slot];
-            if (!ti.valid) break;
+            const tile_info ti = tile_of(it, ok);
+            if (!ok || !ti.valid) break;
             const block_range rg0 = range_of(p, ti.qt[0]), rg1 = range_of(p, ti.qt[ti.nblk - 1]);
             const uint32_t lo = min(rg0.lo, rg1.lo), hi = max(rg0.hi, rg1.hi);
-            const bool two = ti.nblk > 1;
-            if (lane == 0) TLT(4, 1);                            // tile known
-
-            ok = mbar_wait(&sm.q_full, it & 1, limit);
-            if (lane == 0) TLT(4, 2);                            // Q landed
-            if (ok) ok = mbar_wait(&sm.k_full[kc % kStages], (kc / kStages) & 1, limit);
+            const block_range me = (b == 0) ? rg0 : rg1;
+            const bool present = b < ti.nblk;
+            // steps this block takes part in (none when it is absent from the tile)
+            const uint32_t my_lo = present ? me.lo : hi, my_hi = present ? me.hi : hi;
+            if (tl_mma) TLT(4, 1);                               // tile known
+            bool q_seen = false;
+            // this block's scores of step jj from the K tile at the ring's head, then the tile is let go
+            // (the caller has seen the K tile land)
+            auto scores = [&](uint32_t jj) {
+                if (jj >= my_lo && jj < my_hi) {
+                    const uint32_t k_lo = k_lo0 + k_st * (kKVTile >> 4);
+                    const uint32_t x = seq & 1, d = s_tmem + 64 * x;
+                    if (lead) {
+#pragma unroll
+                        for (int kk = 0; kk < kHd / 16; ++kk) {
+                            const uint32_t qoff = ((kk >> 2) * kQHalfBytes + (kk & 3) * 32) >> 4;
+                            const uint32_t koff = ((kk >> 2) * kKHalfBytes + (kk & 3) * 32) >> 4;
+                            umma_ss(d, q_lo + qoff, kmaj_hi, k_lo + koff, kmaj_hi, idesc_s, kk > 0);
+                        }
+                        umma_commit(&sm.s_full[b][x]);
+                        umma_commit(&sm.k_free[k_st]);
+                        if (jj + 1 == hi) umma_commit(&sm.q_free);   // Q is no longer read
+                    }
+                    ++seq;
+                } else if (lead) {
+                    mbar_arrive(&sm.k_free[k_st]);
+                    if (jj + 1 == hi) mbar_arrive(&sm.q_free);
+                }
+                if (++k_st == kStages) { k_st = 0; k_par ^= 1; }
+            };
+            auto k_landed = [&]() -> bool { return mbar_wait(&sm.k_full[k_st], k_par, limit); };
+            auto q_landed = [&]() -> bool {
+                if (q_seen || !present) return true;
+                q_seen = true;
+                return mbar_wait(&sm.q_full[b], (q_uses++) & 1, limit);
+            };
+            // scores run two steps ahead of the softmax
+            ok = k_landed() && q_landed();
             if (!ok) break;
-            if (lane == 0) TLT(4, 3);                            // first K landed
             tc_fence_after();
-            if (lo >= rg0.lo && lo < rg0.hi) issue_s(0, kc % kStages);
-            if (two && lo >= rg1.lo && lo < rg1.hi) issue_s(1, kc % kStages);
-            if (lead) umma_commit(&sm.k_free[kc % kStages]);
-            ++kc;
-            if (lo + 1 == hi && lead) umma_commit(&sm.q_free);       // Q is no longer read
-            for (uint32_t j = lo; j < hi && ok; ++j) {
-                const bool more = j + 1 < hi;
-                const uint32_t vst = vc % kStages, kst = kc % kStages;
-                ok = mbar_wait(&sm.v_full[vst], (vc / kStages) & 1, limit);
-                if (ok && more) ok = mbar_wait(&sm.k_full[kst], (kc / kStages) & 1, limit);
+            scores(lo);
+            if (tl_mma) TLT(4, 3);                               // first scores issued
+            if (lo + 1 < hi) {
+                ok = k_landed();
                 if (!ok) break;
-                // one block: wait for its P, issue its P.V, then its next scores
-                auto step_block = [&](uint32_t b, const block_range &rg, uint32_t &p_uses, uint32_t &o_uses) -> bool {
-                    if (j >= rg.lo && j < rg.hi) {
-                        bool good = mbar_wait(&sm.p_full[b], p_uses & 1, limit);
-                        ++p_uses;
-                        // the first P.V of a tile overwrites O: the previous tile's rows must have left TMEM
-                        if (good && j == rg.lo && o_uses > 0) good = mbar_wait(&sm.o_free[b], (o_uses - 1) & 1, limit);
-                        if (!good) return false;
-                        if (lane == 0) TL(2);                    // P of block b seen
-                        tc_fence_after();
-                        const bool last = (j + 1 == rg.hi);
-                        // steps of 16 keys; the last tile stops at the block's last key
-                        const uint32_t n_kk = last ? (rg.key_end - j * kBN + 15u) / 16u : (uint32_t)(kBN / 16);
-                        issue_pv(b, vst, n_kk, j > rg.lo);
-                        if (last) {
-                            if (lead) umma_commit(&sm.o_done[b]);
-                            ++o_uses;
+                tc_fence_after();
+                scores(lo + 1);
+            }
+            for (uint32_t j = lo; j < hi && ok; ++j) {
+                // the operands of this step's P.V and of the scores two steps ahead landed long ago
+                ok = mbar_wait(&sm.v_full[v_st], v_par, limit);
+                if (ok && j + 2 < hi) ok = k_landed();
+                if (!ok) break;
+                if (j >= my_lo && j < my_hi) {
+                    // the first P.V of a tile overwrites O: the previous tile's rows must have left TMEM
+                    if (j == my_lo && o_uses > 0) ok = mbar_wait(&sm.o_free[b], (o_uses - 1) & 1, limit);
+                    const uint32_t x = p_uses & 1;               // P sits in the buffer its scores came from
+                    const bool last = (j + 1 == my_hi);
+                    // steps of 16 keys; the last tile stops at the block's last key
+                    const uint32_t n_kk = last ? (me.key_end - j * kBN + 15u) / 16u : (uint32_t)(kBN / 16);
+                    const uint32_t v_lo = v_lo0 + v_st * (kKVTile >> 4), a = s_tmem + 64 * x;
+                    const bool accumulate = j > my_lo;
+                    if (tl_mma) TL(2);                           // ready for P
+                    if (ok) ok = mbar_wait(&sm.p_full[b], p_uses & 1, limit);
+                    ++p_uses;
+                    if (!ok) break;
+                    if (tl_mma) TL(2);                           // P seen
+                    tc_fence_after();
+                    if (lead) {
+                        if (n_kk == kBN / 16) {
+#pragma unroll
+                            for (int kk = 0; kk < kBN / 16; ++kk)
+                                umma_ts(o_tmem, a + 8 * kk, v_lo + ((kk * 2048) >> 4), mnmaj_hi, idesc_o, accumulate || kk > 0);
+                        } else {
+                            for (uint32_t kk = 0; kk < n_kk; ++kk)
+                                umma_ts(o_tmem, a + 8 * kk, v_lo + ((kk * 2048) >> 4), mnmaj_hi, idesc_o, accumulate || kk > 0);
                         }
                     }
-                    if (lane == 0) TL(2);                        // P.V issued
-                    if (more && j + 1 >= rg.lo && j + 1 < rg.hi) issue_s(b, kst);    // (P_b of step j was consumed just above)
-                    if (lane == 0) TL(2);                        // next scores issued
-                    return true;
-                };
-                ok = step_block(0, rg0, p_uses0, o_uses0);
-                if (ok && two) ok = step_block(1, rg1, p_uses1, o_uses1);
-                if (!ok) break;
-                if (lead) umma_commit(&sm.v_free[vst]);
-                ++vc;
-                if (more) {
-                    if (lead) umma_commit(&sm.k_free[kst]);
-                    ++kc;
-                    if (j + 2 == hi && lead) umma_commit(&sm.q_free);
+                    // the scores of step j+2 go into the buffer whose P was consumed just above
+                    if (j + 2 < hi) scores(j + 2);
+                    if (tl_mma) TL(2);                           // P.V and next scores issued
+                    if (lead) {
+                        if (j + 2 == my_hi) umma_commit(&sm.pv_pen[b]);
+                        if (last) umma_commit(&sm.o_done[b]);
+                        umma_commit(&sm.v_free[v_st]);
+                    }
+                    if (last) ++o_uses;
+                } else {
+                    if (lead) mbar_arrive(&sm.v_free[v_st]);
+                    if (j + 2 < hi) scores(j + 2);
                 }
+                if (++v_st == kStages) { v_st = 0; v_par ^= 1; }
             }
         }
         if (!ok && lane == 0) atomicExch(p.err, 12);
@@ -564,8 +596,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         const uint32_t s_addr = tmem + lane_base + kTmemS + 128 * b;
         const uint32_t o_addr = tmem + lane_base + kTmemO + 128 * b;
         const float c2 = p.scale_log2;
-        uint8_t *stage = sm.ostage[warp];
-        uint32_t s_uses = 0, o_uses = 0, vc = 0;
+        uint32_t seq = 0, o_uses = 0, pen_uses = 0, vc = 0;  // seq: score tiles consumed (buffer = seq & 1)
         bool ok = true;
         TL_DECL;
 #ifdef WR_PREFILL_TIMELINE
@@ -577,13 +608,10 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
 #define TLST(tag)
 #endif
         TLST(0);                                             // role started
-        bool store_pending = false;                          // lane 0: a TMA store may still read the staging tile
+        uint32_t stores = 0;                                 // lane 0: staging tiles handed to TMA so far
         for (uint32_t it = 0; ok; ++it) {
-            const uint32_t slot = it % kTileSlots;
-            ok = mbar_wait(&sm.tile_ready[slot], (it / kTileSlots) & 1, limit);
-            if (!ok) break;
-            const tile_info ti = sm.tile[slot];
-            if (!ti.valid) break;
+            const tile_info ti = tile_of(it, ok);
+            if (!ok || !ti.valid) break;
             const block_range rg0 = range_of(p, ti.qt[0]), rg1 = range_of(p, ti.qt[ti.nblk - 1]);
             const uint32_t lo = min(rg0.lo, rg1.lo), hi = max(rg0.hi, rg1.hi);
             if (b >= ti.nblk) {                              // a lone block: this group sits the tile out
@@ -591,23 +619,34 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 continue;
             }
             const block_range me = (b == 0) ? rg0 : rg1;
+            const uint32_t pen_phase = pen_uses;             // this tile's phase of pv_pen (tiles of two steps or more)
+            if (me.hi - me.lo >= 2) ++pen_uses;
             TLST(1);                                         // tile known
             const uint32_t qpos = p.p0 + me.tok0 + row;      // absolute position of this query
             uint32_t lo_key = 0;
             if (p.window > 0 && qpos + 1 > p.window) lo_key = qpos + 1 - p.window;
             float m_ref = WR_NEG_SENTINEL;                   // reference max, log2 domain
             float l = 0.f;
-            for (uint32_t j = me.lo; j < me.hi && ok; ++j) {
-                ok = mbar_wait(&sm.s_full[b], s_uses & 1, limit);
-                ++s_uses;
-                if (!ok) break;
-                TLS();                                           // 0: scores ready
-                tc_fence_after();
-                float s[kBN];
-#pragma unroll
-                for (int c = 0; c < kBN; c += 32) tmem_ld32_nowait(s_addr + c, s + c);
-                tmem_wait_ld();
-                TLS();                                           // 1: scores in registers
+            // The scores of the current step live in s[]; the next step's are fetched
+            // from TMEM while this step is still being exponentiated.
+            float s[kBN];
+            ok = mbar_wait(&sm.s_full[b][seq & 1], (seq >> 1) & 1, limit);
+            if (!ok) break;
+            tc_fence_after();
+            tmem_ld32_nowait(s_addr + 64 * (seq & 1), s);
+            tmem_ld32_nowait(s_addr + 64 * (seq & 1) + 32, s + 32);
+            tmem_wait_ld();
+            if (b == 1 && kStaggerClk > 0) {
+                // Both groups hand their P over and need the scores of two steps ahead; asked
+                // for at the same moment, the second block's scores arrive late (the tensor core
+                // serves both requests back to back) and its softmax stalls every step.  Half a
+                // step apart, each request finds the tensor core free.
+                const long long t0 = clock64();
+                while (clock64() - t0 < kStaggerClk) { }
+            }
+            for (uint32_t j = me.lo; j < me.hi && ok; ++j, ++seq) {
+                TLS();                                           // 0: scores in registers
+                const uint32_t x = seq & 1;
                 const uint32_t key0 = j * kBN;
                 // steps that no row's causal or window limit cuts through need no masking
                 const bool edge = (key0 + kBN - 1 > p.p0 + me.tok0) || (p.window > 0);
@@ -618,25 +657,38 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                         if (key > qpos || key < lo_key) s[i] = WR_NEG_SENTINEL;
                     }
                 }
-                float mx[8];
+                float mx[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) mx[i] = s[i];
-#pragma unroll
-                for (int i = 8; i < kBN; i += 8)
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) mx[e] = fmaxf(mx[e], s[i + e]);
-                const float tmax = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                                         fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+                for (int i = 4; i < kBN; i += 4) {
+                    mx[0] = fmaxf(mx[0], s[i]);
+                    mx[1] = fmaxf(mx[1], s[i + 1]);
+                    mx[2] = fmaxf(mx[2], s[i + 2]);
+                    mx[3] = fmaxf(mx[3], s[i + 3]);
+                }
+                const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 // Move the reference max (and rescale O) only when it is far behind.
                 // The rescale uses warp-wide TMEM instructions, so the warp decides
-                // together; rows that do not need it multiply by one.  O is quiet here:
-                // this step's scores were issued after the previous step's P.V, so that
-                // P.V has completed, and the next one waits for the P written below.
+                // together; rows that do not need it multiply by one.  O must hold
+                // every earlier step: the last P.V issued is that of step j-1, and the
+                // scores of step j+1 were issued right behind it — once those have
+                // arrived, it has completed (the tensor core executes in issue order).
                 const float tm2 = tmax * c2;
                 const bool grow = (tmax > WR_NEG_SENTINEL) && (m_ref != WR_NEG_SENTINEL) && (tm2 > m_ref + kRescaleLog2);
                 if (tmax > WR_NEG_SENTINEL && m_ref == WR_NEG_SENTINEL) m_ref = tm2;
+                const bool more = j + 1 < me.hi;
+                bool next_seen = false;
                 if (__any_sync(0xffffffffu, grow)) {
                     const float a = grow ? ex2_approx(m_ref - tm2) : 1.0f;
+                    if (more) {
+                        ok = mbar_wait(&sm.s_full[b][x ^ 1], ((seq + 1) >> 1) & 1, limit);
+                        next_seen = true;
+                    } else {
+                        // last step of the block: nothing was issued behind P.V of step j-1,
+                        // the MMA warp signals its completion on its own
+                        ok = mbar_wait(&sm.pv_pen[b], pen_phase & 1, limit);
+                    }
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < kHd; c += 32) {
                         float o[32];
@@ -651,11 +703,13 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                         m_ref = tm2;
                     }
                 }
-                // P = 2^(s*c2 - m_ref) as F16, two keys per TMEM column, over the first 64 columns of S
-                // (no visible key yet for this row: every score is the sentinel and must give 0)
+                TLS();                                           // 1: maximum known
+                // P = 2^(s*c2 - m_ref) as F16, two keys per TMEM column, over the first 32 columns of
+                // the score buffer (no visible key yet for this row: every score is the sentinel, gives 0)
                 const float neg_m = (m_ref == WR_NEG_SENTINEL) ? 0.f : -m_ref;
-                TLS();                                           // 2: maximum known
                 float psum[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t p_addr = s_addr + 64 * x;
+                const uint32_t s_next = s_addr + 64 * (x ^ 1);
 #pragma unroll
                 for (int c = 0; c < kBN / 32; ++c) {
                     uint32_t w[16];
@@ -671,21 +725,34 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                         const __half2 hh = __floats2half2_rn(p0, p1);
                         w[e] = *reinterpret_cast<const uint32_t *>(&hh);
                     }
-                    tmem_st16(s_addr + 16 * c, w);
+                    tmem_st16(p_addr + 16 * c, w);
                 }
+                if (more) {
+                    // the scores are spent: refill them with the next step's (issued a whole
+                    // step ago, so this wait normally falls through)
+                    if (!next_seen) {
+                        ok = mbar_wait(&sm.s_full[b][x ^ 1], ((seq + 1) >> 1) & 1, limit);
+                        tc_fence_after();
+                    }
+                    if (ok) {
+                        tmem_ld32_nowait(s_next, s);
+                        tmem_ld32_nowait(s_next + 32, s + 32);
+                    }
+                }
+                if (!ok) break;
                 l += (psum[0] + psum[1]) + (psum[2] + psum[3]);
-                TLS();                                           // 3: P stores issued
+                TLS();                                           // 2: P stores issued
                 if (key0 + kBN > p.p0 + p.n) {
                     // Cache rows past the prompt's last key were never written for it
                     // (or belong to a rolled-back step): clear them in the staged V
                     // tile so that 0 * garbage cannot make a NaN (both groups do it
                     // before releasing their own P.V; the writes are equal).
-                    const uint32_t vst = (vc + (j - lo)) % kStages;
-                    ok = mbar_wait(&sm.v_full[vst], ((vc + (j - lo)) / kStages) & 1, limit);
+                    const uint32_t vn = vc + (j - lo), vst = vn % kStages;
+                    ok = mbar_wait(&sm.v_full[vst], (vn / kStages) & 1, limit);
                     if (!ok) break;
                     const uint32_t first_bad = p.p0 + p.n - key0;
-                    if (row >= first_bad) {
-                        uint8_t *vrow = sm.v[vst] + (row >> 6) * kPageBlock + (row & 63u) * 128;
+                    if (row < kBN && row >= first_bad) {
+                        uint8_t *vrow = sm.v[vst] + row * 128;
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
                             *reinterpret_cast<uint4 *>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
@@ -698,8 +765,10 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm.p_full[b]);
-                TLS();                                           // 4: P handed over
+                TLS();                                           // 3: P handed over
+                if (more) tmem_wait_ld();
             }
+            tmem_wait_ld();                                  // (an early exit may leave a fetch in flight)
             vc += hi - lo;
             if (!ok) break;
             TLST(2);                                         // last P handed over
@@ -722,30 +791,36 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             // columns (128-byte rows, the eight 16-byte chunks of a row XOR-swizzled with
             // the row number: conflict free for these row-wise writes and the layout a
             // 128-byte-swizzled tensor map expects); rows beyond the prompt are dropped
-            // by the hardware.
+            // by the hardware.  Two staging tiles are filled and handed over together.
             const bool rows_live = wq * 32u < me.rows;
             const int y = (int)(me.tok0 + wq * 32u);
-            const int x = (int)((b == 0 ? ti.head[0] : ti.head[1]) * kHd);
+            const int x0 = (int)((b == 0 ? ti.head[0] : ti.head[1]) * kHd);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (lane == 0 && store_pending) tma_store_wait_read();
+            for (int c2 = 0; c2 < 2; ++c2) {
+                // (the two staging tiles were handed to TMA as one group: wait for its reads)
+                if (lane == 0 && stores > 0) tma_store_wait_read0();
                 __syncwarp();
-                float4 *trow = reinterpret_cast<float4 *>(stage + lane * 128);
 #pragma unroll
-                for (int e = 0; e < 8; ++e)
-                    trow[e ^ (lane & 7)] = make_float4(o[32 * c + 4 * e] * inv, o[32 * c + 4 * e + 1] * inv,
-                                                        o[32 * c + 4 * e + 2] * inv, o[32 * c + 4 * e + 3] * inv);
+                for (int h = 0; h < 2; ++h) {
+                    const int c = 2 * c2 + h;
+                    float4 *trow = reinterpret_cast<float4 *>(sm.ostage[warp][h] + lane * 128);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        trow[e ^ (lane & 7)] = make_float4(o[32 * c + 4 * e] * inv, o[32 * c + 4 * e + 1] * inv,
+                                                            o[32 * c + 4 * e + 2] * inv, o[32 * c + 4 * e + 3] * inv);
+                }
                 fence_proxy_async();                           // generic writes -> TMA reads
                 __syncwarp();
                 if (lane == 0 && rows_live) {
-                    tma_store_2d(&out_map, x + 32 * c, y, stage);
+                    tma_store_2d(&out_map, x0 + 64 * c2, y, sm.ostage[warp][0]);
+                    tma_store_2d(&out_map, x0 + 64 * c2 + 32, y, sm.ostage[warp][1]);
                     tma_store_commit();
-                    store_pending = true;
+                    ++stores;
                 }
             }
             TLST(5);                                         // stores issued
         }
-        if (lane == 0 && store_pending) tma_store_wait_all();   // the staging tile is read, the rows are written
+        if (lane == 0 && stores > 0) tma_store_wait_all();   // the staging tiles are read, the rows are written
         if (!ok) atomicExch(p.err, 13);
     }
 
