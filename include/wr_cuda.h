@@ -95,6 +95,9 @@ int  wr_cuda_ctx_set_attn_max_seq(wr_cuda_ctx *ctx, uint32_t max_seq);
  * :589-592).  Default WR_CUDA_WAIT_LIMIT_DEFAULT, about two seconds. */
 #define WR_CUDA_WAIT_LIMIT_DEFAULT 4000000000LL
 int  wr_cuda_ctx_set_wait_limit(wr_cuda_ctx *ctx, int64_t cycles);
+/* The error word of the last give-up reported (0: none yet): a small number
+ * naming the wait that ran out, for a log line next to WR_CUDA_ERR_INTERNAL. */
+int  wr_cuda_ctx_last_device_error(wr_cuda_ctx *ctx);
 
 /* Page-locked host memory for a caller's row buffers (Q / K / V / attention
  * rows): with such buffers the WR_CUDA_MEM_HOST calls need no staging copy —

@@ -30,6 +30,7 @@ _STATUS = {
 EXPORTS = [
     "wr_cuda_device_check", "wr_cuda_ctx_create", "wr_cuda_ctx_destroy", "wr_cuda_ctx_sync",
     "wr_cuda_ctx_stream", "wr_cuda_ctx_set_attn_max_seq", "wr_cuda_ctx_set_wait_limit",
+    "wr_cuda_ctx_last_device_error",
     "wr_cuda_ctx_launch_count", "wr_cuda_host_alloc", "wr_cuda_host_free",
     "wr_cuda_kv_create", "wr_cuda_kv_destroy", "wr_cuda_kv_max_ctx", "wr_cuda_kv_write_rows",
     "wr_cuda_kv_read_rows", "wr_cuda_kv_append", "wr_cuda_attn_decode", "wr_cuda_attn_prefill",
@@ -73,6 +74,7 @@ def load_library():
         "wr_cuda_ctx_stream": (vp, [vp]),
         "wr_cuda_ctx_set_attn_max_seq": (i32, [vp, u32]),
         "wr_cuda_ctx_set_wait_limit": (i32, [vp, C.c_int64]),
+        "wr_cuda_ctx_last_device_error": (i32, [vp]),
         "wr_cuda_ctx_launch_count": (C.c_uint64, [vp]),
         "wr_cuda_host_alloc": (i32, [vp, C.c_uint64, C.POINTER(vp)]),
         "wr_cuda_host_free": (None, [vp, vp]),
@@ -176,6 +178,11 @@ class Context:
 
     def set_attn_max_seq(self, n: int):
         _check(self._lib.wr_cuda_ctx_set_attn_max_seq(self._h, n), "wr_cuda_ctx_set_attn_max_seq")
+
+    @property
+    def last_device_error(self) -> int:
+        """Error word of the last device-side give-up that was reported (0: none)."""
+        return int(self._lib.wr_cuda_ctx_last_device_error(self._h))
 
     def set_wait_limit(self, cycles: int):
         """SM clock cycles after which a device-side wait gives up (default about 2 s)."""

@@ -64,7 +64,7 @@ constexpr uint32_t kTmemO = 256;                 // O of block b at columns 256 
 constexpr float kRescaleLog2 = 8.0f;             // move the reference max when it is 2^8 behind
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kTileSlots = 4;                    // ring of published work tiles
-// Of every kPolyPeriod exponentials one is evaluated on the FMA pipe (0: none; else even).
+// Of every kPolyPeriod pairs of exponentials one pair is evaluated on the FMA pipe (0: none).
 #ifndef WR_PREFILL_POLY_PERIOD
 #define WR_PREFILL_POLY_PERIOD 4
 #endif
@@ -86,10 +86,13 @@ constexpr int kTlRoles = 5, kTlEvents = 512;
 #define TL_DECL uint32_t tl_n = 0, tl_m = 0; const bool tl_on = (blockIdx.x == 0) && p.tl != nullptr
 #define TL(role) do { if (tl_on && tl_n < kTlEvents) p.tl[(role) * kTlEvents + tl_n++] = clock64(); } while (0)
 #define TLT(role, tag) do { if (tl_on && tl_m < kTlEvents) p.tl[(role) * kTlEvents + tl_m++] = clock64() * 16 + (tag); } while (0)
+// where a role was when one of its waits ran out: four values at the end of its row
+#define TLFAIL(role, a, b, c, d) do { if (p.tl) { long long *r = p.tl + (role) * kTlEvents + kTlEvents - 4; r[0] = (a); r[1] = (b); r[2] = (c); r[3] = (d); } } while (0)
 #else
 #define TL_DECL
 #define TL(role)
 #define TLT(role, tag)
+#define TLFAIL(role, a, b, c, d)
 #endif
 
 struct prefill_params {
@@ -129,6 +132,7 @@ struct smem_layout {
     uint64_t tile_ready[kTileSlots];
     tile_info tile[kTileSlots];
     uint32_t tmem_base;
+    int pipe_lock;                                       // held by the MMA warp that is issuing a step's instructions
 };
 
 // ---- tcgen05 / TMA wrappers ------------------------------------------------
@@ -232,6 +236,42 @@ __device__ __forceinline__ float ex2_approx(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two F32 values in one 64-bit register, for the packed FMA-pipe instructions
+// (one issue slot for two elements: the softmax warps are issue-bound).
+__device__ __forceinline__ uint64_t pack2(float a, float b)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &a, float &b)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // 2^x on the FMA pipe: x = r + f with r the nearest integer, a degree-3
 // polynomial for 2^f on [-0.5, 0.5] (relative error 7.6e-5, well inside the
 // F16 rounding of P), r added to the exponent field.  x <= -126 gives ~1e-38.
@@ -244,6 +284,24 @@ __device__ __forceinline__ float ex2_poly(float x)
     p = fmaf(p, f, 0.69326085f);
     p = fmaf(p, f, 0.99992865f);
     return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+// The same for a packed pair.
+__device__ __forceinline__ void ex2_poly2(uint64_t x2, float &p0, float &p1)
+{
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x2 = pack2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t magic = pack2(12582912.0f, 12582912.0f);
+    const uint64_t t2 = add2(x2, magic);
+    const uint64_t f2 = sub2(x2, sub2(t2, magic));
+    uint64_t q2 = fma2(pack2(0.05516839f, 0.05516839f), f2, pack2(0.24260326f, 0.24260326f));
+    q2 = fma2(q2, f2, pack2(0.69326085f, 0.69326085f));
+    q2 = fma2(q2, f2, pack2(0.99992865f, 0.99992865f));
+    float q0, q1, t0, t1;
+    unpack2(q2, q0, q1);
+    unpack2(t2, t0, t1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
 }
 // Tiled 2-D tensor copy global -> shared (no multicast).  The inner coordinate
 // x is in elements; x * 2 bytes is a multiple of 16 for every caller.
@@ -361,6 +419,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             mbar_init(&sm.o_free[b], 4);
         }
         for (int i = 0; i < kTileSlots; ++i) mbar_init(&sm.tile_ready[i], 1);
+        sm.pipe_lock = 0;
         fence_barrier_init();
     }
     if (warp == 0) {
@@ -396,8 +455,6 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             tile_info ti = decode_tile(p, blockIdx.x);
             bool ok = true;
             for (uint32_t it = 0; ok && ti.valid; ++it) {
-                // the next tile's number is on its way while this tile's loads are issued
-                const uint32_t next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
                 if (it > 0) {                                    // the previous tile's scores have all been issued
                     ok = mbar_wait(&sm.q_free, (it - 1) & 1, limit);
                     if (!ok) break;
@@ -421,14 +478,27 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 load_q(0, ti.head[0], ti.qt[0]);
                 ok = load_k(lo);
                 if (ti.nblk > 1) load_q(1, ti.head[1], ti.qt[1]);
-                for (uint32_t j = lo + 1; j < hi && ok; ++j) ok = load_k(j);
+                // The next tile is claimed late — when this tile's last K tiles are being
+                // requested, a few steps before its end — so that the tiles still unclaimed
+                // go to the CTAs that really finish first; claimed at the start, every CTA
+                // would hold its second tile before it had done any work.
+                uint32_t next_tile = 0;
+                bool claimed = false;
+                for (uint32_t j = lo + 1; j < hi && ok; ++j) {
+                    if (!claimed && j + 2 >= hi) {
+                        next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
+                        claimed = true;
+                    }
+                    ok = load_k(j);
+                }
                 if (!ok) break;
+                if (!claimed) next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
                 ti = decode_tile(p, next_tile);
                 const uint32_t slot = (it + 1) % kTileSlots;
                 sm.tile[slot] = ti;
                 mbar_arrive(&sm.tile_ready[slot]);               // (release: the tile is visible to the waiters)
             }
-            if (!ok) atomicExch(p.err, 11);
+            if (!ok) atomicCAS(p.err, 0, 11);
         } else if (lane == 1) {
             uint32_t vcount = 0;
             bool ok = true;
@@ -447,7 +517,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                     bulk_g2s(sm.v[st], page_ptr(j) + wr_block_off(ti.kvh, 1, kHd), kKVTile, &sm.v_full[st]);
                 }
             }
-            if (!ok) atomicExch(p.err, 14);
+            if (!ok) atomicCAS(p.err, 0, 14);
         }
     } else if (warp >= 9) {
         // ------------------------------------------------ MMA warps, one per block
@@ -504,13 +574,14 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 if (jj >= my_lo && jj < my_hi) {
                     const uint32_t k_lo = k_lo0 + k_st * (kKVTile >> 4);
                     const uint32_t x = seq & 1, d = s_tmem + 64 * x;
-                    if (lead) {
+                    // (operands are worked out by the whole warp; only the instruction itself is predicated)
 #pragma unroll
-                        for (int kk = 0; kk < kHd / 16; ++kk) {
-                            const uint32_t qoff = ((kk >> 2) * kQHalfBytes + (kk & 3) * 32) >> 4;
-                            const uint32_t koff = ((kk >> 2) * kKHalfBytes + (kk & 3) * 32) >> 4;
-                            umma_ss(d, q_lo + qoff, kmaj_hi, k_lo + koff, kmaj_hi, idesc_s, kk > 0);
-                        }
+                    for (int kk = 0; kk < kHd / 16; ++kk) {
+                        const uint32_t qoff = ((kk >> 2) * kQHalfBytes + (kk & 3) * 32) >> 4;
+                        const uint32_t koff = ((kk >> 2) * kKHalfBytes + (kk & 3) * 32) >> 4;
+                        if (lead) umma_ss(d, q_lo + qoff, kmaj_hi, k_lo + koff, kmaj_hi, idesc_s, kk > 0);
+                    }
+                    if (lead) {
                         umma_commit(&sm.s_full[b][x]);
                         umma_commit(&sm.k_free[k_st]);
                         if (jj + 1 == hi) umma_commit(&sm.q_free);   // Q is no longer read
@@ -542,7 +613,9 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             }
             for (uint32_t j = lo; j < hi && ok; ++j) {
                 // the operands of this step's P.V and of the scores two steps ahead landed long ago
+                if (tl_mma) TL(2);                               // loop top
                 ok = mbar_wait(&sm.v_full[v_st], v_par, limit);
+                if (tl_mma) TL(2);                               // V seen
                 if (ok && j + 2 < hi) ok = k_landed();
                 if (!ok) break;
                 if (j >= my_lo && j < my_hi) {
@@ -559,26 +632,44 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                     ++p_uses;
                     if (!ok) break;
                     if (tl_mma) TL(2);                           // P seen
-                    tc_fence_after();
+                    // One block's step goes to the tensor core as a whole.  With the two
+                    // warps' instructions interleaved, both blocks would get their next scores
+                    // late and at the same moment, and would ask again at the same moment for
+                    // ever; served one after the other, the blocks settle half a step apart and
+                    // each finds the tensor core free.
                     if (lead) {
-                        if (n_kk == kBN / 16) {
-#pragma unroll
-                            for (int kk = 0; kk < kBN / 16; ++kk)
-                                umma_ts(o_tmem, a + 8 * kk, v_lo + ((kk * 2048) >> 4), mnmaj_hi, idesc_o, accumulate || kk > 0);
-                        } else {
-                            for (uint32_t kk = 0; kk < n_kk; ++kk)
-                                umma_ts(o_tmem, a + 8 * kk, v_lo + ((kk * 2048) >> 4), mnmaj_hi, idesc_o, accumulate || kk > 0);
+                        const long long t0 = clock64();
+                        while (atomicCAS(&sm.pipe_lock, 0, 1) != 0) {
+                            if (clock64() - t0 > limit) {
+                                ok = false;
+                                break;
+                            }
                         }
                     }
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    if (tl_mma) TL(2);                           // lock held
+                    tc_fence_after();
+                    if (n_kk == kBN / 16) {
+#pragma unroll
+                        for (int kk = 0; kk < kBN / 16; ++kk)
+                            if (lead) umma_ts(o_tmem, a + 8 * kk, v_lo + ((kk * 2048) >> 4), mnmaj_hi, idesc_o, accumulate || kk > 0);
+                    } else {
+                        for (uint32_t kk = 0; kk < n_kk; ++kk)
+                            if (lead) umma_ts(o_tmem, a + 8 * kk, v_lo + ((kk * 2048) >> 4), mnmaj_hi, idesc_o, accumulate || kk > 0);
+                    }
+                    if (tl_mma) TL(2);                           // P.V issued
                     // the scores of step j+2 go into the buffer whose P was consumed just above
                     if (j + 2 < hi) scores(j + 2);
-                    if (tl_mma) TL(2);                           // P.V and next scores issued
+                    if (tl_mma) TL(2);                           // next scores issued and committed
+                    if (lead) atomicExch(&sm.pipe_lock, 0);
                     if (lead) {
                         if (j + 2 == my_hi) umma_commit(&sm.pv_pen[b]);
                         if (last) umma_commit(&sm.o_done[b]);
                         umma_commit(&sm.v_free[v_st]);
                     }
                     if (last) ++o_uses;
+                    if (tl_mma) TL(2);                           // step closed
                 } else {
                     if (lead) mbar_arrive(&sm.v_free[v_st]);
                     if (j + 2 < hi) scores(j + 2);
@@ -586,7 +677,8 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 if (++v_st == kStages) { v_st = 0; v_par ^= 1; }
             }
         }
-        if (!ok && lane == 0) atomicExch(p.err, 12);
+        if (!ok && lane == 0 && blockIdx.x == 0) TLFAIL(2 + 2 * b, 2000 + seq, p_uses, o_uses, k_st * 100 + v_st * 10 + k_par * 2 + v_par);
+        if (!ok && lane == 0) atomicCAS(p.err, 0, 12);
     } else {
         // ----------------------------- softmax warpgroup b: one thread per query row
         const uint32_t b = warp >> 2;
@@ -657,14 +749,17 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                         if (key > qpos || key < lo_key) s[i] = WR_NEG_SENTINEL;
                     }
                 }
-                float mx[4] = {s[0], s[1], s[2], s[3]};
+                // four independent chains of three-input maxima
+                float mx[4] = {max3(s[0], s[1], s[2]), max3(s[3], s[4], s[5]), max3(s[6], s[7], s[8]), max3(s[9], s[10], s[11])};
 #pragma unroll
-                for (int i = 4; i < kBN; i += 4) {
-                    mx[0] = fmaxf(mx[0], s[i]);
-                    mx[1] = fmaxf(mx[1], s[i + 1]);
-                    mx[2] = fmaxf(mx[2], s[i + 2]);
-                    mx[3] = fmaxf(mx[3], s[i + 3]);
+                for (int i = 12; i + 8 <= kBN; i += 8) {
+                    mx[0] = max3(mx[0], s[i], s[i + 1]);
+                    mx[1] = max3(mx[1], s[i + 2], s[i + 3]);
+                    mx[2] = max3(mx[2], s[i + 4], s[i + 5]);
+                    mx[3] = max3(mx[3], s[i + 6], s[i + 7]);
                 }
+                mx[0] = max3(mx[0], s[kBN - 4], s[kBN - 3]);
+                mx[1] = max3(mx[1], s[kBN - 2], s[kBN - 1]);
                 const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 // Move the reference max (and rescale O) only when it is far behind.
                 // The rescale uses warp-wide TMEM instructions, so the warp decides
@@ -707,29 +802,39 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 // P = 2^(s*c2 - m_ref) as F16, two keys per TMEM column, over the first 32 columns of
                 // the score buffer (no visible key yet for this row: every score is the sentinel, gives 0)
                 const float neg_m = (m_ref == WR_NEG_SENTINEL) ? 0.f : -m_ref;
-                float psum[4] = {0.f, 0.f, 0.f, 0.f};
                 const uint32_t p_addr = s_addr + 64 * x;
                 const uint32_t s_next = s_addr + 64 * (x ^ 1);
+                const uint64_t c2_2 = pack2(c2, c2), neg_m2 = pack2(neg_m, neg_m);
+                uint64_t psum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
                 for (int c = 0; c < kBN / 32; ++c) {
                     uint32_t w[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
                         // a masked score is -1e30: the fused multiply-add stays hugely negative, 2^x gives 0
-                        const float x0 = fmaf(s[c * 32 + 2 * e], c2, neg_m);
-                        const float x1 = fmaf(s[c * 32 + 2 * e + 1], c2, neg_m);
-                        const float p0 = ex2_approx(x0);
-                        const bool poly = kPolyPeriod > 0 && (e % (kPolyPeriod > 1 ? kPolyPeriod / 2 : 1)) == 0;
-                        const float p1 = poly ? ex2_poly(x1) : ex2_approx(x1);
-                        psum[e & 3] += p0 + p1;
+                        const uint64_t x2 = fma2(pack2(s[c * 32 + 2 * e], s[c * 32 + 2 * e + 1]), c2_2, neg_m2);
+                        float p0, p1;
+                        // one pair in kPolyPeriod goes to the FMA pipe, the others to the special-function unit
+                        if (kPolyPeriod > 0 && (e % (kPolyPeriod > 0 ? kPolyPeriod : 1)) == kPolyPeriod - 1) {
+                            ex2_poly2(x2, p0, p1);
+                        } else {
+                            float x0, x1;
+                            unpack2(x2, x0, x1);
+                            p0 = ex2_approx(x0);
+                            p1 = ex2_approx(x1);
+                        }
+                        psum2[e & 1] = add2(psum2[e & 1], pack2(p0, p1));
                         const __half2 hh = __floats2half2_rn(p0, p1);
                         w[e] = *reinterpret_cast<const uint32_t *>(&hh);
                     }
                     tmem_st16(p_addr + 16 * c, w);
                 }
+                // The scores are spent: refill them with the next step's (issued a whole step
+                // ago).  This wait stays in front of the hand-over of P on purpose: it keeps a
+                // warp from running a step ahead of its group, which the per-warp arrivals on
+                // p_full rely on.
                 if (more) {
-                    // the scores are spent: refill them with the next step's (issued a whole
-                    // step ago, so this wait normally falls through)
+                    TLS();                                       // 2: exponentials done
                     if (!next_seen) {
                         ok = mbar_wait(&sm.s_full[b][x ^ 1], ((seq + 1) >> 1) & 1, limit);
                         tc_fence_after();
@@ -740,8 +845,13 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                     }
                 }
                 if (!ok) break;
-                l += (psum[0] + psum[1]) + (psum[2] + psum[3]);
-                TLS();                                           // 2: P stores issued
+                {
+                    float pa, pb, pc, pd;
+                    unpack2(psum2[0], pa, pb);
+                    unpack2(psum2[1], pc, pd);
+                    l += (pa + pb) + (pc + pd);
+                }
+                TLS();                                           // 3: next scores seen
                 if (key0 + kBN > p.p0 + p.n) {
                     // Cache rows past the prompt's last key were never written for it
                     // (or belong to a rolled-back step): clear them in the staged V
@@ -765,7 +875,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm.p_full[b]);
-                TLS();                                           // 3: P handed over
+                TLS();                                           // 4: P handed over
                 if (more) tmem_wait_ld();
             }
             tmem_wait_ld();                                  // (an early exit may leave a fetch in flight)
@@ -821,7 +931,8 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             TLST(5);                                         // stores issued
         }
         if (lane == 0 && stores > 0) tma_store_wait_all();   // the staging tiles are read, the rows are written
-        if (!ok) atomicExch(p.err, 13);
+        if (!ok && lane == 0 && wq == 0 && blockIdx.x == 0) TLFAIL(b, 1000 + seq, o_uses, vc, pen_uses);
+        if (!ok) atomicCAS(p.err, 0, 13);
     }
 
     tc_fence_before();

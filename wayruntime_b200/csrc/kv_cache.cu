@@ -89,6 +89,7 @@ int wr_ctx_sync_checked(wr_cuda_ctx *ctx)
                                 ctx->stream));
     WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     if (*ctx->host_err != 0) {
+        ctx->last_err = *ctx->host_err;
         *ctx->host_err = 0;
         WR_CUDA_TRY(cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
         // A kernel that gave up left its arrival tickets and work queue mid-count.
@@ -108,6 +109,13 @@ extern "C" int wr_cuda_ctx_sync(wr_cuda_ctx *ctx)
     std::lock_guard<std::mutex> g(ctx->lock);
     WR_CUDA_TRY(cudaSetDevice(ctx->device));
     return wr_ctx_sync_checked(ctx);
+}
+
+extern "C" int wr_cuda_ctx_last_device_error(wr_cuda_ctx *ctx)
+{
+    if (!ctx) return 0;
+    std::lock_guard<std::mutex> g(ctx->lock);
+    return ctx->last_err;
 }
 
 extern "C" int wr_cuda_ctx_set_wait_limit(wr_cuda_ctx *ctx, int64_t cycles)

@@ -78,6 +78,7 @@ struct wr_cuda_ctx {
     void *debug_buf = nullptr;       // development builds only (kernel timelines)
     int *dev_err = nullptr;          // device-side error flag
     int *host_err = nullptr;         // pinned mirror
+    int last_err = 0;                // the last non-zero error word read back (which wait gave up)
     // staging for WR_CUDA_MEM_HOST calls
     void *stage_dev = nullptr;
     size_t stage_dev_bytes = 0;
@@ -187,6 +188,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, long l
         if (first) t0 = clock64();
         else if (clock64() - t0 > limit) return false;
     }
+}
+// One non-blocking look at a barrier phase.
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
 }
 __device__ __forceinline__ void fence_barrier_init()
 {
