@@ -13,30 +13,30 @@
 // next tile's queries and first scores are in flight while the previous
 // tile's output leaves.
 //
-// Per CTA, per step of 64 keys (one cache page):
-//   * producer warp: K and V tiles come straight from the paged cache with one
-//     linear 16 KB bulk copy each — the page layout already is the swizzled
-//     operand image the tensor core reads; Q tiles come through a 2-D tensor map
+// Per CTA, per step of 128 keys (two cache pages):
+//   * producer warp: K and V tiles come straight from the paged cache with
+//     linear bulk copies — the page layout already is the swizzled operand image
+//     the tensor core reads; Q tiles come through a 2-D tensor map
 //     (cp.async.bulk.tensor, 128-byte swizzle, rows past the prompt zero-filled);
-//   * MMA warp (the whole warp runs the control flow, one elected lane issues):
-//     S_b = Q_b.K^T as eight tcgen05.mma M128 N64 K16 into one of the block's two
-//     64-column score buffers in TMEM, and O_b += P_b.V as four M128 N128 K16
-//     with P read from TMEM (the A operand) and V as the MN-major B operand.
-//     Scores run two steps ahead of the softmax that consumes them, so a softmax
-//     group goes from one step to the next without waiting for the tensor core;
-//     P overwrites the first 32 columns of the score buffer it came from, and
-//     the scores of step j+2 are issued into that buffer right behind P.V of
-//     step j (the tensor core executes in issue order);
+//   * MMA warp (the whole warp runs the control flow and works the operands
+//     out, one elected lane issues): S_b = Q_b.K^T as eight tcgen05.mma M128 N128
+//     K16 into the block's 128 score columns of TMEM, and O_b += P_b.V as eight
+//     more with P read from TMEM (the A operand) and V as the MN-major B operand.
+//     The two blocks alternate — the tensor core works on one block's tiles
+//     while the other block's scores are being exponentiated — so neither S nor
+//     P needs a second buffer: P overwrites the first 64 columns of its own S,
+//     and the next scores are issued right behind the P.V that consumed it (the
+//     tensor core executes in issue order);
 //   * two softmax warpgroups (one per block, one thread per query row): fetch
-//     the 64 scores from TMEM (the next step's are fetched while this step's are
-//     exponentiated), mask (causal / window), row maximum, exponentiate against
-//     a running reference maximum (a share of the exponentials runs as a
-//     polynomial on the FMA pipe, because the special-function unit is as
-//     loaded as the tensor core here), write P as F16 back into TMEM.  O stays
-//     in TMEM; it is rescaled only when the row maximum has grown by more than
-//     2^8 (exact: the final division by l uses the same reference maximum),
-//     read once at the end, normalised, and stored by TMA through two small
-//     swizzled staging tiles per warp.
+//     the 128 scores from TMEM, mask (causal / window), row maximum,
+//     exponentiate against a running reference maximum — packed two-element
+//     FMA-pipe instructions and three-input maxima keep the instruction count
+//     down, and a share of the exponentials runs as a polynomial on the FMA
+//     pipe, because the special-function unit is as loaded as the tensor core
+//     here — and write P as F16 back into TMEM.  O stays in TMEM; it is rescaled
+//     only when the row maximum has grown by more than 2^8 (exact: the final
+//     division by l uses the same reference maximum), read once at the end,
+//     normalised, and written out row by row.
 // Every wait has a time limit; on expiry the kernel records an error, still
 // frees its TMEM and returns.
 #include <cuda.h>
@@ -49,17 +49,16 @@ namespace {
 
 constexpr int kHd = 128;
 constexpr int kBM = 128;                 // query rows per block
-constexpr int kBN = 64;                  // keys per step = one cache page
-constexpr int kStages = 3;               // per ring (K and V tiles are staged separately)
+constexpr int kBN = 128;                 // keys per step = two cache pages
+constexpr int kStages = 2;               // per ring (K and V tiles are staged separately)
 constexpr int kGroupThreads = 128;       // one softmax warpgroup
-constexpr int kThreads = 2 * kGroupThreads + 96;     // + producer warp + one MMA warp per block
+constexpr int kThreads = 2 * kGroupThreads + 64;     // + producer warp + MMA warp
 constexpr uint32_t kQHalfBytes = kBM * 128;      // 64 dims of 128 rows
 constexpr uint32_t kQBytes = 2 * kQHalfBytes;    // 32 KB per block
-constexpr uint32_t kKVTile = kBN * kHd * 2;      // 16 KB: K or V of one head in one page
-constexpr uint32_t kKHalfBytes = kBN * 128;      // 64 dims of 64 keys
-constexpr uint32_t kOutStage = 32 * 32 * 4;      // 4 KB: 32 rows x 32 F32 columns
+constexpr uint32_t kPageBlock = 64 * kHd * 2;    // 16 KB: K or V of one head in one page
+constexpr uint32_t kKVTile = 2 * kPageBlock;     // 32 KB: 128 keys
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0;                   // S (then P) of block b, buffer x at columns 128*b + 64*x
+constexpr uint32_t kTmemS = 0;                   // S (then P) of block b at columns 128*b
 constexpr uint32_t kTmemO = 256;                 // O of block b at columns 256 + 128*b
 constexpr float kRescaleLog2 = 8.0f;             // move the reference max when it is 2^8 behind
 constexpr float kLog2e = 1.4426950408889634f;
@@ -69,12 +68,6 @@ constexpr int kTileSlots = 4;                    // ring of published work tiles
 #define WR_PREFILL_POLY_PERIOD 4
 #endif
 constexpr int kPolyPeriod = WR_PREFILL_POLY_PERIOD;
-// Block 1's softmax group starts each work tile this many clocks late, so that the two
-// blocks ask the tensor core for their next scores at different times (see the kernel).
-#ifndef WR_PREFILL_STAGGER
-#define WR_PREFILL_STAGGER 600
-#endif
-constexpr long long kStaggerClk = WR_PREFILL_STAGGER;
 
 // Development aid, off by default: built with -DWR_PREFILL_TIMELINE the kernel's CTA 0
 // writes clock64() stamps of its hand-offs into a device buffer (kTlRoles rows of
@@ -82,7 +75,13 @@ constexpr long long kStaggerClk = WR_PREFILL_STAGGER;
 // wr_cuda_debug_prefill_timeline copies out.
 #ifdef WR_PREFILL_TIMELINE
 // Rows 3 (softmax group of block 0) and 4 (MMA warp) hold tile-level stamps as clock * 16 + tag.
-constexpr int kTlRoles = 5, kTlEvents = 512;
+constexpr int kTlRoles = 5, kTlEvents = 512, kTlCtas = 160;     // + per CTA: start ns, end ns, tiles, steps
+__device__ __forceinline__ long long tl_ns()
+{
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 #define TL_DECL uint32_t tl_n = 0, tl_m = 0; const bool tl_on = (blockIdx.x == 0) && p.tl != nullptr
 #define TL(role) do { if (tl_on && tl_n < kTlEvents) p.tl[(role) * kTlEvents + tl_n++] = clock64(); } while (0)
 #define TLT(role, tag) do { if (tl_on && tl_m < kTlEvents) p.tl[(role) * kTlEvents + tl_m++] = clock64() * 16 + (tag); } while (0)
@@ -102,6 +101,7 @@ struct prefill_params {
     const uint64_t *pages;      // page table of (session, layer)
     const char *page_base;      // non-null: page t = page_base + t * page_bytes
     uint64_t page_bytes;
+    float *out;                 // [n, n_q, hd] F32
     int *err;
     int *sched;                 // [0] next work tile, [1] CTAs that have left
     uint32_t n, p0, n_q, n_kv, group, window, n_qtiles, n_tiles;
@@ -117,22 +117,19 @@ struct tile_info {
 
 struct smem_layout {
     alignas(1024) uint8_t q[2][kQBytes];                 // per block: [64-dim half][128 rows][128 B]
-    alignas(1024) uint8_t k[kStages][kKVTile];           // [64-dim half][64 keys][128 B]
-    alignas(1024) uint8_t v[kStages][kKVTile];
-    alignas(1024) uint8_t ostage[8][2][kOutStage];       // per softmax warp, two tiles in flight
+    alignas(1024) uint8_t k[kStages][kKVTile];           // [64-dim half][128 keys][128 B]
+    alignas(1024) uint8_t v[kStages][kKVTile];           // [page][64-dim half][64 keys][128 B]
     alignas(8) uint64_t q_full[2];                       // per block
     uint64_t q_free;
     uint64_t k_full[kStages], k_free[kStages];
     uint64_t v_full[kStages], v_free[kStages];
-    uint64_t s_full[2][2];                               // [block][buffer]: scores are in TMEM
+    uint64_t s_full[2];                                  // per block: scores are in TMEM
     uint64_t p_full[2];                                  // per block: P is in TMEM (one arrival per warp)
-    uint64_t pv_pen[2];                                  // per block: the tile's last-but-one P.V has completed
     uint64_t o_done[2];                                  // per block: the tile's last P.V has completed
     uint64_t o_free[2];                                  // per block: O has been read out (one arrival per warp)
     uint64_t tile_ready[kTileSlots];
     tile_info tile[kTileSlots];
     uint32_t tmem_base;
-    int pipe_lock;                                       // held by the MMA warp that is issuing a step's instructions
 };
 
 // ---- tcgen05 / TMA wrappers ------------------------------------------------
@@ -393,34 +390,54 @@ __device__ __forceinline__ block_range range_of(const prefill_params &p, uint32_
 // ---- the kernel ------------------------------------------------------------
 
 __global__ void __launch_bounds__(kThreads, 1)
-attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap out_map,
-                          const prefill_params p)
+attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefill_params p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     smem_layout &sm = *reinterpret_cast<smem_layout *>(smem_raw);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef WR_PREFILL_TIMELINE
+    if (tid == 0 && p.tl && blockIdx.x < kTlCtas) p.tl[kTlRoles * kTlEvents + blockIdx.x * 4] = tl_ns();
+#endif
 
     if (warp == 8 && lane == 0) {
         mbar_init(&sm.q_full[0], 1);
         mbar_init(&sm.q_full[1], 1);
-        mbar_init(&sm.q_free, 2);                        // one arrival per MMA warp
+        mbar_init(&sm.q_free, 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sm.k_full[i], 1);
-            mbar_init(&sm.k_free[i], 2);
+            mbar_init(&sm.k_free[i], 1);
             mbar_init(&sm.v_full[i], 1);
-            mbar_init(&sm.v_free[i], 2);
+            mbar_init(&sm.v_free[i], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&sm.s_full[b][0], 1);
-            mbar_init(&sm.s_full[b][1], 1);
+            mbar_init(&sm.s_full[b], 1);
             mbar_init(&sm.p_full[b], 4);
-            mbar_init(&sm.pv_pen[b], 1);
             mbar_init(&sm.o_done[b], 1);
             mbar_init(&sm.o_free[b], 4);
         }
         for (int i = 0; i < kTileSlots; ++i) mbar_init(&sm.tile_ready[i], 1);
-        sm.pipe_lock = 0;
         fence_barrier_init();
+        // The first tile's first loads (Q of block 0, the first K tile, Q of block 1) start
+        // at once: they fly while TMEM is allocated and the other warps reach the barrier.
+        const tile_info ti = decode_tile(p, blockIdx.x);
+        const block_range r0 = range_of(p, ti.qt[0]), r1 = range_of(p, ti.qt[ti.nblk - 1]);
+        const uint32_t lo = min(r0.lo, r1.lo);
+        const uint32_t n_pages_all = (p.p0 + p.n + 63u) / 64u;
+        for (uint32_t b = 0; b < ti.nblk; ++b) {
+            mbar_expect_tx(&sm.q_full[b], kQBytes);
+            tma_load_2d(sm.q[b], &q_map, (int)(ti.head[b] * kHd), (int)(ti.qt[b] * kBM), &sm.q_full[b]);
+            tma_load_2d(sm.q[b] + kQHalfBytes, &q_map, (int)(ti.head[b] * kHd + 64), (int)(ti.qt[b] * kBM), &sm.q_full[b]);
+            if (b == 0) {
+                const uint32_t n_pg = (2 * lo + 1 < n_pages_all) ? 2u : 1u;
+                mbar_expect_tx(&sm.k_full[0], n_pg * kPageBlock);
+                for (uint32_t pg = 0; pg < n_pg; ++pg) {
+                    const char *src = (p.page_base ? p.page_base + (uint64_t)(2 * lo + pg) * p.page_bytes
+                                                   : (const char *)p.pages[2 * lo + pg]) + wr_block_off(ti.kvh, 0, kHd);
+                    bulk_g2s(sm.k[0] + pg * 8192, src, 8192, &sm.k_full[0]);
+                    bulk_g2s(sm.k[0] + kQHalfBytes + pg * 8192, src + 8192, 8192, &sm.k_full[0]);
+                }
+            }
+        }
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -432,6 +449,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
     const long long limit = p.wait_limit;
+    const uint32_t n_pages_total = (p.p0 + p.n + 63u) / 64u;     // pages that hold rows of this prompt
 
     auto page_ptr = [&](uint32_t t) -> const char * {
         return p.page_base ? p.page_base + (uint64_t)t * p.page_bytes : (const char *)p.pages[t];
@@ -469,23 +487,34 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 auto load_k = [&](uint32_t j) -> bool {
                     const uint32_t st = kcount % kStages;
                     if (kcount >= kStages && !mbar_wait(&sm.k_free[st], ((kcount / kStages) - 1) & 1, limit)) return false;
-                    mbar_expect_tx(&sm.k_full[st], kKVTile);
-                    bulk_g2s(sm.k[st], page_ptr(j) + wr_block_off(ti.kvh, 0, kHd), kKVTile, &sm.k_full[st]);
+                    // [64-dim half][128 keys][128 B]: each page contributes 64 keys to each half
+                    const uint32_t n_pg = (2 * j + 1 < n_pages_total) ? 2u : 1u;
+                    mbar_expect_tx(&sm.k_full[st], n_pg * kPageBlock);
+                    for (uint32_t pg = 0; pg < n_pg; ++pg) {
+                        const char *src = page_ptr(2 * j + pg) + wr_block_off(ti.kvh, 0, kHd);
+                        bulk_g2s(sm.k[st] + pg * 8192, src, 8192, &sm.k_full[st]);
+                        bulk_g2s(sm.k[st] + kQHalfBytes + pg * 8192, src + 8192, 8192, &sm.k_full[st]);
+                    }
                     ++kcount;
                     return true;
                 };
                 // what the first scores need goes first: Q of block 0, the first K tile, Q of block 1
-                load_q(0, ti.head[0], ti.qt[0]);
-                ok = load_k(lo);
-                if (ti.nblk > 1) load_q(1, ti.head[1], ti.qt[1]);
-                // The next tile is claimed late — when this tile's last K tiles are being
-                // requested, a few steps before its end — so that the tiles still unclaimed
+                // (the CTA's first tile had these issued before the CTA-wide barrier)
+                if (it > 0) {
+                    load_q(0, ti.head[0], ti.qt[0]);
+                    ok = load_k(lo);
+                    if (ti.nblk > 1) load_q(1, ti.head[1], ti.qt[1]);
+                } else {
+                    kcount = 1;
+                }
+                // The next tile is claimed late — when this tile's last K tile is being
+                // requested, a step or two before its end — so that the tiles still unclaimed
                 // go to the CTAs that really finish first; claimed at the start, every CTA
                 // would hold its second tile before it had done any work.
                 uint32_t next_tile = 0;
                 bool claimed = false;
                 for (uint32_t j = lo + 1; j < hi && ok; ++j) {
-                    if (!claimed && j + 2 >= hi) {
+                    if (!claimed && j + 1 >= hi) {
                         next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
                         claimed = true;
                     }
@@ -499,6 +528,9 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 mbar_arrive(&sm.tile_ready[slot]);               // (release: the tile is visible to the waiters)
             }
             if (!ok) atomicCAS(p.err, 0, 11);
+#ifdef WR_PREFILL_TIMELINE
+            if (p.tl && blockIdx.x < kTlCtas) p.tl[kTlRoles * kTlEvents + blockIdx.x * 4 + 3] = kcount;
+#endif
         } else if (lane == 1) {
             uint32_t vcount = 0;
             bool ok = true;
@@ -513,24 +545,24 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                         ok = mbar_wait(&sm.v_free[st], ((vcount / kStages) - 1) & 1, limit);
                         if (!ok) break;
                     }
-                    mbar_expect_tx(&sm.v_full[st], kKVTile);
-                    bulk_g2s(sm.v[st], page_ptr(j) + wr_block_off(ti.kvh, 1, kHd), kKVTile, &sm.v_full[st]);
+                    const uint32_t n_pg = (2 * j + 1 < n_pages_total) ? 2u : 1u;
+                    mbar_expect_tx(&sm.v_full[st], n_pg * kPageBlock);
+                    for (uint32_t pg = 0; pg < n_pg; ++pg)
+                        bulk_g2s(sm.v[st] + pg * kPageBlock, page_ptr(2 * j + pg) + wr_block_off(ti.kvh, 1, kHd),
+                                 kPageBlock, &sm.v_full[st]);
                 }
             }
             if (!ok) atomicCAS(p.err, 0, 14);
         }
-    } else if (warp >= 9) {
-        // ------------------------------------------------ MMA warps, one per block
-        // The whole warp runs this control flow; one elected lane issues the
-        // tensor-core instructions.  (Issued from a branch that only one lane
-        // takes, every operand has to be moved out of that lane's registers one
-        // instruction at a time, in competition with the softmax warps for issue
-        // slots: measured 100-220 clk per instruction against 64 this way.)
-        // Each block has its own warp so that the two blocks' hand-offs are served
-        // independently: one block's P.V never waits for the other block's softmax.
-        // Both warps walk every step of every work tile, also the steps their block
-        // takes no part in, because a K or V stage is free when BOTH have let it go.
-        const uint32_t b = warp - 9;
+    } else if (warp == 9) {
+        // ------------------------------------------------ MMA warp
+        // The whole warp runs this control flow and works the operands out; one
+        // elected lane issues the tensor-core instructions, and only the
+        // instruction itself is predicated.  (Issued from a branch that only one
+        // lane takes, operand arithmetic included, every value has to be moved out
+        // of that lane's registers one instruction at a time, in competition with
+        // the softmax warps for issue slots: measured 100-220 clk per instruction
+        // against 64 this way.)
         const bool lead = elect_one();
         const uint32_t idesc_s = umma_idesc(kBM, kBN, false);
         const uint32_t idesc_o = umma_idesc(kBM, kHd, true);
@@ -539,145 +571,115 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         const uint64_t kmaj0 = umma_desc(0, 16, 1024), mnmaj0 = umma_desc(0, 8192, 1024);
         const uint32_t kmaj_hi = (uint32_t)(kmaj0 >> 32), kmaj_lo = (uint32_t)kmaj0;
         const uint32_t mnmaj_hi = (uint32_t)(mnmaj0 >> 32), mnmaj_lo = (uint32_t)mnmaj0;
-        const uint32_t q_lo = (kmaj_lo | ((smem_u32(sm.q[0]) & 0x3FFFFu) >> 4)) + b * (kQBytes >> 4);
+        const uint32_t q_lo0 = kmaj_lo | ((smem_u32(sm.q[0]) & 0x3FFFFu) >> 4);
         const uint32_t k_lo0 = kmaj_lo | ((smem_u32(sm.k[0]) & 0x3FFFFu) >> 4);
         const uint32_t v_lo0 = mnmaj_lo | ((smem_u32(sm.v[0]) & 0x3FFFFu) >> 4);
-        const uint32_t s_tmem = tmem + kTmemS + 128 * b, o_tmem = tmem + kTmemO + 128 * b;
         // ring positions advance by one per step; parity flips when a ring wraps
         uint32_t k_st = 0, k_par = 0;            // K stage / parity of the next step to score
         uint32_t v_st = 0, v_par = 0;            // V stage / parity of the next step to multiply
-        uint32_t seq = 0;                        // score tiles issued (buffer = seq & 1)
-        uint32_t p_uses = 0, o_uses = 0, q_uses = 0;   // P hand-offs, finished tiles, Q tiles of this block
+        uint32_t p_uses0 = 0, p_uses1 = 0;       // P hand-offs seen per block
+        uint32_t o_uses0 = 0, o_uses1 = 0;       // work tiles finished per block
+        uint32_t q_uses0 = 0, q_uses1 = 0;       // Q tiles seen per block
         bool ok = true;
         TL_DECL;
-#ifdef WR_PREFILL_TIMELINE
-        const bool tl_mma = (lane == 0 && b == 0);
-#else
-        const bool tl_mma = false;
-#endif
-        (void)tl_mma;
-        if (tl_mma) TLT(4, 0);                                   // role started
+        // S_b = Q_b . K^T for the K tile in stage st
+        auto issue_s = [&](uint32_t b, uint32_t st) {
+            const uint32_t q_lo = q_lo0 + b * (kQBytes >> 4), k_lo = k_lo0 + st * (kKVTile >> 4);
+            const uint32_t d = tmem + kTmemS + 128 * b;
+#pragma unroll
+            for (int kk = 0; kk < kHd / 16; ++kk) {
+                const uint32_t off = ((kk >> 2) * kQHalfBytes + (kk & 3) * 32) >> 4;
+                if (lead) umma_ss(d, q_lo + off, kmaj_hi, k_lo + off, kmaj_hi, idesc_s, kk > 0);
+            }
+            if (lead) umma_commit(&sm.s_full[b]);
+        };
+        // O_b (+)= P_b . V for the V tile in stage st, n_kk steps of 16 keys
+        auto issue_pv = [&](uint32_t b, uint32_t st, uint32_t n_kk, bool accumulate) {
+            const uint32_t v_lo = v_lo0 + st * (kKVTile >> 4);
+            const uint32_t d = tmem + kTmemO + 128 * b, a = tmem + kTmemS + 128 * b;
+            if (n_kk == kBN / 16) {
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk)
+                    if (lead)
+                        umma_ts(d, a + 8 * kk, v_lo + (((kk >> 2) * kPageBlock + (kk & 3) * 2048) >> 4), mnmaj_hi, idesc_o,
+                                accumulate || kk > 0);
+            } else {
+                for (uint32_t kk = 0; kk < n_kk; ++kk)
+                    if (lead)
+                        umma_ts(d, a + 8 * kk, v_lo + (((kk >> 2) * kPageBlock + (kk & 3) * 2048) >> 4), mnmaj_hi, idesc_o,
+                                accumulate || kk > 0);
+            }
+        };
         for (uint32_t it = 0; ok; ++it) {
             const tile_info ti = tile_of(it, ok);
             if (!ok || !ti.valid) break;
             const block_range rg0 = range_of(p, ti.qt[0]), rg1 = range_of(p, ti.qt[ti.nblk - 1]);
             const uint32_t lo = min(rg0.lo, rg1.lo), hi = max(rg0.hi, rg1.hi);
-            const block_range me = (b == 0) ? rg0 : rg1;
-            const bool present = b < ti.nblk;
-            // steps this block takes part in (none when it is absent from the tile)
-            const uint32_t my_lo = present ? me.lo : hi, my_hi = present ? me.hi : hi;
-            if (tl_mma) TLT(4, 1);                               // tile known
-            bool q_seen = false;
-            // this block's scores of step jj from the K tile at the ring's head, then the tile is let go
-            // (the caller has seen the K tile land)
-            auto scores = [&](uint32_t jj) {
-                if (jj >= my_lo && jj < my_hi) {
-                    const uint32_t k_lo = k_lo0 + k_st * (kKVTile >> 4);
-                    const uint32_t x = seq & 1, d = s_tmem + 64 * x;
-                    // (operands are worked out by the whole warp; only the instruction itself is predicated)
-#pragma unroll
-                    for (int kk = 0; kk < kHd / 16; ++kk) {
-                        const uint32_t qoff = ((kk >> 2) * kQHalfBytes + (kk & 3) * 32) >> 4;
-                        const uint32_t koff = ((kk >> 2) * kKHalfBytes + (kk & 3) * 32) >> 4;
-                        if (lead) umma_ss(d, q_lo + qoff, kmaj_hi, k_lo + koff, kmaj_hi, idesc_s, kk > 0);
-                    }
-                    if (lead) {
-                        umma_commit(&sm.s_full[b][x]);
-                        umma_commit(&sm.k_free[k_st]);
-                        if (jj + 1 == hi) umma_commit(&sm.q_free);   // Q is no longer read
-                    }
-                    ++seq;
-                } else if (lead) {
-                    mbar_arrive(&sm.k_free[k_st]);
-                    if (jj + 1 == hi) mbar_arrive(&sm.q_free);
-                }
-                if (++k_st == kStages) { k_st = 0; k_par ^= 1; }
-            };
-            auto k_landed = [&]() -> bool { return mbar_wait(&sm.k_full[k_st], k_par, limit); };
-            auto q_landed = [&]() -> bool {
-                if (q_seen || !present) return true;
-                q_seen = true;
-                return mbar_wait(&sm.q_full[b], (q_uses++) & 1, limit);
-            };
-            // scores run two steps ahead of the softmax
-            ok = k_landed() && q_landed();
+            const bool two = ti.nblk > 1;
+            const uint32_t lo1 = two ? rg1.lo : hi, hi1 = two ? rg1.hi : hi;     // block 1's steps (none when absent)
+
+            // first scores of the tile
+            ok = mbar_wait(&sm.k_full[k_st], k_par, limit);
+            if (ok && lo >= rg0.lo && lo < rg0.hi) ok = mbar_wait(&sm.q_full[0], (q_uses0++) & 1, limit);
             if (!ok) break;
             tc_fence_after();
-            scores(lo);
-            if (tl_mma) TLT(4, 3);                               // first scores issued
-            if (lo + 1 < hi) {
-                ok = k_landed();
+            if (lo >= rg0.lo && lo < rg0.hi) issue_s(0, k_st);
+            if (two) {
+                ok = mbar_wait(&sm.q_full[1], (q_uses1++) & 1, limit);
                 if (!ok) break;
                 tc_fence_after();
-                scores(lo + 1);
+                if (lo >= lo1 && lo < hi1) issue_s(1, k_st);
             }
+            if (lead) {
+                umma_commit(&sm.k_free[k_st]);
+                if (lo + 1 == hi) umma_commit(&sm.q_free);       // Q is no longer read
+            }
+            if (++k_st == kStages) { k_st = 0; k_par ^= 1; }
             for (uint32_t j = lo; j < hi && ok; ++j) {
-                // the operands of this step's P.V and of the scores two steps ahead landed long ago
-                if (tl_mma) TL(2);                               // loop top
+                const bool more = j + 1 < hi;
+                // this step's V tile and the next step's K tile landed long ago
                 ok = mbar_wait(&sm.v_full[v_st], v_par, limit);
-                if (tl_mma) TL(2);                               // V seen
-                if (ok && j + 2 < hi) ok = k_landed();
+                if (ok && more) ok = mbar_wait(&sm.k_full[k_st], k_par, limit);
                 if (!ok) break;
-                if (j >= my_lo && j < my_hi) {
-                    // the first P.V of a tile overwrites O: the previous tile's rows must have left TMEM
-                    if (j == my_lo && o_uses > 0) ok = mbar_wait(&sm.o_free[b], (o_uses - 1) & 1, limit);
-                    const uint32_t x = p_uses & 1;               // P sits in the buffer its scores came from
-                    const bool last = (j + 1 == my_hi);
-                    // steps of 16 keys; the last tile stops at the block's last key
-                    const uint32_t n_kk = last ? (me.key_end - j * kBN + 15u) / 16u : (uint32_t)(kBN / 16);
-                    const uint32_t v_lo = v_lo0 + v_st * (kKVTile >> 4), a = s_tmem + 64 * x;
-                    const bool accumulate = j > my_lo;
-                    if (tl_mma) TL(2);                           // ready for P
-                    if (ok) ok = mbar_wait(&sm.p_full[b], p_uses & 1, limit);
-                    ++p_uses;
-                    if (!ok) break;
-                    if (tl_mma) TL(2);                           // P seen
-                    // One block's step goes to the tensor core as a whole.  With the two
-                    // warps' instructions interleaved, both blocks would get their next scores
-                    // late and at the same moment, and would ask again at the same moment for
-                    // ever; served one after the other, the blocks settle half a step apart and
-                    // each finds the tensor core free.
-                    if (lead) {
-                        const long long t0 = clock64();
-                        while (atomicCAS(&sm.pipe_lock, 0, 1) != 0) {
-                            if (clock64() - t0 > limit) {
-                                ok = false;
-                                break;
-                            }
+                // one block: wait for its P, issue its P.V, then its next scores
+                auto step_block = [&](uint32_t b, uint32_t blo, uint32_t bhi, uint32_t key_end, uint32_t &p_uses,
+                                      uint32_t &o_uses) -> bool {
+                    if (j >= blo && j < bhi) {
+                        bool good = true;
+                        // the first P.V of a tile overwrites O: the previous tile's rows must have left TMEM
+                        if (j == blo && o_uses > 0) good = mbar_wait(&sm.o_free[b], (o_uses - 1) & 1, limit);
+                        const bool last = (j + 1 == bhi);
+                        // steps of 16 keys; the last tile stops at the block's last key
+                        const uint32_t n_kk = last ? (key_end - j * kBN + 15u) / 16u : (uint32_t)(kBN / 16);
+                        if (good) good = mbar_wait(&sm.p_full[b], p_uses & 1, limit);
+                        ++p_uses;
+                        if (!good) return false;
+                        if (lane == 0) TL(2);                    // P seen
+                        tc_fence_after();
+                        issue_pv(b, v_st, n_kk, j > blo);
+                        if (last) {
+                            if (lead) umma_commit(&sm.o_done[b]);
+                            ++o_uses;
                         }
                     }
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    if (tl_mma) TL(2);                           // lock held
-                    tc_fence_after();
-                    if (n_kk == kBN / 16) {
-#pragma unroll
-                        for (int kk = 0; kk < kBN / 16; ++kk)
-                            if (lead) umma_ts(o_tmem, a + 8 * kk, v_lo + ((kk * 2048) >> 4), mnmaj_hi, idesc_o, accumulate || kk > 0);
-                    } else {
-                        for (uint32_t kk = 0; kk < n_kk; ++kk)
-                            if (lead) umma_ts(o_tmem, a + 8 * kk, v_lo + ((kk * 2048) >> 4), mnmaj_hi, idesc_o, accumulate || kk > 0);
+                    if (more && j + 1 >= blo && j + 1 < bhi) issue_s(b, k_st);      // (P_b of step j was consumed just above)
+                    if (lane == 0) TL(2);                        // P.V and next scores issued
+                    return true;
+                };
+                ok = step_block(0, rg0.lo, rg0.hi, rg0.key_end, p_uses0, o_uses0);
+                if (ok && two) ok = step_block(1, lo1, hi1, rg1.key_end, p_uses1, o_uses1);
+                if (!ok) break;
+                if (lead) {
+                    umma_commit(&sm.v_free[v_st]);
+                    if (more) {
+                        umma_commit(&sm.k_free[k_st]);
+                        if (j + 2 == hi) umma_commit(&sm.q_free);
                     }
-                    if (tl_mma) TL(2);                           // P.V issued
-                    // the scores of step j+2 go into the buffer whose P was consumed just above
-                    if (j + 2 < hi) scores(j + 2);
-                    if (tl_mma) TL(2);                           // next scores issued and committed
-                    if (lead) atomicExch(&sm.pipe_lock, 0);
-                    if (lead) {
-                        if (j + 2 == my_hi) umma_commit(&sm.pv_pen[b]);
-                        if (last) umma_commit(&sm.o_done[b]);
-                        umma_commit(&sm.v_free[v_st]);
-                    }
-                    if (last) ++o_uses;
-                    if (tl_mma) TL(2);                           // step closed
-                } else {
-                    if (lead) mbar_arrive(&sm.v_free[v_st]);
-                    if (j + 2 < hi) scores(j + 2);
                 }
                 if (++v_st == kStages) { v_st = 0; v_par ^= 1; }
+                if (more && ++k_st == kStages) { k_st = 0; k_par ^= 1; }
             }
         }
-        if (!ok && lane == 0 && blockIdx.x == 0) TLFAIL(2 + 2 * b, 2000 + seq, p_uses, o_uses, k_st * 100 + v_st * 10 + k_par * 2 + v_par);
         if (!ok && lane == 0) atomicCAS(p.err, 0, 12);
     } else {
         // ----------------------------- softmax warpgroup b: one thread per query row
@@ -688,19 +690,15 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         const uint32_t s_addr = tmem + lane_base + kTmemS + 128 * b;
         const uint32_t o_addr = tmem + lane_base + kTmemO + 128 * b;
         const float c2 = p.scale_log2;
-        uint32_t seq = 0, o_uses = 0, pen_uses = 0, vc = 0;  // seq: score tiles consumed (buffer = seq & 1)
+        uint32_t s_uses = 0, o_uses = 0, vc = 0;
         bool ok = true;
         TL_DECL;
 #ifdef WR_PREFILL_TIMELINE
         const bool tl_me = (lane == 0 && wq == 0);
 #define TLS() do { if (tl_me) TL(b); } while (0)
-#define TLST(tag) do { if (tl_me && b == 0) TLT(3, tag); } while (0)
 #else
 #define TLS()
-#define TLST(tag)
 #endif
-        TLST(0);                                             // role started
-        uint32_t stores = 0;                                 // lane 0: staging tiles handed to TMA so far
         for (uint32_t it = 0; ok; ++it) {
             const tile_info ti = tile_of(it, ok);
             if (!ok || !ti.valid) break;
@@ -711,79 +709,60 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 continue;
             }
             const block_range me = (b == 0) ? rg0 : rg1;
-            const uint32_t pen_phase = pen_uses;             // this tile's phase of pv_pen (tiles of two steps or more)
-            if (me.hi - me.lo >= 2) ++pen_uses;
-            TLST(1);                                         // tile known
+            const uint32_t head = (b == 0) ? ti.head[0] : ti.head[1];
             const uint32_t qpos = p.p0 + me.tok0 + row;      // absolute position of this query
             uint32_t lo_key = 0;
             if (p.window > 0 && qpos + 1 > p.window) lo_key = qpos + 1 - p.window;
             float m_ref = WR_NEG_SENTINEL;                   // reference max, log2 domain
             float l = 0.f;
-            // The scores of the current step live in s[]; the next step's are fetched
-            // from TMEM while this step is still being exponentiated.
-            float s[kBN];
-            ok = mbar_wait(&sm.s_full[b][seq & 1], (seq >> 1) & 1, limit);
-            if (!ok) break;
-            tc_fence_after();
-            tmem_ld32_nowait(s_addr + 64 * (seq & 1), s);
-            tmem_ld32_nowait(s_addr + 64 * (seq & 1) + 32, s + 32);
-            tmem_wait_ld();
-            if (b == 1 && kStaggerClk > 0) {
-                // Both groups hand their P over and need the scores of two steps ahead; asked
-                // for at the same moment, the second block's scores arrive late (the tensor core
-                // serves both requests back to back) and its softmax stalls every step.  Half a
-                // step apart, each request finds the tensor core free.
-                const long long t0 = clock64();
-                while (clock64() - t0 < kStaggerClk) { }
-            }
-            for (uint32_t j = me.lo; j < me.hi && ok; ++j, ++seq) {
-                TLS();                                           // 0: scores in registers
-                const uint32_t x = seq & 1;
+            for (uint32_t j = me.lo; j < me.hi && ok; ++j) {
+                ok = mbar_wait(&sm.s_full[b], s_uses & 1, limit);
+                ++s_uses;
+                if (!ok) break;
+                TLS();                                           // 0: scores ready
+                tc_fence_after();
+                float s[kBN];
+#pragma unroll
+                for (int c = 0; c < kBN; c += 32) tmem_ld32_nowait(s_addr + c, s + c);
+                tmem_wait_ld();
                 const uint32_t key0 = j * kBN;
                 // steps that no row's causal or window limit cuts through need no masking
                 const bool edge = (key0 + kBN - 1 > p.p0 + me.tok0) || (p.window > 0);
                 if (edge) {
+                    if (p.window == 0) {
+                        // causal limit only: key i of this step is visible iff i <= qpos - key0
+                        // (negative for a row that lies before the whole step: nothing visible)
+                        const int last_visible = (int)(qpos - key0);
 #pragma unroll
-                    for (int i = 0; i < kBN; ++i) {
-                        const uint32_t key = key0 + i;
-                        if (key > qpos || key < lo_key) s[i] = WR_NEG_SENTINEL;
+                        for (int i = 0; i < kBN; ++i)
+                            if (i > last_visible) s[i] = WR_NEG_SENTINEL;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < kBN; ++i) {
+                            const uint32_t key = key0 + i;
+                            if (key > qpos || key < lo_key) s[i] = WR_NEG_SENTINEL;
+                        }
                     }
                 }
-                // four independent chains of three-input maxima
-                float mx[4] = {max3(s[0], s[1], s[2]), max3(s[3], s[4], s[5]), max3(s[6], s[7], s[8]), max3(s[9], s[10], s[11])};
+                // eight independent chains of three-input maxima
+                float mx[8];
 #pragma unroll
-                for (int i = 12; i + 8 <= kBN; i += 8) {
-                    mx[0] = max3(mx[0], s[i], s[i + 1]);
-                    mx[1] = max3(mx[1], s[i + 2], s[i + 3]);
-                    mx[2] = max3(mx[2], s[i + 4], s[i + 5]);
-                    mx[3] = max3(mx[3], s[i + 6], s[i + 7]);
-                }
-                mx[0] = max3(mx[0], s[kBN - 4], s[kBN - 3]);
-                mx[1] = max3(mx[1], s[kBN - 2], s[kBN - 1]);
-                const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                for (int e = 0; e < 8; ++e) mx[e] = fmaxf(s[2 * e], s[2 * e + 1]);
+#pragma unroll
+                for (int i = 16; i < kBN; i += 16)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) mx[e] = max3(mx[e], s[i + 2 * e], s[i + 2 * e + 1]);
+                const float tmax = fmaxf(max3(mx[0], mx[1], mx[2]), max3(max3(mx[3], mx[4], mx[5]), mx[6], mx[7]));
                 // Move the reference max (and rescale O) only when it is far behind.
                 // The rescale uses warp-wide TMEM instructions, so the warp decides
-                // together; rows that do not need it multiply by one.  O must hold
-                // every earlier step: the last P.V issued is that of step j-1, and the
-                // scores of step j+1 were issued right behind it — once those have
-                // arrived, it has completed (the tensor core executes in issue order).
+                // together; rows that do not need it multiply by one.  O is quiet here:
+                // this step's scores were issued behind the previous step's P.V, so that
+                // P.V has completed, and the next one waits for the P written below.
                 const float tm2 = tmax * c2;
                 const bool grow = (tmax > WR_NEG_SENTINEL) && (m_ref != WR_NEG_SENTINEL) && (tm2 > m_ref + kRescaleLog2);
                 if (tmax > WR_NEG_SENTINEL && m_ref == WR_NEG_SENTINEL) m_ref = tm2;
-                const bool more = j + 1 < me.hi;
-                bool next_seen = false;
                 if (__any_sync(0xffffffffu, grow)) {
                     const float a = grow ? ex2_approx(m_ref - tm2) : 1.0f;
-                    if (more) {
-                        ok = mbar_wait(&sm.s_full[b][x ^ 1], ((seq + 1) >> 1) & 1, limit);
-                        next_seen = true;
-                    } else {
-                        // last step of the block: nothing was issued behind P.V of step j-1,
-                        // the MMA warp signals its completion on its own
-                        ok = mbar_wait(&sm.pv_pen[b], pen_phase & 1, limit);
-                    }
-                    if (!ok) break;
-                    tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < kHd; c += 32) {
                         float o[32];
@@ -799,11 +778,9 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                     }
                 }
                 TLS();                                           // 1: maximum known
-                // P = 2^(s*c2 - m_ref) as F16, two keys per TMEM column, over the first 32 columns of
-                // the score buffer (no visible key yet for this row: every score is the sentinel, gives 0)
+                // P = 2^(s*c2 - m_ref) as F16, two keys per TMEM column, over the first 64 columns of S
+                // (no visible key yet for this row: every score is the sentinel and must give 0)
                 const float neg_m = (m_ref == WR_NEG_SENTINEL) ? 0.f : -m_ref;
-                const uint32_t p_addr = s_addr + 64 * x;
-                const uint32_t s_next = s_addr + 64 * (x ^ 1);
                 const uint64_t c2_2 = pack2(c2, c2), neg_m2 = pack2(neg_m, neg_m);
                 uint64_t psum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
@@ -827,31 +804,15 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                         const __half2 hh = __floats2half2_rn(p0, p1);
                         w[e] = *reinterpret_cast<const uint32_t *>(&hh);
                     }
-                    tmem_st16(p_addr + 16 * c, w);
+                    tmem_st16(s_addr + 16 * c, w);
                 }
-                // The scores are spent: refill them with the next step's (issued a whole step
-                // ago).  This wait stays in front of the hand-over of P on purpose: it keeps a
-                // warp from running a step ahead of its group, which the per-warp arrivals on
-                // p_full rely on.
-                if (more) {
-                    TLS();                                       // 2: exponentials done
-                    if (!next_seen) {
-                        ok = mbar_wait(&sm.s_full[b][x ^ 1], ((seq + 1) >> 1) & 1, limit);
-                        tc_fence_after();
-                    }
-                    if (ok) {
-                        tmem_ld32_nowait(s_next, s);
-                        tmem_ld32_nowait(s_next + 32, s + 32);
-                    }
-                }
-                if (!ok) break;
                 {
                     float pa, pb, pc, pd;
                     unpack2(psum2[0], pa, pb);
                     unpack2(psum2[1], pc, pd);
                     l += (pa + pb) + (pc + pd);
                 }
-                TLS();                                           // 3: next scores seen
+                TLS();                                           // 2: P stores issued
                 if (key0 + kBN > p.p0 + p.n) {
                     // Cache rows past the prompt's last key were never written for it
                     // (or belong to a rolled-back step): clear them in the staged V
@@ -861,8 +822,8 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                     ok = mbar_wait(&sm.v_full[vst], (vn / kStages) & 1, limit);
                     if (!ok) break;
                     const uint32_t first_bad = p.p0 + p.n - key0;
-                    if (row < kBN && row >= first_bad) {
-                        uint8_t *vrow = sm.v[vst] + row * 128;
+                    if (row >= first_bad) {
+                        uint8_t *vrow = sm.v[vst] + (row >> 6) * kPageBlock + (row & 63u) * 128;
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
                             *reinterpret_cast<uint4 *>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
@@ -874,19 +835,17 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
+                // (a warp cannot arrive twice in one phase: its next scores are issued
+                // behind the P.V that waits for all four arrivals of this one)
                 if (lane == 0) mbar_arrive(&sm.p_full[b]);
-                TLS();                                           // 4: P handed over
-                if (more) tmem_wait_ld();
+                TLS();                                           // 3: P handed over
             }
-            tmem_wait_ld();                                  // (an early exit may leave a fetch in flight)
             vc += hi - lo;
             if (!ok) break;
-            TLST(2);                                         // last P handed over
             // ---- the tile's last P.V has completed: O leaves TMEM, normalised
             ok = mbar_wait(&sm.o_done[b], o_uses & 1, limit);
             ++o_uses;
             if (!ok) break;
-            TLST(3);                                         // O complete
             tc_fence_after();
             float o[kHd];
 #pragma unroll
@@ -895,43 +854,16 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.o_free[b]);       // the next tile may overwrite O
-            TLST(4);                                         // O in registers
-            const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-            // Each warp hands its 32 rows to the TMA engine as four tiles of 32 rows x 32
-            // columns (128-byte rows, the eight 16-byte chunks of a row XOR-swizzled with
-            // the row number: conflict free for these row-wise writes and the layout a
-            // 128-byte-swizzled tensor map expects); rows beyond the prompt are dropped
-            // by the hardware.  Two staging tiles are filled and handed over together.
-            const bool rows_live = wq * 32u < me.rows;
-            const int y = (int)(me.tok0 + wq * 32u);
-            const int x0 = (int)((b == 0 ? ti.head[0] : ti.head[1]) * kHd);
+            // Each thread writes its own row (512 contiguous bytes) with 16-byte stores;
+            // nothing is waited for, the softmax group goes straight on to its next tile.
+            if (row < me.rows) {
+                const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+                float4 *dst = reinterpret_cast<float4 *>(p.out + ((size_t)(me.tok0 + row) * p.n_q + head) * kHd);
 #pragma unroll
-            for (int c2 = 0; c2 < 2; ++c2) {
-                // (the two staging tiles were handed to TMA as one group: wait for its reads)
-                if (lane == 0 && stores > 0) tma_store_wait_read0();
-                __syncwarp();
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int c = 2 * c2 + h;
-                    float4 *trow = reinterpret_cast<float4 *>(sm.ostage[warp][h] + lane * 128);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e)
-                        trow[e ^ (lane & 7)] = make_float4(o[32 * c + 4 * e] * inv, o[32 * c + 4 * e + 1] * inv,
-                                                            o[32 * c + 4 * e + 2] * inv, o[32 * c + 4 * e + 3] * inv);
-                }
-                fence_proxy_async();                           // generic writes -> TMA reads
-                __syncwarp();
-                if (lane == 0 && rows_live) {
-                    tma_store_2d(&out_map, x0 + 64 * c2, y, sm.ostage[warp][0]);
-                    tma_store_2d(&out_map, x0 + 64 * c2 + 32, y, sm.ostage[warp][1]);
-                    tma_store_commit();
-                    ++stores;
-                }
+                for (int e = 0; e < kHd / 4; ++e)
+                    dst[e] = make_float4(o[4 * e] * inv, o[4 * e + 1] * inv, o[4 * e + 2] * inv, o[4 * e + 3] * inv);
             }
-            TLST(5);                                         // stores issued
         }
-        if (lane == 0 && stores > 0) tma_store_wait_all();   // the staging tiles are read, the rows are written
-        if (!ok && lane == 0 && wq == 0 && blockIdx.x == 0) TLFAIL(b, 1000 + seq, o_uses, vc, pen_uses);
         if (!ok) atomicCAS(p.err, 0, 13);
     }
 
@@ -941,6 +873,9 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
                      : "memory");
     }
+#ifdef WR_PREFILL_TIMELINE
+    if (tid == 0 && p.tl && blockIdx.x < kTlCtas) p.tl[kTlRoles * kTlEvents + blockIdx.x * 4 + 1] = tl_ns();
+#endif
     // The last CTA to leave rewinds the work counter for the next launch.
     if (tid == 0) {
         __threadfence();
@@ -1052,26 +987,18 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return WR_CUDA_ERR_INTERNAL;
 
-    CUtensorMap out_map;                                          // F32 [n, n_q_heads * hd], boxes of 32 x 32
-    const cuuint64_t odims[2] = {(cuuint64_t)n_q_heads * kHd, (cuuint64_t)n};
-    const cuuint64_t ostrides[1] = {(cuuint64_t)n_q_heads * kHd * 4};
-    const cuuint32_t obox[2] = {32, 32};
-    if (encode(&out_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)dout, odims, ostrides, obox, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return WR_CUDA_ERR_INTERNAL;
-
     prefill_params p;
     p.pages = kv->d_pages + (size_t)layer * kv->n_pages;
     p.page_base = kv->contig[layer] ? (const char *)kv->pages[(size_t)layer * kv->n_pages] : nullptr;
     p.page_bytes = wr_page_bytes(kv->n_kv, kHd);
 #ifdef WR_PREFILL_TIMELINE
     if (!ctx->debug_buf) {
-        WR_CUDA_TRY(cudaMalloc(&ctx->debug_buf, kTlRoles * kTlEvents * sizeof(long long)));
+        WR_CUDA_TRY(cudaMalloc(&ctx->debug_buf, (kTlRoles * kTlEvents + 4 * kTlCtas) * sizeof(long long)));
     }
-    WR_CUDA_TRY(cudaMemsetAsync(ctx->debug_buf, 0, kTlRoles * kTlEvents * sizeof(long long), ctx->stream));
+    WR_CUDA_TRY(cudaMemsetAsync(ctx->debug_buf, 0, (kTlRoles * kTlEvents + 4 * kTlCtas) * sizeof(long long), ctx->stream));
     p.tl = (long long *)ctx->debug_buf;
 #endif
+    p.out = dout;
     p.err = ctx->dev_err;
     p.sched = ctx->prefill_sched;
     p.wait_limit = ctx->wait_limit;
@@ -1091,7 +1018,7 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
         ctx->attr_flags |= 2u;
     }
     const uint32_t grid = std::min<uint32_t>(p.n_tiles, (uint32_t)ctx->sm_count);
-    attn_prefill_hd128_kernel<<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, out_map, p);
+    attn_prefill_hd128_kernel<<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, p);
     ctx->launches++;
     WR_CUDA_TRY(cudaGetLastError());
     if (host) {
@@ -1108,7 +1035,7 @@ extern "C" int wr_cuda_debug_prefill_timeline(wr_cuda_ctx *ctx, long long *host_
     if (!ctx || !host_out || !ctx->debug_buf) return WR_CUDA_ERR_INVAL;
     std::lock_guard<std::mutex> g(ctx->lock);
     WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    const size_t want = std::min<size_t>(n, (size_t)kTlRoles * kTlEvents) * sizeof(long long);
+    const size_t want = std::min<size_t>(n, (size_t)kTlRoles * kTlEvents + 4 * kTlCtas) * sizeof(long long);
     WR_CUDA_TRY(cudaMemcpy(host_out, ctx->debug_buf, want, cudaMemcpyDeviceToHost));
     return WR_CUDA_OK;
 }
