@@ -371,8 +371,10 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
         if xchg is not None:
             out_f = torch.empty_like(q)
 
-            def step_fused():
+            def step_fused_two_kernels():
                 splitkv.decode_split_kv(ctx, batch, 0, lens, q, out_f, HQ, triples=triples, exchange=xchg)
+
+            step_fused = step_fused_two_kernels
 
             def run(n, end_event=None):
                 try:
@@ -400,6 +402,26 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
                          "identical_to_allgather_path": bool(torch.equal(out_f, out))}
                 if want0 is not None:
                     fused["parity_max_abs_err"] = r4(np.abs(out_f[:1].cpu().numpy() - want0).max())
+                # the decode kernel's own warps deliver the triples to the peers
+                out_d = torch.empty_like(q)
+
+                def step_fused_decode():
+                    splitkv.decode_split_kv(ctx, batch, 0, lens, q, out_d, HQ, exchange=xchg, fused_decode=True)
+
+                step_fused = step_fused_decode
+                good = all_ok(run(3))
+                if good:
+                    dist.barrier()
+                    a.record(stream)
+                    good = all_ok(run(reps, b))
+                    torch.cuda.synchronize()
+                if good:
+                    t = torch.tensor([a.elapsed_time(b) / reps], device="cuda", dtype=torch.float64)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    fused["in_decode_kernel_ms_per_step"] = r4(t.item())
+                    fused["in_decode_kernel_identical"] = bool(torch.equal(out_d, out))
+                else:
+                    fused["in_decode_kernel_error"] = why or "a peer rank failed"
             splitkv.close_exchange(xchg, ctx)                      # destroy is collective
         if fused is None:
             fused = {"error": why or "a peer rank failed"}

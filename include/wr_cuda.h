@@ -273,6 +273,19 @@ void wr_cuda_xchg_destroy(wr_cuda_xchg *x);
 int wr_cuda_attn_exchange_combine(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_rows,
                                   const float *triples, float *out);
 
+/* Key-sharded decode with the exchange fused into the decode kernel (no
+ * reference counterpart, as above): wr_cuda_attn_decode_partial and
+ * wr_cuda_attn_exchange_combine in one call.  The decode kernel's own warps
+ * store every finished (session, q head) triple into all ranks' buffers and
+ * publish the step; a small second kernel waits (bounded) for every rank's
+ * step and merges in rank order into out (device, F32 [n_sess, n_q_heads,
+ * head_dim]).  q is device memory; head_dim 128.  Identical bits to the
+ * two-call sequence.  Every rank makes the same sequence of calls. */
+int wr_cuda_attn_decode_exchange(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_sess,
+                                 wr_cuda_kv *const *kv, uint32_t layer,
+                                 const uint32_t *seq_lens, const float *q, float *out,
+                                 uint32_t n_q_heads, float scale_override);
+
 #ifdef __cplusplus
 }
 #endif

@@ -276,6 +276,19 @@ def test_exchange_single_rank_and_refusals(ctx):
         x.combine(rows, triples, got)
         ctx.sync()
         assert torch.equal(got, want)
+    # the decode kernel delivering its triples itself (exchange fused in): same bits again,
+    # with multi-chunk sessions (merge warps), a one-chunk session (engine) and an empty shard
+    out3 = torch.full((len(lens), hq, hd), float("nan"), dtype=torch.float32, device="cuda")
+    for _ in range(3):
+        x.decode(kvs, 0, lens, qd, out3, hq)
+        ctx.sync()
+        assert torch.equal(out3.view(rows, hd), want)
+    lens0 = [300, 0, 1]
+    ctx.attn_decode_partial(kvs, 0, lens0, qd, triples, hq)
+    ctx.attn_combine(1, rows, hd, triples, want)
+    x.decode(kvs, 0, lens0, qd, out3, hq)
+    ctx.sync()
+    assert torch.equal(out3.view(rows, hd), want)
     with pytest.raises(wr.WrCudaError) as e:
         x.combine(rows + 1, triples, got)                       # more rows than the buffers hold
     assert e.value.status == -4

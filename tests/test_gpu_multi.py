@@ -61,6 +61,13 @@ def _worker(rank, world, port_no, result_q):
     ctx.sync()
     torch.cuda.synchronize()
     same = bool(np.array_equal(out2.cpu().numpy().view(np.uint32), got.view(np.uint32)))
+    # and with the decode kernel itself delivering the triples to the peers
+    out3 = torch.full_like(qd, float("nan"))
+    for _ in range(3):
+        splitkv.decode_split_kv(ctx, kvs, 0, local, qd, out3, hq, exchange=xchg, fused_decode=True)
+    ctx.sync()
+    torch.cuda.synchronize()
+    same = same and bool(np.array_equal(out3.cpu().numpy().view(np.uint32), got.view(np.uint32)))
     splitkv.close_exchange(xchg, ctx)
     rc, want = P.decode_batch(q, ks, vs, threads=4, max_seq=32768)
     result_q.put((rank, rc, float(np.abs(got - want).max()), same))

@@ -38,7 +38,7 @@ EXPORTS = [
     "wr_cuda_attn_decode_static",
     "wr_cuda_xchg_create", "wr_cuda_xchg_handle", "wr_cuda_xchg_connect", "wr_cuda_xchg_connect_local",
     "wr_cuda_xchg_destroy",
-    "wr_cuda_attn_exchange_combine",
+    "wr_cuda_attn_exchange_combine", "wr_cuda_attn_decode_exchange",
 ]
 
 
@@ -101,6 +101,7 @@ def load_library():
         "wr_cuda_xchg_connect_local": (i32, [vp, C.POINTER(vp)]),
         "wr_cuda_xchg_destroy": (None, [vp]),
         "wr_cuda_attn_exchange_combine": (i32, [vp, vp, u32, vp, vp]),
+        "wr_cuda_attn_decode_exchange": (i32, [vp, vp, u32, C.POINTER(vp), u32, C.POINTER(u32), vp, vp, u32, f32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -323,6 +324,17 @@ class Exchange:
             raise ValueError("wr_cuda_attn_exchange_combine takes device buffers only")
         _check(self._lib.wr_cuda_attn_exchange_combine(self._ctx._h, self._h, n_rows, tp, op),
                "wr_cuda_attn_exchange_combine")
+
+    def decode(self, kvs, layer, seq_lens, q, out, n_q_heads, scale=0.0) -> None:
+        """wr_cuda_attn_decode_exchange: partial attention over this rank's keys with the
+        exchange and the merge fused in (device buffers)."""
+        qp, qm, _q = _buf(q)
+        op, om, _o = _buf(out)
+        if qm != MEM_DEVICE or om != MEM_DEVICE:
+            raise ValueError("wr_cuda_attn_decode_exchange takes device buffers only")
+        _check(self._lib.wr_cuda_attn_decode_exchange(self._ctx._h, self._h, len(kvs), Context._handles(kvs), layer,
+                                                      Context._u32s(seq_lens), qp, op, n_q_heads, scale),
+               "wr_cuda_attn_decode_exchange")
 
     def close(self) -> None:
         if self._h:

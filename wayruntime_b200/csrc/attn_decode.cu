@@ -216,7 +216,7 @@ void wr_decode_plan(uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer, cons
 // ctx->lock and has validated the arguments.
 int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
                      const uint32_t *seq_lens, const float *dq, float *dout, uint32_t n_q,
-                     float scale_override, uint32_t window, int emit_triples)
+                     float scale_override, uint32_t window, int emit_triples, const wr_decode_xchg *xchg)
 {
     const uint32_t n_kv = kv[0]->n_kv, hd = kv[0]->hd;
     const uint32_t group = n_q / n_kv;
@@ -238,6 +238,18 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
         p.wait_limit = ctx->wait_limit;
         p.emit_triples = (uint32_t)emit_triples;
         p.scale = scale;
+        p.x_world = 0;
+        p.x_step = 0;
+        p.x_done = nullptr;
+        if (xchg) {
+            for (uint32_t w = 0; w < xchg->world; ++w) {
+                p.x_rows[w] = xchg->rows[w];
+                p.x_flag[w] = xchg->flag[w];
+            }
+            p.x_done = xchg->done;
+            p.x_world = xchg->world;
+            p.x_step = xchg->step;
+        }
         if (!(ctx->attr_flags & 1u)) {
             WR_CUDA_TRY(cudaFuncSetAttribute(attn_decode_hd128_kernel<1>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -300,7 +312,7 @@ static int decode_common(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *k
         WR_CUDA_TRY(cudaMemcpyAsync((void *)dq, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
     }
     rc = wr_decode_launch(ctx, n_sess, kv, layer, seq_lens, dq, dout, n_q, scale_override, window,
-                          emit_triples);
+                          emit_triples, nullptr);
     if (rc != WR_CUDA_OK) return rc;
     if (mem == WR_CUDA_MEM_HOST) {
         WR_CUDA_TRY(cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -370,7 +382,7 @@ extern "C" int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv
                           n_rot_pairs, flags, dq_in);
     if (rc != WR_CUDA_OK) return rc;
     rc = wr_decode_launch(ctx, n_sess, kv, layer, seq_lens, dq, dout, n_q_heads, scale_override,
-                          window, 0);
+                          window, 0, nullptr);
     if (rc != WR_CUDA_OK) return rc;
     if (mem == WR_CUDA_MEM_HOST) {
         if (staged_out)

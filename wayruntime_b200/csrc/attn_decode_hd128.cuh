@@ -55,8 +55,14 @@ constexpr int kTripleStride = WR_CUDA_TRIPLE_PAD + kHd;  // m, l, 0, 0, o[128]
 constexpr int kMaxChunks = 128;                        // per session (lane c of a merge warp holds chunks c, c+32, c+64, c+96)
 constexpr int kChunkSlots = kMaxChunks / 32;
 constexpr int kChunkBatch = 16;                        // chunk rows a merge keeps in flight per head
-constexpr int kMinChunkTiles = 2;
-constexpr int kItemsPerSessionTarget = 128;            // work items one session should offer the engines
+#ifndef WR_DECODE_MIN_CHUNK_TILES
+#define WR_DECODE_MIN_CHUNK_TILES 2
+#endif
+#ifndef WR_DECODE_ITEMS_TARGET
+#define WR_DECODE_ITEMS_TARGET 128
+#endif
+constexpr int kMinChunkTiles = WR_DECODE_MIN_CHUNK_TILES;
+constexpr int kItemsPerSessionTarget = WR_DECODE_ITEMS_TARGET;   // work items one session should offer the engines
 
 // Tiles per chunk: a function of the session's own span and of the cache
 // geometry only — never of its batch mates (batch invariance).  A session
@@ -98,7 +104,30 @@ struct params {
     uint32_t n_sess, n_q, n_kv, group, qsubs, emit_triples, n_groups;
     float scale;
     long long wait_limit;   // SM clock cycles a device-side wait may last
+    // Key-sharded decode with the exchange fused in (x_world > 0): finished triples go
+    // straight into every rank's exchange buffer, slot of this rank, instead of `out`.
+    float *x_rows[WR_CUDA_XCHG_MAX_WORLD];       // per rank: this rank's row slot in that rank's buffer
+    uint32_t *x_flag[WR_CUDA_XCHG_MAX_WORLD];    // per rank: this rank's step flag in that rank's buffer
+    int *x_done;                                 // rows of this launch that have been stored everywhere
+    uint32_t x_world, x_step;
 };
+
+// Stores of one finished warp's rows are done: count them, and when every row of the launch
+// has been stored on every rank, publish the step number to all ranks (system-scope release).
+__device__ __forceinline__ void xchg_rows_done(const params &p, uint32_t rows, uint32_t lane)
+{
+    __threadfence_system();                      // this lane's peer stores are ordered before the count
+    __syncwarp();
+    if (lane == 0) {
+        const uint32_t total = p.n_sess * p.n_q;
+        if ((uint32_t)atomicAdd(p.x_done, (int)rows) + rows == total) {
+            __threadfence_system();
+            for (uint32_t w = 0; w < p.x_world; ++w)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.x_flag[w]), "r"(p.x_step) : "memory");
+            *p.x_done = 0;                       // ready for the next launch
+        }
+    }
+}
 
 }  // namespace wr_decode
 
@@ -229,7 +258,14 @@ __device__ __forceinline__ void merge_head_pair(const params &p, size_t row0, si
         if (hs >= heads_here) break;
         float4 &a4 = acc[e];
         if (dry_run) continue;
-        if (p.emit_triples) {
+        if (p.x_world > 0) {
+            // the row goes to every rank at once (plain 16-byte stores over NVLink, this rank included)
+            for (uint32_t w = 0; w < p.x_world; ++w) {
+                float *tr = p.x_rows[w] + (row0 + hs) * kTripleStride;
+                reinterpret_cast<float4 *>(tr + WR_CUDA_TRIPLE_PAD)[lane] = a4;
+                if (lane == 0) *reinterpret_cast<float4 *>(tr) = make_float4(mstar[e], L[e], 0.f, 0.f);
+            }
+        } else if (p.emit_triples) {
             float *tr = p.out + (row0 + hs) * kTripleStride;
             reinterpret_cast<float4 *>(tr + WR_CUDA_TRIPLE_PAD)[lane] = a4;
             if (lane == 0) {
@@ -241,6 +277,7 @@ __device__ __forceinline__ void merge_head_pair(const params &p, size_t row0, si
             reinterpret_cast<float4 *>(p.out + (row0 + hs) * kHd)[lane] = a4;
         }
     }
+    if (p.x_world > 0 && !dry_run) xchg_rows_done(p, min(2u, heads_here - hs0), lane);
 }
 
 // One tile of work, with everything the compute loop needs to know about it.
@@ -329,6 +366,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
     if (p.emit_triples && blockIdx.x == 0) {
         for (uint32_t s = 0; s < p.n_sess; ++s) {
             if (p.n_chunks[s] != 0) continue;
+            if (p.x_world > 0) {
+                // engine warp w writes rows w, w + kWarps, ... of the session to every rank
+                uint32_t mine = 0;
+                for (uint32_t r = warp; r < p.n_q; r += kWarps, ++mine)
+                    for (uint32_t w = 0; w < p.x_world; ++w) {
+                        float *tr = p.x_rows[w] + ((size_t)p.row[s] * p.n_q + r) * kTripleStride;
+                        for (uint32_t i = lane; i < (uint32_t)kTripleStride; i += 32) tr[i] = (i == 0) ? WR_NEG_SENTINEL : 0.f;
+                    }
+                if (mine) xchg_rows_done(p, mine, lane);
+                continue;
+            }
             float *base = p.out + (size_t)p.row[s] * p.n_q * kTripleStride;
             for (uint32_t i = threadIdx.x; i < p.n_q * kTripleStride; i += kWarps * 32)   // (engine threads only)
                 base[i] = (i % kTripleStride == 0) ? WR_NEG_SENTINEL : 0.f;
@@ -617,20 +665,25 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
                             o[md * 16 + g + 8] = (oacc[nt][md][2] + oacc[nt][md][3]) * inv;
                         }
                     } else {
-                        float *tr = direct ? p.out + (row0 + hs) * kTripleStride
-                                           : p.ws + ((size_t)d0.it * 8 + hs) * kTripleStride;
+                        // a one-chunk session's triple is final: with the exchange fused in it goes to every rank
+                        const uint32_t n_dst = (direct && p.x_world > 0) ? p.x_world : 1u;
+                        for (uint32_t w = 0; w < n_dst; ++w) {
+                            float *tr = direct ? (p.x_world > 0 ? p.x_rows[w] : p.out) + (row0 + hs) * kTripleStride
+                                               : p.ws + ((size_t)d0.it * 8 + hs) * kTripleStride;
 #pragma unroll
-                        for (int md = 0; md < kHd / 16; ++md) {
-                            tr[WR_CUDA_TRIPLE_PAD + md * 16 + g] = oacc[nt][md][0] + oacc[nt][md][1];
-                            tr[WR_CUDA_TRIPLE_PAD + md * 16 + g + 8] = oacc[nt][md][2] + oacc[nt][md][3];
-                        }
-                        if (g == 0) {
-                            tr[0] = m[nt]; tr[1] = lt; tr[2] = 0.f; tr[3] = 0.f;
+                            for (int md = 0; md < kHd / 16; ++md) {
+                                tr[WR_CUDA_TRIPLE_PAD + md * 16 + g] = oacc[nt][md][0] + oacc[nt][md][1];
+                                tr[WR_CUDA_TRIPLE_PAD + md * 16 + g + 8] = oacc[nt][md][2] + oacc[nt][md][3];
+                            }
+                            if (g == 0) {
+                                tr[0] = m[nt]; tr[1] = lt; tr[2] = 0.f; tr[3] = 0.f;
+                            }
                         }
                     }
                 }
             }
 
+            if (direct && p.x_world > 0) xchg_rows_done(p, heads_here, lane);
             if (!direct) {
                 // Note the arrival (signalled as described above).  __syncwarp
                 // orders every lane's partial stores before lane 0's release; the

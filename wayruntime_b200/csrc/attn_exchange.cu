@@ -44,6 +44,7 @@ struct xchg_params {
     int *done;
     int *err;
     uint32_t world, rank, max_rows, hd, n_rows, step, parity;
+    uint32_t skip_store;     // the rows were delivered by the decode kernel itself
     long long wait_limit;
 };
 
@@ -74,20 +75,22 @@ __global__ void __launch_bounds__(256) attn_exchange_combine_kernel(const xchg_p
     const uint32_t total_f4 = p.n_rows * row_f4;
     const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, gsize = gridDim.x * blockDim.x;
 
-    // 1. this rank's triples into every rank's buffer
-    const float4 *src = reinterpret_cast<const float4 *>(p.local_triples);
-    for (uint32_t peer = 0; peer < p.world; ++peer) {
-        float4 *dst = reinterpret_cast<float4 *>(slot_rows(p.peer[peer], p.parity, p.rank, p));
-        for (uint32_t i = gtid; i < total_f4; i += gsize) dst[i] = src[i];
+    __shared__ int s_ok;
+    if (!p.skip_store) {
+        // 1. this rank's triples into every rank's buffer
+        const float4 *src = reinterpret_cast<const float4 *>(p.local_triples);
+        for (uint32_t peer = 0; peer < p.world; ++peer) {
+            float4 *dst = reinterpret_cast<float4 *>(slot_rows(p.peer[peer], p.parity, p.rank, p));
+            for (uint32_t i = gtid; i < total_f4; i += gsize) dst[i] = src[i];
+        }
+        __threadfence_system();
     }
-    __threadfence_system();
     __syncthreads();
 
     // 2. the last CTA to get here publishes the step number to every rank
-    __shared__ int s_ok;
     if (threadIdx.x == 0) {
         s_ok = 1;
-        if (atomicAdd(p.done, 1) == (int)gridDim.x - 1) {
+        if (!p.skip_store && atomicAdd(p.done, 1) == (int)gridDim.x - 1) {
             __threadfence_system();
             for (uint32_t peer = 0; peer < p.world; ++peer)
                 st_release_sys(slot_flag(p.peer[peer], p.parity, p.rank, p), p.step);
@@ -264,11 +267,64 @@ extern "C" int wr_cuda_attn_exchange_combine(wr_cuda_ctx *ctx, wr_cuda_xchg *x, 
     p.hd = x->hd;
     p.n_rows = n_rows;
     p.wait_limit = ctx->wait_limit;
+    p.skip_store = 0;
     p.step = ++x->step;
     p.parity = x->step & 1u;
     // few CTAs: every one of them has to be resident while it waits for the peers
     const uint32_t work = n_rows * ((WR_CUDA_TRIPLE_PAD + x->hd) / 4);
     const uint32_t blocks = std::max(1u, std::min((work + 255u) / 256u, (uint32_t)ctx->sm_count / 2u));
+    attn_exchange_combine_kernel<<<blocks, 256, 0, ctx->stream>>>(p);
+    ctx->launches++;
+    WR_CUDA_TRY(cudaGetLastError());
+    return WR_CUDA_OK;
+}
+
+// Key-sharded decode with the exchange fused into the decode kernel: the warps that finish
+// a (session, q head) triple store it straight into every rank's exchange buffer, the last
+// one publishes this rank's step flag, and a small second kernel waits for every rank's
+// flag and merges.  Same result bits as wr_cuda_attn_decode_partial + wr_cuda_attn_exchange_combine.
+extern "C" int wr_cuda_attn_decode_exchange(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_sess,
+                                            wr_cuda_kv *const *kv, uint32_t layer, const uint32_t *seq_lens,
+                                            const float *q, float *out, uint32_t n_q_heads, float scale_override)
+{
+    if (!ctx || !x || x->ctx != ctx) return WR_CUDA_ERR_INVAL;
+    if (!x->connected) return WR_CUDA_ERR_STATE;
+    std::lock_guard<std::mutex> g(ctx->lock);
+    int rc = wr_decode_validate(ctx, n_sess, kv, layer, seq_lens, q, out, n_q_heads, WR_CUDA_MEM_DEVICE, 1);
+    if (rc != WR_CUDA_OK) return rc;
+    if (kv[0]->hd != 128 || x->hd != 128) return WR_CUDA_ERR_UNSUPPORTED;      // the fused path is the head_dim-128 kernel's
+    const uint32_t n_rows = n_sess * n_q_heads;
+    if (n_rows == 0 || n_rows > x->max_rows) return WR_CUDA_ERR_INVAL;
+    WR_CUDA_TRY(cudaSetDevice(ctx->device));
+    xchg_params p;
+    for (uint32_t r = 0; r < WR_CUDA_XCHG_MAX_WORLD; ++r) p.peer[r] = x->peer[r];
+    p.local_triples = nullptr;
+    p.out = out;
+    p.done = x->done;
+    p.err = ctx->dev_err;
+    p.world = x->world;
+    p.rank = x->rank;
+    p.max_rows = x->max_rows;
+    p.hd = x->hd;
+    p.n_rows = n_rows;
+    p.wait_limit = ctx->wait_limit;
+    p.skip_store = 1;
+    p.step = ++x->step;
+    p.parity = x->step & 1u;
+    wr_decode_xchg dx;
+    const size_t stride = WR_CUDA_TRIPLE_PAD + x->hd;
+    for (uint32_t w = 0; w < x->world; ++w) {
+        dx.rows[w] = reinterpret_cast<float *>(x->peer[w] + kFlagBytes) +
+                     ((size_t)p.parity * x->world + x->rank) * x->max_rows * stride;
+        dx.flag[w] = reinterpret_cast<uint32_t *>(x->peer[w]) + p.parity * x->world + x->rank;
+    }
+    dx.done = x->done;
+    dx.world = x->world;
+    dx.step = p.step;
+    rc = wr_decode_launch(ctx, n_sess, kv, layer, seq_lens, q, out, n_q_heads, scale_override, 0, 1, &dx);
+    if (rc != WR_CUDA_OK) return rc;
+    const uint32_t work = n_rows * (x->hd / 4);
+    const uint32_t blocks = std::max(1u, std::min((work + 255u) / 256u, (uint32_t)ctx->sm_count));
     attn_exchange_combine_kernel<<<blocks, 256, 0, ctx->stream>>>(p);
     ctx->launches++;
     WR_CUDA_TRY(cudaGetLastError());

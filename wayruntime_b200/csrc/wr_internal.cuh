@@ -118,6 +118,20 @@ struct wr_batch_desc {
         }                                                                   \
     } while (0)
 
+// Where a key-sharded decode launch delivers its triples when the exchange is fused into it.
+struct wr_decode_xchg {
+    float *rows[WR_CUDA_XCHG_MAX_WORLD];       // per rank: this rank's row slot in that rank's buffer
+    uint32_t *flag[WR_CUDA_XCHG_MAX_WORLD];    // per rank: this rank's step flag in that rank's buffer
+    int *done;
+    uint32_t world, step;
+};
+int wr_decode_validate(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
+                       const uint32_t *seq_lens, const void *q, const void *out, uint32_t n_q, int mem,
+                       int emit_triples);
+int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
+                     const uint32_t *seq_lens, const float *dq, float *dout, uint32_t n_q,
+                     float scale_override, uint32_t window, int emit_triples, const wr_decode_xchg *xchg);
+
 int wr_ctx_reserve_stage(wr_cuda_ctx *ctx, size_t dev_bytes, size_t host_bytes);
 // Wait for the context's stream and report (and clear) the device-side error
 // word: WR_CUDA_ERR_INTERNAL when a kernel gave up on a bounded wait.  Every

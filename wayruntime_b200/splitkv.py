@@ -91,16 +91,21 @@ def close_exchange(x, ctx, group=None):
 
 
 def decode_split_kv(ctx, kvs, layer, local_lens, q, out, n_q_heads, scale=0.0, group=None,
-                    triples=None, gathered=None, exchange=None):
+                    triples=None, gathered=None, exchange=None, fused_decode=False):
     """One decode step over key-sharded caches.  q, out: CUDA float32 tensors
     [n_sess, n_q_heads, hd]; local_lens: keys of each session held by this rank.
     Everything is enqueued on the context's stream (set it current for NCCL).
     With `exchange` (see make_exchange) the all-gather and the merge are one
-    kernel over peer memory instead of an NCCL collective and a merge kernel."""
+    kernel over peer memory instead of an NCCL collective and a merge kernel;
+    with `fused_decode` as well, the decode kernel itself stores its triples
+    into the peers' buffers (wr_cuda_attn_decode_exchange, head_dim 128)."""
     import torch
     import torch.distributed as dist
     n_sess, _, hd = q.shape
     rows = n_sess * n_q_heads
+    if exchange is not None and fused_decode:
+        exchange.decode(kvs, layer, local_lens, q, out, n_q_heads, scale=scale)
+        return out
     if triples is None:
         triples = torch.empty((rows, TRIPLE_PAD + hd), dtype=torch.float32, device=q.device)
     ctx.attn_decode_partial(kvs, layer, local_lens, q, triples, n_q_heads, scale=scale)
