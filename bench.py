@@ -547,11 +547,14 @@ def run_gpu_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    json_out = sys.stdout
     if world > 1:
         import torch.distributed as dist
-        # stdout carries exactly one JSON line: keep NCCL's version banner off it
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # stdout carries exactly one JSON line: whatever NCCL (a C library) writes to file
+        # descriptor 1 goes to stderr instead; the line itself is written to the saved descriptor
+        sys.stdout.flush()
+        json_out = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
@@ -865,7 +868,8 @@ def run_gpu_arm(args):
             "kv_head_sharded": kv_head_sharded,
             "split_kv": split_kv,
         }
-        print(json.dumps(line))
+        json_out.write(json.dumps(line) + "\n")
+        json_out.flush()
     for kv in kvs:
         kv.close()
     ctx.close()
