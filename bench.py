@@ -533,6 +533,71 @@ def measure_kv_head_sharded(ctx, stream, torch, rank, world, reps):
             "output_finite": finite}
 
 
+WHOLE_MODEL_SHAPE = dict(n_layers=28, hidden=1024, n_q=16, n_kv=8, head_dim=128, ffn=3072, vocab=151936)
+WHOLE_MODEL_PROMPT, WHOLE_MODEL_TOKENS = 64, 32
+
+
+def measure_whole_model():
+    """BASELINE config 1 end to end through the public C API, `wayrt bench` style
+    (src/cli/wayrt.c:694-854: prefill all prompt tokens but the last, then N
+    greedy steps, wall clock around each phase), on a seeded GGUF of the
+    Qwen3-0.6B shape: the unmodified reference library on the host cores, the
+    drop-in library with only attention on the device (WR_B200_GLUE=host), and the
+    drop-in with the whole layer stack on the device (the default)."""
+    from wayruntime_b200 import wayrt_bench as wb
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libwayruntime_ref.so")
+    b200_path = os.path.join(ROOT, "wayruntime_b200", "lib", "libwayruntime_b200.so")
+    if not (os.path.exists(ref_path) and os.path.exists(b200_path)):
+        return {"unavailable": "the compiled reference and the drop-in library are built where the "
+                               "reference checkout exists; neither was found beside this file"}
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import tempfile
+    import _mkgguf
+    shape = WHOLE_MODEL_SHAPE
+    path = os.path.join(tempfile.mkdtemp(prefix="wr_bench_gguf_"), "qwen3_0p6b_shape.gguf")
+    _mkgguf.write_qwen3(path, seed=SEED, **shape)
+    prompt = wb.seeded_prompt(WHOLE_MODEL_PROMPT, shape["vocab"], SEED)
+    out = {"workload": "c1_single_stream: Qwen3-0.6B shape (28 layers, hidden 1024, 16 Q / 8 KV heads, "
+                       "head_dim 128, QK-norm, SwiGLU 3072, vocab 151936), F16 GGUF with seeded N(0, 0.02) "
+                       "weights (held as F32 by the loader), "
+                       f"{WHOLE_MODEL_PROMPT}-token seeded prompt, {WHOLE_MODEL_TOKENS} greedy tokens",
+           "timer": "wayrt bench restated over the public C API (wayruntime_b200/wayrt_bench.py)"}
+    runs = (("reference", ref_path, None), ("b200_attention_only", b200_path, "host"),
+            ("b200_device_glue", b200_path, "device"))
+    ids = {}
+    try:
+        for name, lib_path, glue in runs:
+            if glue:
+                os.environ["WR_B200_GLUE"] = glue
+            lib = wb.Library(lib_path)
+            try:
+                # one short untimed pass per library first (page cache, lazy kernel loading), as for every arm
+                wb.bench(lib, path, prompt[:8], 2, shape["vocab"])
+                res = wb.bench(lib, path, prompt, WHOLE_MODEL_TOKENS, shape["vocab"])
+            finally:
+                lib.close()
+            ids[name] = res["ids"]
+            out[name] = {"prefill_tok_s": r4(wb.rate(res["n_prefill"], res["prefill_s"])),
+                         "prefill_ms": r4(1e3 * res["prefill_s"]),
+                         "decode_tok_s": r4(wb.rate(res["produced"], res["decode_s"])),
+                         "decode_ms_per_token": r4(1e3 * res["decode_s"] / max(1, res["produced"])),
+                         "threads": res["threads"],
+                         "attention_calls": res["counters"][3], "matmul_calls": res["counters"][0]}
+    finally:
+        os.environ.pop("WR_B200_GLUE", None)
+        os.remove(path)
+    for name in ("b200_attention_only", "b200_device_glue"):
+        same = 0
+        for a, b in zip(ids["reference"], ids[name]):
+            if a != b:
+                break
+            same += 1
+        out[name]["greedy_ids_equal_to_reference"] = f"{same} of {len(ids['reference'])} (free-running)"
+        out[name]["decode_speedup_vs_reference"] = r4(out[name]["decode_tok_s"] / out["reference"]["decode_tok_s"])
+        out[name]["prefill_speedup_vs_reference"] = r4(out[name]["prefill_tok_s"] / out["reference"]["prefill_tok_s"])
+    return out
+
+
 def wr_batch(kvs):
     import wayruntime_b200 as wr
     return wr.Batch(kvs)
@@ -807,6 +872,13 @@ def run_gpu_arm(args):
         if world > 1:
             raise
 
+    whole_model = None
+    if rank == 0 and world == 1 and not args.no_whole_model:
+        try:
+            whole_model = measure_whole_model()
+        except Exception as exc:
+            whole_model = {"error": f"{type(exc).__name__}: {exc}"}
+
     # ---- parity spot check + CPU baseline on rank 0 (bounded sample)
     cpu = None
     max_err = None
@@ -864,6 +936,7 @@ def run_gpu_arm(args):
             "cpu_baseline": cpu,
             "parity_max_abs_err": r4(max_err),
             "roofline_prefill": prefill,
+            "whole_model": whole_model,
             # the two multi-GPU sections go last: a reader of the line's tail sees them
             "kv_head_sharded": kv_head_sharded,
             "split_kv": split_kv,
@@ -886,6 +959,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step from Python instead of replaying a CUDA graph")
+    ap.add_argument("--no-whole-model", action="store_true",
+                    help="skip the config-1 whole-model section (about a minute of host time)")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="'prefill' / 'decode': run only that kernel's measurement (for profiling)")
     args = ap.parse_args()

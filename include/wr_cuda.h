@@ -286,6 +286,76 @@ int wr_cuda_attn_decode_exchange(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_s
                                  const uint32_t *seq_lens, const float *q, float *out,
                                  uint32_t n_q_heads, float scale_override);
 
+/* ---- the layer stack around attention, device-resident ------------------- */
+
+/* A device copy of one model's F32 weights plus the row scratch of a forward
+ * pass.  Replaces, for the callers of attention, the host loop of the
+ * reference's decode body (src/core/session.c:405-568: RMSNorm, Q/K/V
+ * projections, per-head QK-norm, attention, output projection, residual,
+ * RMSNorm, SwiGLU FFN, residual; then final RMSNorm and LM head,
+ * session.c:540-560) so that a row enters the device as a token id and leaves
+ * as logits instead of crossing the bus twice per layer.  Llama / Qwen3-class
+ * layers only (no sandwich norms, no per-layer embeddings).
+ *
+ * Weights are host pointers to F32 data in the GGML layout the reference keeps
+ * them in: a [in -> out] projection is out rows of in floats
+ * (src/core/kernels.c:978-1000).  embed and lm_head are [vocab][hidden]; they
+ * may be the same pointer (tied), and are then uploaded once. */
+#define WR_CUDA_MAX_LAYERS  64   /* WR_MAX_LAYERS, src/core/internal.h:184 */
+#define WR_CUDA_FWD_DECODE  0    /* row r = next token of session kv[r] at positions[r] */
+#define WR_CUDA_FWD_PREFILL 1    /* rows = consecutive tokens of kv[0] from positions[0] */
+
+typedef struct wr_cuda_model wr_cuda_model;
+
+typedef struct wr_cuda_layer_desc {
+    const float *attn_norm;           /* [hidden] */
+    const float *wq, *wk, *wv;        /* [n_q*hd][hidden], [n_kv*hd][hidden] x2 */
+    const float *q_norm, *k_norm;     /* [head_dim] each, or both NULL */
+    const float *wo;                  /* [hidden][n_q*hd] */
+    const float *ffn_norm;            /* [hidden] */
+    const float *w_gate, *w_up;       /* [ffn_dim][hidden] */
+    const float *w_down;              /* [hidden][ffn_dim] */
+    uint32_t ffn_dim, reserved;
+} wr_cuda_layer_desc;
+
+typedef struct wr_cuda_model_desc {
+    uint32_t n_layers, hidden, n_q_heads, n_kv_heads, head_dim, vocab;
+    uint32_t n_rot_pairs;             /* as wr_cuda_kv_append */
+    uint32_t max_rows;                /* rows one forward pass may carry (prefill chunk) */
+    float rms_eps, rope_theta, attn_scale /* <= 0: 1/sqrt(head_dim) */, reserved;
+    const float *embed, *lm_head, *final_norm;
+    const wr_cuda_layer_desc *layers; /* n_layers entries */
+} wr_cuda_model_desc;
+
+/* Uploads every weight (one device allocation) and takes the row scratch; the
+ * host copies are not referenced after the call returns. */
+int  wr_cuda_model_create(wr_cuda_ctx *ctx, const wr_cuda_model_desc *desc, wr_cuda_model **out);
+void wr_cuda_model_destroy(wr_cuda_model *m);
+uint64_t wr_cuda_model_bytes(const wr_cuda_model *m);      /* device bytes held */
+uint64_t wr_cuda_model_launches(const wr_cuda_model *m);   /* glue kernels launched so far */
+/* host time, in ns, that the last forward pass spent enqueueing before it began to wait for the device */
+uint64_t wr_cuda_model_last_enqueue_ns(const wr_cuda_model *m);
+
+/* One forward pass over n_rows rows (decode: n_rows <= WR_CUDA_BATCH_MAX
+ * sessions, one new token each; prefill: n_rows <= max_rows tokens of one
+ * session), KV appended at `positions` as wr_cuda_decode_step /
+ * wr_cuda_kv_append do — the caller commits the new length only when the call
+ * returns 0.  A token id >= vocab is WR_CUDA_ERR_INVAL before anything runs
+ * (session.c:413).  Results are written for rows [out_from, n_rows), all to
+ * host memory, each pointer optional: hidden_out [n][hidden] (the residual
+ * stream before the final norm), normed_out [n][hidden], logits_out[i] ->
+ * [vocab] for row out_from+i (an entry may be NULL), argmax_out[i] = the first
+ * maximum of that row's logits (the lowest id wins a tie, src/cli/wayrt.c:805).
+ * Logits / arg-max for at most WR_CUDA_BATCH_MAX rows per call.  attn_tap_out,
+ * when given, receives every layer's attention rows, [n_layers][n_rows][n_q*hd].
+ * The call synchronises and reports a device-side give-up like every
+ * host-buffer call.  One forward pass per model at a time (serialised inside). */
+int wr_cuda_model_forward(wr_cuda_ctx *ctx, wr_cuda_model *m, int mode, uint32_t n_rows,
+                          wr_cuda_kv *const *kv, const uint32_t *positions,
+                          const uint32_t *tokens, uint32_t out_from, float *hidden_out,
+                          float *normed_out, float *const *logits_out, uint32_t *argmax_out,
+                          float *attn_tap_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,9 @@ their place and the engine gate of wr_b200_engine.c in front of its
 wr_engine_create (wayruntime_b200/host/Makefile); `oracle/_ref/libwayruntime_ref*.so`
 is the unmodified reference.  Both are driven through the reference's public API
 (include/wayruntime/wayruntime.h) on the same seeded GGUF and token ids:
-  * teacher-forced greedy decoding: identical argmax at every step, logits
+  * teacher-forced greedy decoding, with the layer glue on the device (the
+    default) and on the host (WR_B200_GLUE=host), the prompt through the prefill
+    kernel and token by token: identical argmax at every step, logits
     within tolerance (BASELINE config 1: Qwen3-0.6B shape, 64-token prompt),
     and every layer's attention output of every token within tolerance: the
     reference's rows are captured by `libwayruntime_ref_tap.so` (same sources,
@@ -86,7 +88,10 @@ def test_session_self_tests_pass_on_device(libs):
     assert b.L.wri_self_test_batch_step() == 0
 
 
-def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol, attn_tol=2e-3):
+RUNS = (("device", "kernel"), ("device", "decode"), ("host", "kernel"), ("host", "decode"))
+
+
+def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol, attn_tol=2e-3, runs=RUNS):
     ref, b = libs
     vocab = shape["vocab"]
     path = os.path.join(tempfile.mkdtemp(prefix="wr_gguf_"), "model.gguf")
@@ -128,8 +133,10 @@ def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol, attn_tol=2e
     b_cb = B200_TAP(on_b200)
     b.L.wr_b200_set_attn_tap(b_cb, None)
     mb = b.load(path)
-    for mode in ("kernel", "decode"):
-        os.environ["WR_B200_PREFILL"] = mode
+    for glue, pf in runs:
+        mode = f"{glue}/{pf}"
+        os.environ["WR_B200_PREFILL"] = pf
+        os.environ["WR_B200_GLUE"] = glue               # read when the session is created
         sb = b.session(mb)
         assert b.prefill(sb, prompt[:-1]) == n_prompt - 1
         assert b.L.wr_session_pos(sb) == n_prompt - 1
@@ -152,6 +159,7 @@ def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol, attn_tol=2e
         attn.update(worst=0.0, rows=0)
     b.L.wr_b200_set_attn_tap(B200_TAP(0), None)
     os.environ.pop("WR_B200_PREFILL", None)
+    os.environ.pop("WR_B200_GLUE", None)
     b.L.wr_model_free(mb)
     os.remove(path)
     print("teacher-forced parity (argmax matches, worst logit err, min top-2 margin, worst attn err):", out)
@@ -173,11 +181,14 @@ def test_config1_qwen3_0p6b_shape(libs):
     WR_TEST_QUICK=1: each step is a full CPU forward in both libraries)."""
     shape = dict(n_layers=28, hidden=1024, n_q=16, n_kv=8, head_dim=128, ffn=3072, vocab=151936)
     steps = 24 if os.environ.get("WR_TEST_QUICK") == "1" else 128
-    _teacher_forced(libs, shape, n_prompt=64, n_steps=steps, seed=20261125, logit_tol=2e-3)
+    _teacher_forced(libs, shape, n_prompt=64, n_steps=steps, seed=20261125, logit_tol=2e-3,
+                    runs=(("device", "kernel"), ("device", "decode"), ("host", "kernel")))
 
 
-def test_batched_step_is_byte_equal_to_serial(libs):
+@pytest.mark.parametrize("glue", ["device", "host"])
+def test_batched_step_is_byte_equal_to_serial(libs, glue, monkeypatch):
     _ref, b = libs
+    monkeypatch.setenv("WR_B200_GLUE", glue)
     shape = dict(n_layers=2, hidden=256, n_q=8, n_kv=2, head_dim=128, ffn=512, vocab=777)
     path = os.path.join(tempfile.mkdtemp(prefix="wr_gguf_"), "model.gguf")
     _mkgguf.write_qwen3(path, seed=5, **shape)

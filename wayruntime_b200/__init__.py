@@ -9,6 +9,7 @@ from .binding import (  # noqa: F401
     Batch,
     Exchange,
     Context,
+    DeviceModel,
     KVCache,
     WrCudaError,
     MEM_DEVICE,
@@ -23,6 +24,6 @@ from .binding import (  # noqa: F401
 )
 
 __all__ = [
-    "Batch", "Context", "Exchange", "KVCache", "WrCudaError", "MEM_DEVICE", "MEM_HOST", "F16", "F32",
+    "Batch", "Context", "DeviceModel", "Exchange", "KVCache", "WrCudaError", "MEM_DEVICE", "MEM_HOST", "F16", "F32",
     "APPEND_ROPE", "TRIPLE_PAD", "device_check", "load_library", "status_name",
 ]

@@ -39,6 +39,8 @@ EXPORTS = [
     "wr_cuda_xchg_create", "wr_cuda_xchg_handle", "wr_cuda_xchg_connect", "wr_cuda_xchg_connect_local",
     "wr_cuda_xchg_destroy",
     "wr_cuda_attn_exchange_combine", "wr_cuda_attn_decode_exchange",
+    "wr_cuda_model_create", "wr_cuda_model_destroy", "wr_cuda_model_bytes", "wr_cuda_model_launches", "wr_cuda_model_last_enqueue_ns",
+    "wr_cuda_model_forward",
 ]
 
 
@@ -50,6 +52,22 @@ class WrCudaError(RuntimeError):
     def __init__(self, rc: int, what: str):
         super().__init__(f"{what}: {status_name(rc)}")
         self.status = rc
+
+
+class LayerDesc(C.Structure):
+    """wr_cuda_layer_desc (include/wr_cuda.h)."""
+    _fields_ = [(n, C.c_void_p) for n in ("attn_norm", "wq", "wk", "wv", "q_norm", "k_norm", "wo",
+                                          "ffn_norm", "w_gate", "w_up", "w_down")] + \
+               [("ffn_dim", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class ModelDesc(C.Structure):
+    """wr_cuda_model_desc (include/wr_cuda.h)."""
+    _fields_ = [(n, C.c_uint32) for n in ("n_layers", "hidden", "n_q_heads", "n_kv_heads", "head_dim",
+                                          "vocab", "n_rot_pairs", "max_rows")] + \
+               [(n, C.c_float) for n in ("rms_eps", "rope_theta", "attn_scale", "reserved")] + \
+               [("embed", C.c_void_p), ("lm_head", C.c_void_p), ("final_norm", C.c_void_p),
+                ("layers", C.POINTER(LayerDesc))]
 
 
 _lib = None
@@ -102,6 +120,13 @@ def load_library():
         "wr_cuda_xchg_destroy": (None, [vp]),
         "wr_cuda_attn_exchange_combine": (i32, [vp, vp, u32, vp, vp]),
         "wr_cuda_attn_decode_exchange": (i32, [vp, vp, u32, C.POINTER(vp), u32, C.POINTER(u32), vp, vp, u32, f32]),
+        "wr_cuda_model_create": (i32, [vp, C.POINTER(ModelDesc), C.POINTER(vp)]),
+        "wr_cuda_model_destroy": (None, [vp]),
+        "wr_cuda_model_bytes": (C.c_uint64, [vp]),
+        "wr_cuda_model_launches": (C.c_uint64, [vp]),
+        "wr_cuda_model_last_enqueue_ns": (C.c_uint64, [vp]),
+        "wr_cuda_model_forward": (i32, [vp, vp, i32, u32, C.POINTER(vp), C.POINTER(u32), C.POINTER(u32), u32,
+                                        vp, vp, C.POINTER(vp), C.POINTER(u32), vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -340,6 +365,89 @@ class Exchange:
         if self._h:
             self._lib.wr_cuda_xchg_destroy(self._h)
             self._h = None
+
+
+class DeviceModel:
+    """wr_cuda_model: a model's F32 weights mirrored on the device and the layer
+    stack around attention run there.  `weights` maps names to C-contiguous
+    float32 numpy arrays in GGML layout (a [in -> out] projection is [out][in]):
+    embed, lm_head (may be the same array), final_norm, and per layer i
+    `l{i}.attn_norm|wq|wk|wv|q_norm|k_norm|wo|ffn_norm|w_gate|w_up|w_down`."""
+
+    FWD_DECODE, FWD_PREFILL = 0, 1
+
+    def __init__(self, ctx: "Context", weights: dict, *, n_layers, hidden, n_q_heads, n_kv_heads, head_dim,
+                 vocab, ffn, rms_eps=1e-6, rope_theta=10000.0, n_rot_pairs=0, attn_scale=0.0, max_rows=256):
+        self._ctx, self._lib = ctx, ctx._lib
+        self.vocab, self.hidden, self.n_layers = vocab, hidden, n_layers
+        self.n_q, self.hd = n_q_heads, head_dim
+
+        def ptr(name, optional=False):
+            a = weights.get(name)
+            if a is None:
+                if optional:
+                    return None
+                raise KeyError(name)
+            if a.dtype != np.float32 or not a.flags["C_CONTIGUOUS"]:
+                raise ValueError(f"{name}: C-contiguous float32 expected")
+            return a.ctypes.data
+
+        layers = (LayerDesc * n_layers)()
+        for i in range(n_layers):
+            for f in ("attn_norm", "wq", "wk", "wv", "wo", "ffn_norm", "w_gate", "w_up", "w_down"):
+                setattr(layers[i], f, ptr(f"l{i}.{f}"))
+            layers[i].q_norm = ptr(f"l{i}.q_norm", optional=True)
+            layers[i].k_norm = ptr(f"l{i}.k_norm", optional=True)
+            layers[i].ffn_dim = ffn[i] if isinstance(ffn, (list, tuple)) else ffn
+        d = ModelDesc(n_layers=n_layers, hidden=hidden, n_q_heads=n_q_heads, n_kv_heads=n_kv_heads,
+                      head_dim=head_dim, vocab=vocab, n_rot_pairs=n_rot_pairs, max_rows=max_rows,
+                      rms_eps=rms_eps, rope_theta=rope_theta, attn_scale=attn_scale,
+                      embed=ptr("embed"), lm_head=ptr("lm_head"), final_norm=ptr("final_norm"), layers=layers)
+        h = C.c_void_p()
+        _check(self._lib.wr_cuda_model_create(ctx._h, C.byref(d), C.byref(h)), "wr_cuda_model_create")
+        self._h = h
+
+    def close(self):
+        if self._h:
+            self._lib.wr_cuda_model_destroy(self._h)
+            self._h = None
+
+    @property
+    def device_bytes(self) -> int:
+        return int(self._lib.wr_cuda_model_bytes(self._h))
+
+    @property
+    def launches(self) -> int:
+        return int(self._lib.wr_cuda_model_launches(self._h))
+
+    @property
+    def last_enqueue_ms(self) -> float:
+        """Host time the last forward pass spent enqueueing work, before waiting for the device."""
+        return self._lib.wr_cuda_model_last_enqueue_ns(self._h) * 1e-6
+
+    def forward(self, mode, kvs, positions, tokens, out_from=0, *, hidden=False, normed=False, logits=False,
+                argmax=False, attn_tap=False) -> dict:
+        """One forward pass; returns the requested results for rows [out_from, n) as numpy arrays."""
+        n = len(tokens)
+        n_out = n - out_from
+        res = {}
+        hid = np.empty((n_out, self.hidden), np.float32) if hidden else None
+        nrm = np.empty((n_out, self.hidden), np.float32) if normed else None
+        lg = np.empty((n_out, self.vocab), np.float32) if logits else None
+        am = (C.c_uint32 * max(n_out, 1))() if argmax else None
+        tap = np.empty((self.n_layers, n, self.n_q * self.hd), np.float32) if attn_tap else None
+        lptrs = (C.c_void_p * max(n_out, 1))(*[lg[i].ctypes.data for i in range(n_out)]) if logits else None
+        _check(self._lib.wr_cuda_model_forward(
+            self._ctx._h, self._h, mode, n, Context._handles(kvs), Context._u32s(positions),
+            Context._u32s(tokens), out_from, hid.ctypes.data if hidden else None,
+            nrm.ctypes.data if normed else None, lptrs, am, tap.ctypes.data if attn_tap else None),
+            "wr_cuda_model_forward")
+        if hidden: res["hidden"] = hid
+        if normed: res["normed"] = nrm
+        if logits: res["logits"] = lg
+        if argmax: res["argmax"] = np.array([am[i] for i in range(n_out)], np.uint32)
+        if attn_tap: res["attn"] = tap
+        return res
 
 
 class Batch:

@@ -14,11 +14,22 @@
  * checks, locking order and cursor rules (they are the contract a drop-in has
  * to reproduce); everything behind them is new.
  *
- * What stays on the host, through the reference's own ops and therefore with
- * the reference's own numerics: embedding, RMSNorm, the Q/K/V/O and FFN
- * matmuls, per-head QK-norm, residual adds, the LM head.  What moves to the
- * GPU: RoPE on Q and K, the F16 KV append and the attention itself
- * (src/core/session.c:471-496), through libwr_cuda.so.
+ * Two ways to run the layers around attention, chosen per model at session
+ * create:
+ *   device glue (default when every weight the stack needs is F32 in GGML
+ *     layout, which is what the reference's loader produces from F32 / F16 /
+ *     BF16 files): the weights are mirrored on the device once per model
+ *     (wr_cuda_model) and the whole stack — embedding, RMSNorm, projections,
+ *     QK-norm, RoPE + KV append + attention, FFN, final norm, LM head — runs
+ *     there; a step moves token ids in and logits out.  F32 arithmetic in a
+ *     different summation order than the host's: agrees with the reference to
+ *     F32 rounding, not bit for bit.
+ *   host glue (WR_B200_GLUE=host, quantised weights, or any model the device
+ *     stack does not cover): embedding, RMSNorm, matmuls, QK-norm, residual
+ *     adds and the LM head run through the reference's own ops, with the
+ *     reference's own numerics; only RoPE on Q and K, the F16 KV append and
+ *     the attention itself (src/core/session.c:471-496) go to the GPU.
+ * Both go through libwr_cuda.so; neither has a CPU attention path.
  *
  * Execution order is layer-lockstep over a set of rows: the n sessions of a
  * batched step, or the n tokens of a prefill.  Rows interact only through
@@ -39,7 +50,7 @@
  * positions, so chunking does not change any row's result.
  *
  * Environment: WR_CUDA_DEVICE selects the device (default 0);
- * WR_B200_PREFILL=decode makes wr_prefill run token by token through the
+ * WR_B200_GLUE=host keeps the layer glue on the host; WR_B200_PREFILL=decode makes wr_prefill run token by token through the
  * decode kernel (F32-exact queries) instead of the tensor-core prefill kernel
  * (F16 queries and probabilities).
  */
@@ -91,6 +102,7 @@ typedef struct row_buffers {
     float *k, *v;   /* [rows][n_kv*hd] */
     float *attn;    /* [rows][n_q*hd]  */
     float *normed, *proj, *gate, *up;   /* one row each */
+    float *hid_out, *norm_out;          /* [WR_BATCH_MAX][hidden], dense: results of a device pass */
     void  *block;              /* page-locked (wr_cuda_host_alloc) */
 } row_buffers;
 
@@ -98,7 +110,8 @@ typedef struct b200_session {
     struct wr_session pub;     /* first member: generate.c reads s->model through it */
     wr_cuda_kv *kv;
     wr_cuda_ctx *cuda;
-    float      *host;          /* one aligned block holding the scratch tensors */
+    wr_cuda_model *dm;         /* the model's device mirror (shared by its sessions), or NULL: host glue */
+    float      *host;          /* one page-locked block holding the scratch tensors */
     row_buffers rb;            /* taken once at create */
 } b200_session;
 
@@ -135,7 +148,7 @@ static int rows_alloc(row_buffers *rb, wr_cuda_ctx *cuda, const wr_model *m, uin
     const size_t hid = m->hidden_dim, nq = (size_t)m->n_q_heads * m->head_dim,
                  nkv = (size_t)m->n_kv_heads * m->head_dim, ffn = max_ffn(m);
     const size_t total = rows * (pad16(hid) + 2 * pad16(nq) + 2 * pad16(nkv)) + 2 * pad16(hid) +
-                         2 * pad16(ffn);
+                         2 * pad16(ffn) + 2 * WR_BATCH_MAX * pad16(hid);
     memset(rb, 0, sizeof(*rb));
     int rc = wr_cuda_host_alloc(cuda, total * sizeof(float), &rb->block);
     if (rc != 0) return rc;
@@ -149,8 +162,141 @@ static int rows_alloc(row_buffers *rb, wr_cuda_ctx *cuda, const wr_model *m, uin
     rb->normed = p; p += pad16(hid);
     rb->proj = p;   p += pad16(hid);
     rb->gate = p;   p += pad16(ffn);
-    rb->up = p;
+    rb->up = p;     p += pad16(ffn);
+    rb->hid_out = p;  p += WR_BATCH_MAX * pad16(hid);
+    rb->norm_out = p;
     return WR_OK;
+}
+
+/* ------------------------------------------------------ device model mirrors
+ *
+ * One wr_cuda_model per wr_model, shared by the model's sessions and dropped
+ * with the last of them.  The table is tiny (models per process) and touched
+ * only at session create / destroy. */
+
+typedef struct dev_model_slot {
+    const wr_model *m;
+    wr_cuda_model  *dm;
+    uint32_t        refs;
+} dev_model_slot;
+
+#define DEV_MODEL_SLOTS 16
+static dev_model_slot g_dev_models[DEV_MODEL_SLOTS];
+static volatile int   g_dev_guard;
+
+static void dev_lock(void)   { while (__atomic_exchange_n(&g_dev_guard, 1, __ATOMIC_ACQUIRE)) { } }
+static void dev_unlock(void) { __atomic_store_n(&g_dev_guard, 0, __ATOMIC_RELEASE); }
+
+static int f32_vec(const wr_tensor *t, uint32_t n)
+{
+    return t->data && t->dtype == WR_DTYPE_F32 && t->size_bytes >= (uint64_t)n * 4u;
+}
+
+/* a [in -> out] projection kept as F32 in GGML layout (out rows of in floats) */
+static int f32_ggml(const wr_tensor *t, uint32_t in, uint32_t out)
+{
+    return t->data && t->dtype == WR_DTYPE_F32 && (t->flags & WR_TENSOR_GGML_WEIGHT) && t->ndim == 2 &&
+           t->shape[0] == in && t->shape[1] == out && t->size_bytes >= (uint64_t)in * out * 4u;
+}
+
+/* Can the device stack run this model as it sits in memory? */
+static int device_glue_covers(const wr_model *m)
+{
+    const char *mode = getenv("WR_B200_GLUE");
+    if (mode && strcmp(mode, "host") == 0) return 0;
+    const uint32_t hid = m->hidden_dim, hd = m->head_dim, nq = m->n_q_heads * hd, nkv = m->n_kv_heads * hd;
+    if ((hid & 3u) || (hd & 3u) || m->n_layers > WR_CUDA_MAX_LAYERS) return 0;
+    if (!(m->embed_table.data && m->embed_table.dtype == WR_DTYPE_F32 && m->embed_table.ndim == 2 &&
+          m->embed_table.shape[0] == m->vocab_size && m->embed_table.shape[1] == hid))
+        return 0;
+    if (!(m->lm_head.data && m->lm_head.dtype == WR_DTYPE_F32 && m->lm_head.ndim == 2 &&
+          m->lm_head.shape[0] == m->vocab_size && m->lm_head.shape[1] == hid))
+        return 0;
+    if (!f32_vec(&m->final_norm, hid)) return 0;
+    for (uint32_t L = 0; L < m->n_layers; L++) {
+        const uint32_t ffn = m->ffn_dim_per_layer[L] ? m->ffn_dim_per_layer[L] : m->ffn_dim;
+        if (ffn == 0 || (ffn & 3u)) return 0;
+        if (!f32_vec(&m->attn_norm[L], hid) || !f32_vec(&m->ffn_norm[L], hid)) return 0;
+        if (!f32_ggml(&m->wq[L], hid, nq) || !f32_ggml(&m->wk[L], hid, nkv) ||
+            !f32_ggml(&m->wv[L], hid, nkv) || !f32_ggml(&m->wo[L], nq, hid) ||
+            !f32_ggml(&m->w_gate[L], hid, ffn) || !f32_ggml(&m->w_up[L], hid, ffn) ||
+            !f32_ggml(&m->w_down[L], ffn, hid))
+            return 0;
+        const int qk = m->has_qk_norm && m->q_norm[L].data && m->k_norm[L].data;
+        if (qk && (!f32_vec(&m->q_norm[L], hd) || !f32_vec(&m->k_norm[L], hd))) return 0;
+    }
+    return 1;
+}
+
+static wr_cuda_model *dev_model_acquire(const wr_model *m, wr_cuda_ctx *cuda)
+{
+    if (!device_glue_covers(m)) return NULL;
+    wr_cuda_model *dm = NULL;
+    dev_lock();
+    dev_model_slot *free_slot = NULL;
+    for (int i = 0; i < DEV_MODEL_SLOTS; i++) {
+        if (g_dev_models[i].m == m && g_dev_models[i].dm) {
+            g_dev_models[i].refs++;
+            dm = g_dev_models[i].dm;
+            break;
+        }
+        if (!g_dev_models[i].dm && !free_slot) free_slot = &g_dev_models[i];
+    }
+    if (!dm && free_slot) {
+        wr_cuda_layer_desc *layers = calloc(m->n_layers, sizeof(*layers));
+        if (layers) {
+            wr_cuda_model_desc d;
+            memset(&d, 0, sizeof(d));
+            d.n_layers = m->n_layers; d.hidden = m->hidden_dim; d.n_q_heads = m->n_q_heads;
+            d.n_kv_heads = m->n_kv_heads; d.head_dim = m->head_dim; d.vocab = m->vocab_size;
+            d.n_rot_pairs = m->n_rot_pairs; d.max_rows = WR_B200_ROWS_MAX;
+            d.rms_eps = m->rms_eps;
+            d.rope_theta = (m->rope_freq_base > 0.0f) ? m->rope_freq_base : 10000.0f;
+            d.attn_scale = (m->attn_scale > 0.0f) ? m->attn_scale : 0.0f;
+            d.embed = m->embed_table.data; d.lm_head = m->lm_head.data; d.final_norm = m->final_norm.data;
+            d.layers = layers;
+            for (uint32_t L = 0; L < m->n_layers; L++) {
+                wr_cuda_layer_desc *l = &layers[L];
+                const int qk = m->has_qk_norm && m->q_norm[L].data && m->k_norm[L].data;
+                l->attn_norm = m->attn_norm[L].data; l->wq = m->wq[L].data; l->wk = m->wk[L].data;
+                l->wv = m->wv[L].data; l->wo = m->wo[L].data; l->ffn_norm = m->ffn_norm[L].data;
+                l->w_gate = m->w_gate[L].data; l->w_up = m->w_up[L].data; l->w_down = m->w_down[L].data;
+                l->q_norm = qk ? m->q_norm[L].data : NULL;
+                l->k_norm = qk ? m->k_norm[L].data : NULL;
+                l->ffn_dim = m->ffn_dim_per_layer[L] ? m->ffn_dim_per_layer[L] : m->ffn_dim;
+            }
+            int rc = wr_cuda_model_create(cuda, &d, &dm);
+            free(layers);
+            if (rc == 0) {
+                free_slot->m = m; free_slot->dm = dm; free_slot->refs = 1;
+                wri_log_msg(2, "b200 session: layer glue on the device (%" PRIu64 " MiB of weights and scratch)",
+                            wr_cuda_model_bytes(dm) >> 20);
+            } else {
+                dm = NULL;
+                wri_log_msg(1, "b200 session: device mirror of the weights failed (rc=%d); the layer glue "
+                               "stays on the host, attention on the device", rc);
+            }
+        }
+    }
+    dev_unlock();
+    return dm;
+}
+
+static void dev_model_release(wr_cuda_model *dm)
+{
+    if (!dm) return;
+    wr_cuda_model *drop = NULL;
+    dev_lock();
+    for (int i = 0; i < DEV_MODEL_SLOTS; i++)
+        if (g_dev_models[i].dm == dm) {
+            if (--g_dev_models[i].refs == 0) {
+                drop = dm;
+                memset(&g_dev_models[i], 0, sizeof(g_dev_models[i]));
+            }
+            break;
+        }
+    dev_unlock();
+    if (drop) wr_cuda_model_destroy(drop);
 }
 
 wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_session **out)
@@ -190,8 +336,12 @@ wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_ses
     const size_t nq = (size_t)m->n_q_heads * hd, nkv = (size_t)m->n_kv_heads * hd;
     const size_t total = pad16(hid) * 3 + pad16(nq) * 2 + pad16(nkv) * 2 + pad16(ffn) * 2 +
                          pad16(m->vocab_size);
-    bs->host = aligned_alloc(64, total * sizeof(float));
-    if (!bs->host) { wr_mutex_destroy(s->lock); free(bs); return WR_ERR_NOMEM; }
+    /* page-locked: the device pass writes logits / hidden rows straight into these tensors */
+    void *host_block = NULL;
+    if (wr_cuda_host_alloc(cuda, total * sizeof(float), &host_block) != 0 || !host_block) {
+        wr_mutex_destroy(s->lock); free(bs); return WR_ERR_NOMEM;
+    }
+    bs->host = host_block;
     memset(bs->host, 0, total * sizeof(float));
     float *p = bs->host;
     f32_tensor(&s->residual, p, 1, hid, 0, 0);                 p += pad16(hid);
@@ -215,11 +365,12 @@ wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_ses
     }
     if (rc != 0) {
         wri_log_msg(0, "b200 session: device KV / row scratch allocation failed (rc=%d)", rc);
-        free(bs->host);
+        wr_cuda_host_free(cuda, bs->host);
         wr_mutex_destroy(s->lock);
         free(bs);
         return (wr_status)rc;
     }
+    bs->dm = dev_model_acquire(m, cuda);
     wr_mutex_lock(m->lock);
     m->session_refs++;
     wr_mutex_unlock(m->lock);
@@ -237,9 +388,10 @@ void wr_session_destroy(wr_session *s)
         if (m->session_refs > 0) m->session_refs--;
         wr_mutex_unlock(m->lock);
     }
+    dev_model_release(bs->dm);
     if (bs->kv) wr_cuda_kv_destroy(bs->kv);
     if (bs->rb.block) wr_cuda_host_free(bs->cuda, bs->rb.block);
-    free(bs->host);
+    if (bs->host) wr_cuda_host_free(bs->cuda, bs->host);
     if (s->lock) wr_mutex_destroy(s->lock);
     free(bs);
 }
@@ -398,16 +550,71 @@ static wr_status finish_row(wr_session *s, const float *resid_row, int compute_l
     return WR_OK;
 }
 
-/* One token of one session, without the LM head; pos is not advanced.
- * Kept as an external symbol because the reference exports it. */
-wr_status wri_session_decode_body(wr_session *s, uint32_t token)
+/* The same pass with the layer glue on the device: one call, token ids in,
+ * results for rows [out_from, R) out.  outs[i] is the session that receives row
+ * out_from+i: its residual / normed tensors, and its logits when want_logits. */
+static wr_status forward_device(const wr_model *m, wr_cuda_model *dm, row_buffers *rb, uint32_t R,
+                                const uint32_t *tokens, wr_cuda_kv *const *kvs, const uint32_t *pos,
+                                int mode, uint32_t out_from, wr_session *const *outs, int want_logits)
+{
+    if (R == 0 || R > rb->rows || out_from > R || R - out_from > WR_BATCH_MAX) return WR_ERR_INTERNAL;
+    int crc = 0;
+    wr_cuda_ctx *cuda = cuda_ctx(&crc);
+    if (!cuda) return (crc < 0) ? (wr_status)crc : WR_ERR_UNSUPPORTED;
+    const uint32_t hid = m->hidden_dim, nq = m->n_q_heads * m->head_dim, n_out = R - out_from;
+    float *logit_ptrs[WR_BATCH_MAX];
+    for (uint32_t i = 0; i < n_out; i++) logit_ptrs[i] = want_logits ? (float *)outs[i]->logits.data : NULL;
+    float *tap = NULL;
+    if (g_attn_tap) {
+        tap = malloc((size_t)m->n_layers * R * nq * sizeof(float));
+        if (!tap) return WR_ERR_NOMEM;
+    }
+    int rc = wr_cuda_model_forward(cuda, dm, mode == ATTN_DECODE ? WR_CUDA_FWD_DECODE : WR_CUDA_FWD_PREFILL,
+                                   R, kvs, pos, tokens, out_from, n_out ? rb->hid_out : NULL,
+                                   n_out ? rb->norm_out : NULL, (want_logits && n_out) ? logit_ptrs : NULL,
+                                   NULL, tap);
+    if (rc != 0) {
+        free(tap);
+        return fail("device forward pass", 0, rc);
+    }
+    /* what the host ops would have counted (kernels.c:990-991, :1423) */
+    WRI_CTR_ADD(WR_CTR_ATTENTION_CALLS, (uint64_t)R * m->n_layers);
+    WRI_CTR_ADD(WR_CTR_MATMUL_CALLS, (uint64_t)R * m->n_layers * 7u + (want_logits ? n_out : 0u));
+    if (tap) {
+        for (uint32_t L = 0; L < m->n_layers; L++)
+            for (uint32_t r = 0; r < R; r++)
+                g_attn_tap(g_attn_tap_user, L, mode == ATTN_DECODE ? pos[r] : pos[0] + r,
+                           tap + ((size_t)L * R + r) * nq, nq);
+        free(tap);
+    }
+    for (uint32_t i = 0; i < n_out; i++) {
+        memcpy(outs[i]->residual.data, rb->hid_out + (size_t)i * hid, (size_t)hid * 4u);
+        memcpy(outs[i]->normed.data, rb->norm_out + (size_t)i * hid, (size_t)hid * 4u);
+    }
+    return WR_OK;
+}
+
+/* One token of one session (the row's results land in the session's tensors). */
+static wr_status step_one(wr_session *s, uint32_t token, int compute_logits)
 {
     row_buffers *rb = &priv(s)->rb;
     wr_cuda_kv *kv = priv(s)->kv;
     uint32_t pos = s->pos;
+    if (priv(s)->dm) {
+        if (token >= s->model->vocab_size) return WR_ERR_INVAL;
+        return forward_device(s->model, priv(s)->dm, rb, 1, &token, &kv, &pos, ATTN_DECODE, 0, &s,
+                              compute_logits);
+    }
     wr_status st = forward_rows(s->model, rb, 1, &token, &kv, &pos, ATTN_DECODE);
-    if (st == WR_OK) st = finish_row(s, rb->resid, 0);
+    if (st == WR_OK) st = finish_row(s, rb->resid, compute_logits);
     return st;
+}
+
+/* One token of one session, without the LM head; pos is not advanced.
+ * Kept as an external symbol because the reference exports it. */
+wr_status wri_session_decode_body(wr_session *s, uint32_t token)
+{
+    return step_one(s, token, 0);
 }
 
 wr_status wri_session_step(wr_session *s, uint32_t token, int compute_logits)
@@ -418,11 +625,7 @@ wr_status wri_session_step(wr_session *s, uint32_t token, int compute_logits)
     if (s->pos >= s->max_context) {
         st = WR_ERR_CTX_FULL;                       /* consumed nothing */
     } else {
-        row_buffers *rb = &priv(s)->rb;
-        wr_cuda_kv *kv = priv(s)->kv;
-        uint32_t pos = s->pos;
-        st = forward_rows(s->model, rb, 1, &token, &kv, &pos, ATTN_DECODE);
-        if (st == WR_OK) st = finish_row(s, rb->resid, compute_logits);
+        st = step_one(s, token, compute_logits);
         if (st == WR_OK) __atomic_store_n(&s->pos, s->pos + 1, __ATOMIC_RELEASE);
     }
     __atomic_store_n(&s->last_status, st, __ATOMIC_RELEASE);
@@ -446,11 +649,33 @@ int wri_session_prefill(wr_session *s, const uint32_t *ids, uint32_t n)
         const int by_token = (mode && strcmp(mode, "decode") == 0) || s->model->head_dim != 128;
         wr_cuda_kv *kv = priv(s)->kv;
         row_buffers *rb = &priv(s)->rb;
-        if (by_token) {
+        wr_cuda_model *dm = priv(s)->dm;
+        if (dm) {
+            for (uint32_t i = 0; i < n && st == WR_OK; i++)
+                if (ids[i] >= s->model->vocab_size) st = WR_ERR_INVAL;   /* before anything is appended */
+        }
+        if (st != WR_OK) {
+            /* refused */
+        } else if (by_token) {
             uint32_t pos = s->pos;
-            for (uint32_t i = 0; st == WR_OK && i < n; i++, pos++)
-                st = forward_rows(s->model, rb, 1, &ids[i], &kv, &pos, ATTN_DECODE);
-            if (st == WR_OK) st = finish_row(s, rb->resid, 0);
+            for (uint32_t i = 0; st == WR_OK && i < n; i++, pos++) {
+                if (dm)
+                    st = forward_device(s->model, dm, rb, 1, &ids[i], &kv, &pos, ATTN_DECODE,
+                                        (i + 1 == n) ? 0u : 1u, &s, 0);
+                else
+                    st = forward_rows(s->model, rb, 1, &ids[i], &kv, &pos, ATTN_DECODE);
+            }
+            if (st == WR_OK && !dm) st = finish_row(s, rb->resid, 0);
+        } else if (dm) {
+            uint32_t done = 0;
+            while (st == WR_OK && done < n) {
+                const uint32_t cnt = (n - done < rb->rows) ? n - done : rb->rows;
+                uint32_t pos = s->pos + done;
+                const int last_chunk = (done + cnt == n);
+                st = forward_device(s->model, dm, rb, cnt, ids + done, &kv, &pos, ATTN_PREFILL,
+                                    last_chunk ? cnt - 1 : cnt, &s, 0);
+                done += cnt;
+            }
         } else {
             /* chunks of at most rb->rows tokens: rows are independent, key tiles absolute */
             uint32_t done = 0, last = 0;
@@ -510,9 +735,19 @@ int wri_batch_decode_step(wr_session *const *sessions, const uint32_t *tokens, u
         wr_cuda_kv *kvs[WR_BATCH_MAX];
         uint32_t pos[WR_BATCH_MAX];
         for (uint32_t i = 0; i < n; i++) { kvs[i] = priv(sessions[i])->kv; pos[i] = sessions[i]->pos; }
-        st = forward_rows(m, rb, n, tokens, kvs, pos, ATTN_DECODE);    /* all sessions, one grid per layer */
-        for (uint32_t i = 0; i < n && st == WR_OK; i++)
-            st = finish_row(sessions[i], rb->resid + (size_t)i * pad16(m->hidden_dim), 1);
+        wr_cuda_model *dm = priv(order[0])->dm;
+        for (uint32_t i = 0; i < n && dm; i++)
+            if (priv(sessions[i])->dm != dm) dm = NULL;
+        if (dm) {
+            for (uint32_t i = 0; i < n && st == WR_OK; i++)
+                if (tokens[i] >= m->vocab_size) st = WR_ERR_INVAL;
+            if (st == WR_OK)
+                st = forward_device(m, dm, rb, n, tokens, kvs, pos, ATTN_DECODE, 0, sessions, 1);
+        } else {
+            st = forward_rows(m, rb, n, tokens, kvs, pos, ATTN_DECODE);    /* all sessions, one grid per layer */
+            for (uint32_t i = 0; i < n && st == WR_OK; i++)
+                st = finish_row(sessions[i], rb->resid + (size_t)i * pad16(m->hidden_dim), 1);
+        }
     }
     if (st == WR_OK)
         for (uint32_t i = 0; i < n; i++)
