@@ -169,3 +169,85 @@ def test_argmax_takes_the_first_maximum_and_bad_tokens_are_refused():
     kv.close()
     dm.close()
     ctx.close()
+
+
+def _prefill(dm, kv, tokens, chunk=64):
+    done = 0
+    while done < len(tokens):
+        part = tokens[done:done + chunk]
+        dm.forward(dm.FWD_PREFILL, [kv], [done], part, out_from=len(part))
+        done += len(part)
+
+
+def test_short_context_step_kernel_matches_the_three_kernel_path(monkeypatch):
+    """Sessions of at most 1024 keys take QK-norm + RoPE + append + attention in one
+    kernel; the same steps through head-norm / append / split-KV decode kernels must
+    store the same cache bytes (layer 0, whose inputs are identical) and give the
+    same logits within the attention tolerance."""
+    import wayruntime_b200 as wr
+    ctx = wr.Context(0)
+    shape = dict(SHAPE, n_layers=2)
+    w = _weights(shape, 905)
+    dm = _model(ctx, w, shape, max_rows=64)
+    lens = [5, 70, 130]
+    out = {}
+    for mode in ("one_kernel", "three_kernels"):
+        if mode == "three_kernels":
+            monkeypatch.setenv("WR_CUDA_STEP_SMALL_OFF", "1")
+        kvs = [ctx.kv_create(2, shape["n_kv_heads"], shape["head_dim"], 256) for _ in lens]
+        for kv, n in zip(kvs, lens):
+            _prefill(dm, kv, [(13 * i + n) % shape["vocab"] for i in range(n)])
+        steps = []
+        for t in range(3):
+            toks = [(7 * i + t + 1) % shape["vocab"] for i in range(len(lens))]
+            steps.append(dm.forward(dm.FWD_DECODE, kvs, [n + t for n in lens], toks, logits=True, attn_tap=True))
+        rows = [(kv.read_rows(0, 0, n, 3), kv.read_rows(0, 1, n, 3)) for kv, n in zip(kvs, lens)]
+        out[mode] = (steps, rows)
+        for kv in kvs:
+            kv.close()
+    monkeypatch.delenv("WR_CUDA_STEP_SMALL_OFF")
+    for (ka, va), (kb, vb) in zip(out["one_kernel"][1], out["three_kernels"][1]):
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)            # cache bytes of layer 0
+    for a, b in zip(out["one_kernel"][0], out["three_kernels"][0]):
+        assert np.abs(a["attn"][0] - b["attn"][0]).max() <= 2e-3
+        assert np.abs(a["logits"] - b["logits"]).max() <= 2e-3 * max(1.0, np.abs(b["logits"]).max())
+    dm.close()
+    ctx.close()
+
+
+def test_mixed_short_and_long_sessions_in_one_batch_stay_byte_equal_to_serial():
+    """Sessions beyond 1024 keys keep the split-KV kernels; a batch that mixes both
+    kinds reorders its rows internally.  Every row must still carry the bits it has
+    when its session steps alone."""
+    import wayruntime_b200 as wr
+    ctx = wr.Context(0)
+    shape = dict(SHAPE)
+    w = _weights(shape, 906)
+    dm = _model(ctx, w, shape, max_rows=256)
+    lens = [1100, 10, 1300, 3, 1024]
+    toks = [(31 * i + 7) % shape["vocab"] for i in range(len(lens))]
+
+    def sessions():
+        kvs = [ctx.kv_create(1, shape["n_kv_heads"], shape["head_dim"], 1536) for _ in lens]
+        for kv, n in zip(kvs, lens):
+            _prefill(dm, kv, [(11 * i + n) % shape["vocab"] for i in range(n)], chunk=256)
+        return kvs
+
+    a = sessions()
+    serial = [dm.forward(dm.FWD_DECODE, [kv], [n], [t], logits=True, hidden=True, argmax=True)
+              for kv, n, t in zip(a, lens, toks)]
+    b = sessions()
+    batched = dm.forward(dm.FWD_DECODE, b, lens, toks, logits=True, hidden=True, argmax=True, normed=True)
+    for i in range(len(lens)):
+        assert np.array_equal(batched["logits"][i].view(np.uint32), serial[i]["logits"][0].view(np.uint32)), i
+        assert np.array_equal(batched["hidden"][i].view(np.uint32), serial[i]["hidden"][0].view(np.uint32)), i
+        assert batched["argmax"][i] == serial[i]["argmax"][0]
+    # a partial output range on a reordered batch: rows 2.. only
+    c = sessions()
+    part = dm.forward(dm.FWD_DECODE, c, lens, toks, out_from=2, logits=True, argmax=True)
+    for i in range(2, len(lens)):
+        assert np.array_equal(part["logits"][i - 2].view(np.uint32), serial[i]["logits"][0].view(np.uint32)), i
+    for kv in a + b + c:
+        kv.close()
+    dm.close()
+    ctx.close()

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libwr_cuda.so")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 
 SOURCES = ["kv_cache.cu", "attn_decode.cu", "attn_decode_static.cu", "attn_prefill.cu", "attn_exchange.cu",
-           "model_glue.cu"]
+           "model_glue.cu", "attn_step_small.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

@@ -24,6 +24,7 @@
 // row RMSNorm; arg-max with the reference's tie rule (first maximum wins,
 // src/cli/wayrt.c:805-812).
 #include <math.h>
+#include <stdlib.h>
 
 #include <chrono>
 
@@ -754,10 +755,34 @@ extern "C" int wr_cuda_model_forward(wr_cuda_ctx *ctx, wr_cuda_model *m, int mod
     const auto t_begin = std::chrono::steady_clock::now();
     cudaStream_t st = ctx->stream;
     const uint32_t hid = m->hidden, nq = m->n_q * m->hd, nkv = m->n_kv * m->hd;
+
+    // Decode rows are processed in an order of their own: the sessions that the one-kernel
+    // short-context step covers first, the others after them, so that each kind is a contiguous
+    // block of rows.  Which kind a session is depends on that session alone.  perm[i] = caller's row.
+    uint32_t perm[WR_CUDA_BATCH_MAX], pos_p[WR_CUDA_BATCH_MAX], n_short = 0;
+    wr_cuda_kv *kv_p[WR_CUDA_BATCH_MAX];
+    bool permuted = false;
+    if (mode == WR_CUDA_FWD_DECODE) {
+        const bool use_small = (getenv("WR_CUDA_STEP_SMALL_OFF") == nullptr);
+        uint32_t n = 0;
+        for (int pass = 0; pass < 2; ++pass)
+            for (uint32_t r = 0; r < n_rows; ++r) {
+                const bool small = use_small && wr_step_small_covers(kv[r], m->n_q, positions[r]);
+                if (small == (pass == 0)) perm[n++] = r;
+            }
+        for (uint32_t i = 0; i < n_rows; ++i) {
+            if (perm[i] != i) permuted = true;
+            kv_p[i] = kv[perm[i]];
+            pos_p[i] = positions[perm[i]];
+            if (use_small && wr_step_small_covers(kv_p[i], m->n_q, pos_p[i])) n_short = i + 1;
+            if (pos_p[i] >= kv_p[i]->max_ctx) return WR_CUDA_ERR_CTX_FULL;
+        }
+    }
     {
         std::lock_guard<std::mutex> g(ctx->lock);
         WR_CUDA_TRY(cudaSetDevice(ctx->device));
-        for (uint32_t r = 0; r < n_rows; ++r) m->h_tokens[r] = tokens[r];
+        for (uint32_t r = 0; r < n_rows; ++r)
+            m->h_tokens[r] = tokens[mode == WR_CUDA_FWD_DECODE ? perm[r] : r];
         WR_CUDA_TRY(cudaMemcpyAsync(m->tokens, m->h_tokens, n_rows * sizeof(uint32_t),
                                     cudaMemcpyHostToDevice, st));
         embed_rows_kernel<<<n_rows, 128, 0, st>>>(m->tokens, m->embed, m->resid, hid);
@@ -778,19 +803,29 @@ extern "C" int wr_cuda_model_forward(wr_cuda_ctx *ctx, wr_cuda_model *m, int mod
             p.norm_w = l.attn_norm; p.eps = m->eps;
             rc = gemv(m, p, nq + 2 * nkv);
             if (rc != WR_CUDA_OK) return rc;
-            if (l.q_norm) {
-                const uint32_t n_a = n_rows * m->n_q, n_b = n_rows * m->n_kv;
-                head_rmsnorm_kernel<<<(n_a + n_b + 3) / 4, 128, 0, st>>>(m->q, l.q_norm, n_a, m->k, l.k_norm,
-                                                                       n_b, m->hd, m->eps);
+            const uint32_t r_lo = (mode == WR_CUDA_FWD_DECODE) ? n_short : 0;    // rows of the three-kernel path
+            if (l.q_norm && r_lo < n_rows) {
+                const uint32_t n_a = (n_rows - r_lo) * m->n_q, n_b = (n_rows - r_lo) * m->n_kv;
+                head_rmsnorm_kernel<<<(n_a + n_b + 3) / 4, 128, 0, st>>>(m->q + (size_t)r_lo * nq, l.q_norm, n_a,
+                                                                       m->k + (size_t)r_lo * nkv, l.k_norm, n_b,
+                                                                       m->hd, m->eps);
                 ++m->launches;
                 WR_CUDA_TRY(cudaGetLastError());
             }
+            if (mode == WR_CUDA_FWD_DECODE && n_short) {
+                rc = wr_step_small_launch(ctx, n_short, kv_p, L, pos_p, m->q, m->k, m->v, m->attn, m->n_q,
+                                          m->theta, m->n_rot, l.q_norm, l.k_norm, m->eps, m->scale);
+                if (rc != WR_CUDA_OK) return rc;
+            }
         }
         if (mode == WR_CUDA_FWD_DECODE) {
-            rc = wr_cuda_decode_step(ctx, n_rows, kv, L, positions, m->q, m->k, m->v, m->attn, m->n_q,
-                                     m->theta, m->n_rot, WR_CUDA_APPEND_ROPE, m->scale, 0,
-                                     WR_CUDA_MEM_DEVICE);
-            if (rc != WR_CUDA_OK) return rc;
+            if (n_short < n_rows) {
+                rc = wr_cuda_decode_step(ctx, n_rows - n_short, kv_p + n_short, L, pos_p + n_short,
+                                         m->q + (size_t)n_short * nq, m->k + (size_t)n_short * nkv,
+                                         m->v + (size_t)n_short * nkv, m->attn + (size_t)n_short * nq, m->n_q,
+                                         m->theta, m->n_rot, WR_CUDA_APPEND_ROPE, m->scale, 0, WR_CUDA_MEM_DEVICE);
+                if (rc != WR_CUDA_OK) return rc;
+            }
         } else {
             rc = wr_cuda_kv_append(ctx, 1, kv, L, positions, n_rows, m->k, m->v, m->q, m->n_q, m->theta,
                                    m->n_rot, WR_CUDA_APPEND_ROPE, WR_CUDA_MEM_DEVICE);
@@ -801,9 +836,16 @@ extern "C" int wr_cuda_model_forward(wr_cuda_ctx *ctx, wr_cuda_model *m, int mod
         }
         {
             std::lock_guard<std::mutex> g(ctx->lock);
-            if (attn_tap_out)
-                WR_CUDA_TRY(cudaMemcpyAsync(attn_tap_out + (size_t)L * n_rows * nq, m->attn,
-                                            (size_t)n_rows * nq * 4, cudaMemcpyDeviceToHost, st));
+            if (attn_tap_out) {
+                float *dst = attn_tap_out + (size_t)L * n_rows * nq;
+                if (!permuted) {
+                    WR_CUDA_TRY(cudaMemcpyAsync(dst, m->attn, (size_t)n_rows * nq * 4, cudaMemcpyDeviceToHost, st));
+                } else {
+                    for (uint32_t i = 0; i < n_rows; ++i)
+                        WR_CUDA_TRY(cudaMemcpyAsync(dst + (size_t)perm[i] * nq, m->attn + (size_t)i * nq,
+                                                    (size_t)nq * 4, cudaMemcpyDeviceToHost, st));
+                }
+            }
             GemvParams p{};
             p.seg[0] = {l.wo, m->resid, hid, hid};
             p.n_seg = 1;
@@ -832,47 +874,76 @@ extern "C" int wr_cuda_model_forward(wr_cuda_ctx *ctx, wr_cuda_model *m, int mod
         }
     }
     std::lock_guard<std::mutex> g(ctx->lock);
-    const float *res_out = m->resid + (size_t)out_from * hid;
-    if (hidden_out && n_out)
-        WR_CUDA_TRY(cudaMemcpyAsync(hidden_out, res_out, (size_t)n_out * hid * 4, cudaMemcpyDeviceToHost, st));
+    // Device rows [o_lo, n_rows) are finished (final norm, LM head); device row i is the caller's row
+    // perm[i] when the decode rows were reordered, and then every row is finished and only the asked
+    // ones are copied out.
+    const uint32_t o_lo = permuted ? 0u : out_from, n_fin = n_rows - o_lo;
+    auto caller_row = [&](uint32_t i) { return permuted ? perm[i] : i; };
+    if ((logits_out || argmax_out) && n_fin > kLogitRowsMax) return WR_CUDA_ERR_LIMIT;
+    const float *res_out = m->resid + (size_t)o_lo * hid;
+    if (hidden_out && n_out) {
+        if (!permuted) {
+            WR_CUDA_TRY(cudaMemcpyAsync(hidden_out, res_out, (size_t)n_out * hid * 4, cudaMemcpyDeviceToHost, st));
+        } else {
+            for (uint32_t i = 0; i < n_rows; ++i)
+                if (perm[i] >= out_from)
+                    WR_CUDA_TRY(cudaMemcpyAsync(hidden_out + (size_t)(perm[i] - out_from) * hid,
+                                                m->resid + (size_t)i * hid, (size_t)hid * 4,
+                                                cudaMemcpyDeviceToHost, st));
+        }
+    }
     if ((normed_out || logits_out || argmax_out) && n_out) {
         // the final norm of at most 16 rows is kept for the LM head; more rows (normed_out only) go in passes
-        for (uint32_t done = 0; done < n_out; done += kLogitRowsMax) {
-            const uint32_t nr = (n_out - done < kLogitRowsMax) ? n_out - done : kLogitRowsMax;
+        for (uint32_t done = 0; done < n_fin; done += kLogitRowsMax) {
+            const uint32_t nr = (n_fin - done < kLogitRowsMax) ? n_fin - done : kLogitRowsMax;
             rmsnorm_rows_kernel<<<nr, 256, 0, st>>>(res_out + (size_t)done * hid, hid, m->final_norm, m->normed,
                                                     hid, hid, m->eps);
             ++m->launches;
             WR_CUDA_TRY(cudaGetLastError());
-            if (normed_out)
-                WR_CUDA_TRY(cudaMemcpyAsync(normed_out + (size_t)done * hid, m->normed, (size_t)nr * hid * 4,
-                                            cudaMemcpyDeviceToHost, st));
+            if (normed_out) {
+                if (!permuted) {
+                    WR_CUDA_TRY(cudaMemcpyAsync(normed_out + (size_t)done * hid, m->normed, (size_t)nr * hid * 4,
+                                                cudaMemcpyDeviceToHost, st));
+                } else {
+                    for (uint32_t i = 0; i < nr; ++i)
+                        if (perm[done + i] >= out_from)
+                            WR_CUDA_TRY(cudaMemcpyAsync(normed_out + (size_t)(perm[done + i] - out_from) * hid,
+                                                        m->normed + (size_t)i * hid, (size_t)hid * 4,
+                                                        cudaMemcpyDeviceToHost, st));
+                }
+            }
         }
     }
     if ((logits_out || argmax_out) && n_out) {
         GemvParams p{};
         p.seg[0] = {m->lm_head, m->logits, m->vocab, m->vocab};
         p.n_seg = 1;
-        p.x = m->normed; p.x_stride = hid; p.k = hid; p.rows = n_out;
+        p.x = m->normed; p.x_stride = hid; p.k = hid; p.rows = n_fin;
         int rc = gemv(m, p, m->vocab);
         if (rc != WR_CUDA_OK) return rc;
         if (argmax_out) {
-            argmax_rows_kernel<<<n_out, 1024, 0, st>>>(m->logits, m->vocab, m->best);
+            argmax_rows_kernel<<<n_fin, 1024, 0, st>>>(m->logits, m->vocab, m->best);
             ++m->launches;
             WR_CUDA_TRY(cudaGetLastError());
-            WR_CUDA_TRY(cudaMemcpyAsync(m->h_tokens + m->max_rows, m->best, n_out * sizeof(uint32_t),
+            WR_CUDA_TRY(cudaMemcpyAsync(m->h_tokens + m->max_rows, m->best, n_fin * sizeof(uint32_t),
                                         cudaMemcpyDeviceToHost, st));
         }
         if (logits_out)
-            for (uint32_t r = 0; r < n_out; ++r)
-                if (logits_out[r])
-                    WR_CUDA_TRY(cudaMemcpyAsync(logits_out[r], m->logits + (size_t)r * m->vocab,
+            for (uint32_t i = 0; i < n_fin; ++i) {
+                const uint32_t c = caller_row(o_lo + i);
+                if (c >= out_from && logits_out[c - out_from])
+                    WR_CUDA_TRY(cudaMemcpyAsync(logits_out[c - out_from], m->logits + (size_t)i * m->vocab,
                                                 (size_t)m->vocab * 4, cudaMemcpyDeviceToHost, st));
+            }
     }
     m->last_enqueue_ns = (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(
                              std::chrono::steady_clock::now() - t_begin).count();
     int rc = wr_ctx_sync_checked(ctx);
     if (rc != WR_CUDA_OK) return rc;
     if (argmax_out)
-        for (uint32_t r = 0; r < n_out; ++r) argmax_out[r] = m->h_tokens[m->max_rows + r];
+        for (uint32_t i = 0; i < n_fin; ++i) {
+            const uint32_t c = caller_row(o_lo + i);
+            if (c >= out_from) argmax_out[c - out_from] = m->h_tokens[m->max_rows + i];
+        }
     return WR_CUDA_OK;
 }

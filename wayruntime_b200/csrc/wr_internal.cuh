@@ -148,6 +148,15 @@ int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
                      uint32_t n_rot_pairs, uint32_t flags,
                      const float *dq_in /* null: rotate dq in place */);
 
+// One-kernel layer-step for short contexts (attn_step_small.cu): QK-norm, RoPE, append and the
+// new token's attention, for sessions of head_dim 128 with at most WR_STEP_SMALL_MAX_KEYS keys.
+#define WR_STEP_SMALL_MAX_KEYS 1024u
+bool wr_step_small_covers(const wr_cuda_kv *kv, uint32_t n_q_heads, uint32_t position);
+int wr_step_small_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
+                         const uint32_t *positions, float *dq, const float *dk, const float *dv, float *dout,
+                         uint32_t n_q_heads, float theta_base, uint32_t n_rot_pairs, const float *q_norm,
+                         const float *k_norm, float eps, float scale_override);
+
 // Resolve the device addresses of the allocation-free decode path's scratch
 // arrays and set its kernels' attributes, once per device (that device current).
 int wr_static_setup(int device);
