@@ -45,8 +45,8 @@ THETA = 500000.0
 SEED = 20261125
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures
 # (profiles/): same seeded workloads as the ones timed here.
-NCU_TRAFFIC_DECODE_C2 = 170_720_000      # algorithmic 165 429 248 B
-NCU_TRAFFIC_PREFILL_C3 = 25_370_000      # operands are re-read from L2; output stays in L2
+NCU_TRAFFIC_DECODE_C2 = 171_000_000      # algorithmic 165 429 248 B
+NCU_TRAFFIC_PREFILL_C3 = 25_800_000      # operands are re-read from L2
 METRIC = "batched_decode_attention_tokens_per_s"
 UNIT = "tok/s"
 
