@@ -216,7 +216,8 @@ void wr_decode_plan(uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer, cons
 // ctx->lock and has validated the arguments.
 int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
                      const uint32_t *seq_lens, const float *dq, float *dout, uint32_t n_q,
-                     float scale_override, uint32_t window, int emit_triples, const wr_decode_xchg *xchg)
+                     float scale_override, uint32_t window, int emit_triples, const wr_decode_xchg *xchg,
+                     bool early_tiles)
 {
     const uint32_t n_kv = kv[0]->n_kv, hd = kv[0]->hd;
     const uint32_t group = n_q / n_kv;
@@ -260,10 +261,19 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
             ctx->attr_flags |= 1u;
         }
         const uint32_t grid = std::max(1u, std::min<uint32_t>(items, (uint32_t)ctx->sm_count));
+        // A grid that covers every SM (one CTA each: the kernel takes the whole register file) can
+        // only start on an SM when the CTA before it there has exited, i.e. has passed its own wait;
+        // that is what makes the early first-tile loads safe, so they need the full grid.
+        const bool full = grid == (uint32_t)ctx->sm_count;
+        p.early_tiles = (early_tiles && full) ? 1u : 0u;
+        ctx->pdl_kind = full ? WR_PDL_DECODE_FULL : WR_PDL_DECODE_PART;
+        ctx->pdl_index = ctx->launches + 1;
         if (nt == 1)
-            attn_decode_hd128_kernel<1><<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(p);
+            WR_CUDA_TRY(wr_launch_pdl(attn_decode_hd128_kernel<1>, dim3(grid), dim3(kThreads), sizeof(smem_layout),
+                                      ctx->stream, p));
         else
-            attn_decode_hd128_kernel<2><<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(p);
+            WR_CUDA_TRY(wr_launch_pdl(attn_decode_hd128_kernel<2>, dim3(grid), dim3(kThreads), sizeof(smem_layout),
+                                      ctx->stream, p));
     } else {
         generic_params p;
         for (uint32_t s = 0; s < n_sess; ++s) {
@@ -311,8 +321,12 @@ static int decode_common(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *k
         dout = (float *)((char *)ctx->stage_dev + q_bytes);
         WR_CUDA_TRY(cudaMemcpyAsync((void *)dq, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
     }
+    // Back-to-back decode launches (nothing of this library's in between, so no page is being
+    // written): the second one may request its first tiles while the first one drains.
+    const bool early = mem == WR_CUDA_MEM_DEVICE && ctx->pdl_index == ctx->launches &&
+                       ctx->pdl_kind == WR_PDL_DECODE_FULL;
     rc = wr_decode_launch(ctx, n_sess, kv, layer, seq_lens, dq, dout, n_q, scale_override, window,
-                          emit_triples, nullptr);
+                          emit_triples, nullptr, early);
     if (rc != WR_CUDA_OK) return rc;
     if (mem == WR_CUDA_MEM_HOST) {
         WR_CUDA_TRY(cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -378,11 +392,17 @@ extern "C" int wr_cuda_decode_step(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv
             WR_CUDA_TRY(cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, ctx->stream));
         }
     }
+    // Early first-tile loads in the decode kernel: the append below writes one row per session, into
+    // the session's last page, which those loads skip.  Every other page must be settled when the
+    // decode kernel's CTAs can start: true when the kernel before the append is not one of this
+    // library's early-starting kernels, or is a decode launch that covered every SM.
+    const int prev = (ctx->pdl_index == ctx->launches) ? ctx->pdl_kind : WR_PDL_NONE;
+    const bool early = prev == WR_PDL_NONE || prev == WR_PDL_DECODE_FULL;
     rc = wr_append_launch(ctx, n_sess, kv, layer, positions, 1, dk, dv, dq, n_q_heads, theta_base,
                           n_rot_pairs, flags, dq_in);
     if (rc != WR_CUDA_OK) return rc;
     rc = wr_decode_launch(ctx, n_sess, kv, layer, seq_lens, dq, dout, n_q_heads, scale_override,
-                          window, 0, nullptr);
+                          window, 0, nullptr, early);
     if (rc != WR_CUDA_OK) return rc;
     if (mem == WR_CUDA_MEM_HOST) {
         if (staged_out)

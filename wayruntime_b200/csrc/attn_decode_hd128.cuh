@@ -110,6 +110,10 @@ struct params {
     uint32_t *x_flag[WR_CUDA_XCHG_MAX_WORLD];    // per rank: this rank's step flag in that rank's buffer
     int *x_done;                                 // rows of this launch that have been stored everywhere
     uint32_t x_world, x_step;
+    // An engine may request its first K/V tile before the earlier kernels have completed, unless
+    // that tile is the session's last page (where the row appended just before this launch lands).
+    // Set by the host only where it knows that every other page is settled (wr_cuda_decode_step).
+    uint32_t early_tiles;
 };
 
 // Stores of one finished warp's rows are done: count them, and when every row of the launch
@@ -311,8 +315,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
     constexpr uint32_t kHeadsMax = 4 * NT;
     const uint32_t g = lane >> 2, t4 = lane & 3;
     const uint64_t stream_policy = l2_policy_evict_first();
+    // Let the next kernel in the stream be scheduled while this one runs (it waits for this one's
+    // completion before it touches shared state); everything up to pdl_wait() below is this
+    // kernel's own prologue, overlapped with the tail of the kernel before it.
+    pdl_trigger();
 
     if (warp >= kWarps) {
+        pdl_wait();                      // counters, scratch rows and `out` belong to earlier launches until now
         // ----------------------------------------------------------- merge warps
         // Jobs are (group, head pair) in group order, which is also roughly the
         // order in which groups complete; merge warp w of the grid takes jobs
@@ -364,6 +373,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
     // A session with no keys (an empty split-KV shard) has no items: its
     // triples are the neutral element of the merge.
     if (p.emit_triples && blockIdx.x == 0) {
+        pdl_wait();                      // `out` / the peers' buffers are written here
         for (uint32_t s = 0; s < p.n_sess; ++s) {
             if (p.n_chunks[s] != 0) continue;
             if (p.x_world > 0) {
@@ -396,7 +406,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
     ts.t = ts.t_end = 0;
     ts.s = ts.h = ts.qs = 0;
     ts.pending = 0;
-    if (lane == 0) ts.pending = draw();
     bool started = false;
     auto next_tile = [&]() -> tile_desc {
         tile_desc d;
@@ -440,14 +449,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         ++ts.t;
         return d;
     };
-    auto issue_k = [&](const tile_desc &d) {   // lane 0 only
+    // k_already: the K copy of this (first) tile was issued earlier with mbar_expect_tx_only
+    auto issue_k = [&](const tile_desc &d, bool k_already = false) {   // lane 0 only
         const char *src = d.page + wr_block_off(d.h, 0, kHd);
-        uint32_t bytes = kBlockBytes;
+        uint32_t bytes = k_already ? 0u : kBlockBytes;
         const bool first = (d.flags & 2u) != 0;
         const uint32_t heads = min(kHeadsMax, p.group - d.qs * kHeadsMax);
         if (first) bytes += heads * kHd * 4u;
         mbar_expect_tx(bar_k, bytes);
-        bulk_g2s_hint(ws.k, src, kBlockBytes, bar_k, stream_policy);
+        if (!k_already) bulk_g2s_hint(ws.k, src, kBlockBytes, bar_k, stream_policy);
         if (first) {
             const float *qsrc =
                 p.q + ((size_t)p.row[d.s] * p.n_q + d.h * p.group + d.qs * kHeadsMax) * kHd;
@@ -459,10 +469,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
         bulk_g2s_hint(ws.v, d.page + wr_block_off(d.h, 1, kHd), kBlockBytes, bar_v, stream_policy);
     };
 
+    // The engine's first tile is known without the queue.  If it is a page no kernel in flight can
+    // be writing, its K and V are requested now, while the kernels before this one finish.
     tile_desc d0 = next_tile();
-    if (lane == 0 && (d0.flags & 1u)) {
-        issue_k(d0);
+    const bool early = p.early_tiles && (d0.flags & 1u) && d0.t + 1 < p.n_tiles[d0.s];
+    if (early && lane == 0) {
+        mbar_expect_tx_only(bar_k, kBlockBytes);
+        bulk_g2s_hint(ws.k, d0.page + wr_block_off(d0.h, 0, kHd), kBlockBytes, bar_k, stream_policy);
         issue_v(d0);
+    }
+    pdl_wait();                          // Q, the new K/V rows, the queue and the scratch: after the earlier kernels
+    if (lane == 0) ts.pending = draw();
+    if (lane == 0 && (d0.flags & 1u)) {
+        issue_k(d0, early);
+        if (!early) issue_v(d0);
     }
     tile_desc d1 = next_tile();
     uint32_t uses = 0;

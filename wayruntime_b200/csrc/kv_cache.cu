@@ -470,6 +470,7 @@ __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const ap
     const uint32_t s = tok_idx / p.n_tokens, t = tok_idx % p.n_tokens;
     const uint32_t row = p.b.seq_len[s] + t;                     // absolute position = cache row
     float *cs_tab = trig, *sn_tab = trig + half;
+    pdl_trigger();                       // the decode kernel behind this one may be scheduled now
     auto build_table = [&]() {
         if (p.rope) {
             const float ln_theta = wrmath::log_ref(p.theta);
@@ -491,7 +492,11 @@ __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const ap
         const float *__restrict__ krow = p.k_rows + (size_t)tok_idx * p.n_kv * p.hd;
         const float *__restrict__ vrow = p.v_rows + (size_t)tok_idx * p.n_kv * p.hd;
         const uint32_t work = p.n_kv * half;
-        bool table_ready = false;
+        // the pair angles need nothing from earlier kernels: they are evaluated while the kernel
+        // before this one is still finishing; the rows are read after it has completed
+        build_table();
+        bool table_ready = true;
+        pdl_wait();
         for (uint32_t base = 0; base < work; base += kStep) {
             float x0[kAppendBatch], x1[kAppendBatch], v0[kAppendBatch], v1[kAppendBatch];
 #pragma unroll
@@ -535,6 +540,8 @@ __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const ap
     // ---- eight Q heads of this token: rotated in place, or from q_in into q_rows
     // (then the pairs beyond n_rot are copied through as well)
     if (!(p.q_rows && p.rope)) return;
+    build_table();
+    pdl_wait();
     const uint32_t head0 = (blockIdx.y - 1) * kAppendQHeads;
     const uint32_t n_heads = min((uint32_t)kAppendQHeads, p.n_q - head0);
     const size_t qoff = ((size_t)tok_idx * p.n_q + head0) * p.hd;
@@ -543,7 +550,7 @@ __global__ void __launch_bounds__(kAppendThreads) rope_kv_append_kernel(const ap
     const bool in_place = (p.q_in == p.q_rows);
     const uint32_t pairs = in_place ? p.n_rot : half;             // per head
     const uint32_t work = n_heads * pairs;
-    bool table_ready = false;
+    bool table_ready = true;
     for (uint32_t base = 0; base < work; base += kStep) {
         float x0[kAppendBatch], x1[kAppendBatch];
 #pragma unroll
@@ -617,8 +624,10 @@ int wr_append_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
     p.rope = (flags & WR_CUDA_APPEND_ROPE) ? 1u : 0u;
     const uint32_t q_ctas = (dq && p.rope) ? (n_q_heads + kAppendQHeads - 1) / kAppendQHeads : 0u;
     const dim3 grid(n_sess * n_tokens, 1 + q_ctas);
-    rope_kv_append_kernel<<<grid, kAppendThreads, hd * sizeof(float), ctx->stream>>>(p);
+    WR_CUDA_TRY(wr_launch_pdl(rope_kv_append_kernel, grid, dim3(kAppendThreads), hd * sizeof(float), ctx->stream, p));
     ctx->launches++;
+    ctx->pdl_kind = WR_PDL_APPEND;
+    ctx->pdl_index = ctx->launches;
     WR_CUDA_TRY(cudaGetLastError());
     return WR_CUDA_OK;
 }

@@ -89,7 +89,12 @@ struct wr_cuda_ctx {
     // SM clock cycles a device-side wait may last before the kernel gives up
     // (wr_cuda_ctx_set_wait_limit); every kernel of the context gets this value.
     long long wait_limit = WR_CUDA_WAIT_LIMIT_DEFAULT;
+    // The last kernel this context launched with programmatic dependent launch (pdl_kind), valid
+    // while pdl_index == launches (nothing of ours was launched since).
+    uint64_t pdl_index = ~0ull;
+    int pdl_kind = 0;                // WR_PDL_*
 };
+enum { WR_PDL_NONE = 0, WR_PDL_APPEND = 1, WR_PDL_DECODE_FULL = 2, WR_PDL_DECODE_PART = 3 };
 
 struct wr_cuda_kv {
     wr_cuda_ctx *ctx = nullptr;
@@ -130,7 +135,8 @@ int wr_decode_validate(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv,
                        int emit_triples);
 int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
                      const uint32_t *seq_lens, const float *dq, float *dout, uint32_t n_q,
-                     float scale_override, uint32_t window, int emit_triples, const wr_decode_xchg *xchg);
+                     float scale_override, uint32_t window, int emit_triples, const wr_decode_xchg *xchg,
+                     bool early_tiles = false);
 
 int wr_ctx_reserve_stage(wr_cuda_ctx *ctx, size_t dev_bytes, size_t host_bytes);
 // Wait for the context's stream and report (and clear) the device-side error
@@ -169,6 +175,31 @@ const void *wr_host_device_alias(const void *p);
 
 #ifdef __CUDACC__
 
+// Programmatic dependent launch.  A kernel launched with wr_launch_pdl may begin (be scheduled, run
+// its prologue) as soon as every CTA of the kernel before it in the stream has executed
+// pdl_trigger() or exited; it must execute pdl_wait() before it touches anything an earlier kernel
+// may still be reading or writing — the wait returns once the earlier kernels have completed and
+// their memory is visible.  Under an ordinary launch both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename Params>
+inline cudaError_t wr_launch_pdl(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 const Params &p)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // Reference sentinel for "no score yet" / masked keys (src/core/kernels.c:1480).
 #define WR_NEG_SENTINEL (-1e30f)
 
@@ -185,6 +216,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                  "r"(bytes)
+                 : "memory");
+}
+// Adds to the phase's pending byte count without arriving (the arrival comes with a later call).
+__device__ __forceinline__ void mbar_expect_tx_only(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
