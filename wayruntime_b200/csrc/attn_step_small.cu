@@ -66,25 +66,28 @@ __global__ void __launch_bounds__(kSmallThreads) attn_step_small_kernel(const st
     const uint32_t pos = p.b.seq_len[s], n_keys = pos + 1;
     constexpr uint32_t half = kHd / 2;
 
-    // ---- rows in
-    float *qrows = p.q + ((size_t)s * p.n_q + (size_t)kvh * G) * kHd;
-    for (uint32_t i = tid; i < G * kHd; i += kSmallThreads) sq[i / kHd][i % kHd] = qrows[i];
-    if (tid < kHd) sk[tid] = p.k[((size_t)s * p.n_kv + kvh) * kHd + tid];
-    else if (tid < 2 * kHd) sv[tid - kHd] = p.v[((size_t)s * p.n_kv + kvh) * kHd + tid - kHd];
-    // (everything a later phase needs from global memory is requested in this first round trip)
+    // ---- what does not depend on the kernel before this one (the projections): norm weights, the
+    //      session's page pointers, the pair angles of this position (kernels.c:1400-1405).  The kernel
+    //      behind this one may be scheduled meanwhile, and this part overlaps the one before.
+    pdl_trigger();
     const uint64_t *pages = p.b.pages[s];
     if (p.q_norm) {
         if (tid < kHd) s_qnw[tid] = p.q_norm[tid];
         else if (tid < 2 * kHd) s_knw[tid - kHd] = p.k_norm[tid - kHd];
     }
     if (tid < (n_keys + kPageTokens - 1) / kPageTokens) s_page[tid] = (const char *)pages[tid];
-    // pair angles of this position (kernels.c:1400-1405), while the loads land
     if (tid < p.n_rot) {
         float sn, cs;
         wrmath::rope_angle(pos, tid, kHd, wrmath::log_ref(p.theta), sn, cs);
         cs_tab[tid] = cs;
         sn_tab[tid] = sn;
     }
+    pdl_wait();
+    // ---- rows in
+    float *qrows = p.q + ((size_t)s * p.n_q + (size_t)kvh * G) * kHd;
+    for (uint32_t i = tid; i < G * kHd; i += kSmallThreads) sq[i / kHd][i % kHd] = qrows[i];
+    if (tid < kHd) sk[tid] = p.k[((size_t)s * p.n_kv + kvh) * kHd + tid];
+    else if (tid < 2 * kHd) sv[tid - kHd] = p.v[((size_t)s * p.n_kv + kvh) * kHd + tid - kHd];
     __syncthreads();
 
     // ---- per-head RMSNorm of K and of the G q heads (one warp per vector), as head_rmsnorm_kernel
@@ -298,10 +301,11 @@ int wr_step_small_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *k
     p.theta = (theta_base < 1.0f) ? 10000.0f : theta_base;                       // kernels.c:1374
     p.scale = (scale_override > 0.0f) ? scale_override : 1.0f / sqrtf((float)kHd);
     const uint32_t group = n_q_heads / p.n_kv, grid = n_sess * p.n_kv;
-    if (group == 1) attn_step_small_kernel<1><<<grid, kSmallThreads, 0, ctx->stream>>>(p);
-    else if (group == 2) attn_step_small_kernel<2><<<grid, kSmallThreads, 0, ctx->stream>>>(p);
-    else if (group <= 4) attn_step_small_kernel<4><<<grid, kSmallThreads, 0, ctx->stream>>>(p);
-    else attn_step_small_kernel<8><<<grid, kSmallThreads, 0, ctx->stream>>>(p);
+    const dim3 g3(grid), b3(kSmallThreads);
+    if (group == 1) WR_CUDA_TRY(wr_launch_pdl(attn_step_small_kernel<1>, g3, b3, 0, ctx->stream, p));
+    else if (group == 2) WR_CUDA_TRY(wr_launch_pdl(attn_step_small_kernel<2>, g3, b3, 0, ctx->stream, p));
+    else if (group <= 4) WR_CUDA_TRY(wr_launch_pdl(attn_step_small_kernel<4>, g3, b3, 0, ctx->stream, p));
+    else WR_CUDA_TRY(wr_launch_pdl(attn_step_small_kernel<8>, g3, b3, 0, ctx->stream, p));
     ctx->launches++;
     WR_CUDA_TRY(cudaGetLastError());
     return WR_CUDA_OK;

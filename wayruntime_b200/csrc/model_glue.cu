@@ -176,10 +176,13 @@ __device__ __forceinline__ void weight_rows(const GemvParams &p, const GemvSeg &
     }
 }
 
+constexpr int kPrefetchRegs = 16;        // 16-byte weight vectors a lane holds before the dependency wait
+
 template <int RG, int C>
 __global__ void __launch_bounds__(kGemvThreads) gemv_splitk_kernel(const GemvParams p)
 {
     __shared__ float red[kGemvWarps][C * RG + RG];
+    pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t r0 = blockIdx.y * RG;
     uint32_t cta = blockIdx.x, s = 0;
@@ -208,11 +211,21 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_splitk_kernel(const GemvPar
 #pragma unroll
         for (int c = 0; c < C; ++c) acc[c][r] = 0.f;
     }
-#pragma unroll 2
-    for (uint32_t v = v_lo + lane; v < v_hi; v += 32) {
-        float4 w[C];
+    // Weights do not depend on the kernel before this one: the first PV vectors of the lane's walk
+    // (all of it for K up to 512 * PV) are requested before the dependency wait, so their trip from
+    // HBM overlaps that kernel's tail; the activations are read after it.
+    constexpr int PV = kPrefetchRegs / C;
+    float4 wbuf[PV][C];
 #pragma unroll
-        for (int c = 0; c < C; ++c) w[c] = ldg_stream(wrow[c] + 4 * v);
+    for (int i = 0; i < PV; ++i) {
+        const uint32_t v = v_lo + lane + 32u * i;
+        if (v < v_hi) {
+#pragma unroll
+            for (int c = 0; c < C; ++c) wbuf[i][c] = ldg_stream(wrow[c] + 4 * v);
+        }
+    }
+    pdl_wait();
+    auto step = [&](uint32_t v, const float4 (&w)[C]) {
         float4 nw = make_float4(1.f, 1.f, 1.f, 1.f);
         if (p.norm_w) nw = *reinterpret_cast<const float4 *>(p.norm_w + 4 * v);
 #pragma unroll
@@ -225,6 +238,18 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_splitk_kernel(const GemvPar
 #pragma unroll
             for (int c = 0; c < C; ++c) acc[c][r] = dot4(w[c], xv, acc[c][r]);
         }
+    };
+#pragma unroll
+    for (int i = 0; i < PV; ++i) {
+        const uint32_t v = v_lo + lane + 32u * i;
+        if (v < v_hi) step(v, wbuf[i]);
+    }
+#pragma unroll 2
+    for (uint32_t v = v_lo + lane + 32u * PV; v < v_hi; v += 32) {
+        float4 w[C];
+#pragma unroll
+        for (int c = 0; c < C; ++c) w[c] = ldg_stream(wrow[c] + 4 * v);
+        step(v, w);
     }
     {
         constexpr int M = C * RG;
@@ -276,6 +301,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(const GemvParam
     constexpr int kPieceVec = kChunk / 4;            // 16-byte vectors of x staged per row and pass
     __shared__ __align__(16) float xs[RG][kChunk];
     __shared__ float inv_rms[RG];
+    pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t r0 = blockIdx.y * RG;
     uint32_t cta = blockIdx.x, s = 0;
@@ -289,6 +315,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(const GemvParam
     const float *wrow[NW];
     weight_rows<NW>(p, seg, n0, wrow);
     const KQuarters kq(p.k);
+    pdl_wait();
 
     if (p.norm_w) {                                  // sum of squares in the shared order
         for (int r = warp; r < RG; r += kGemvWarps) {
@@ -487,14 +514,14 @@ template <int RG, int NW>
 void launch_gemv_t(const GemvParams &p, uint32_t ctas, cudaStream_t st)
 {
     dim3 grid(ctas, (p.rows + RG - 1) / RG);
-    gemv_rows_kernel<RG, NW><<<grid, kGemvThreads, 0, st>>>(p);
+    (void)wr_launch_pdl(gemv_rows_kernel<RG, NW>, grid, dim3(kGemvThreads), 0, st, p);
 }
 
 template <int RG, int C>
 void launch_splitk_t(const GemvParams &p, uint32_t ctas, cudaStream_t st)
 {
     dim3 grid(ctas, (p.rows + RG - 1) / RG);
-    gemv_splitk_kernel<RG, C><<<grid, kGemvThreads, 0, st>>>(p);
+    (void)wr_launch_pdl(gemv_splitk_kernel<RG, C>, grid, dim3(kGemvThreads), 0, st, p);
 }
 
 template <int C>
