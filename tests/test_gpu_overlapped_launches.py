@@ -122,3 +122,38 @@ def test_back_to_back_decode_launches_match_single_launches():
     for kv in kvs:
         kv.close()
     ctx.close()
+
+
+def test_back_to_back_prefill_launches_match_single_launches():
+    """Prefill launches given F16 queries, one after another with nothing in between: the
+    later one starts its first tiles while the earlier one drains.  Same bits as alone."""
+    import torch
+    import wayruntime_b200 as wr
+    ctx = wr.Context(0)
+    P = port()
+    n, hq, hkv = 2048 + 77, 32, 8                        # 17 row tiles x 16 head pairs: more tiles than SMs
+    kvs = []
+    for i in range(2):
+        kv = ctx.kv_create(1, hkv, HD, n)
+        kv.write_rows(0, 0, 0, P.f32_to_f16(_gen.normal(7700 + i, (n, hkv, HD))))
+        kv.write_rows(0, 1, 0, P.f32_to_f16(_gen.normal(7800 + i, (n, hkv, HD))))
+        kvs.append(kv)
+    qs = [torch.from_numpy(P.f32_to_f16(_gen.normal(7900 + i, (n, hq, HD))).view(np.int16)).cuda() for i in range(2)]
+    alone = []
+    for kv, q in zip(kvs, qs):
+        out = torch.empty((n, hq, HD), device="cuda")
+        ctx.sync()
+        ctx.attn_prefill(kv, 0, 0, n, q.view(torch.float16), out, hq)
+        ctx.sync()
+        alone.append(out.cpu().numpy())
+    outs = [torch.full((n, hq, HD), float("nan"), device="cuda") for _ in range(6)]
+    for i, out in enumerate(outs):
+        ctx.attn_prefill(kvs[i % 2], 0, 0, n, qs[i % 2].view(torch.float16), out, hq)
+    ctx.sync()
+    for i, out in enumerate(outs):
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all(), i
+        assert np.array_equal(got.view(np.uint32), alone[i % 2].view(np.uint32)), i
+    for kv in kvs:
+        kv.close()
+    ctx.close()

@@ -107,6 +107,7 @@ struct prefill_params {
     uint32_t n, p0, n_q, n_kv, group, window, n_qtiles, n_tiles;
     float scale_log2;           // score scale * log2(e)
     long long wait_limit;       // SM clock cycles a device-side wait may last
+    uint32_t early;             // the kernel before this one only reads what this one reads
 };
 
 // A published work tile: up to two blocks over the same KV head.
@@ -398,6 +399,12 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
 #ifdef WR_PREFILL_TIMELINE
     if (tid == 0 && p.tl && blockIdx.x < kTlCtas) p.tl[kTlRoles * kTlEvents + blockIdx.x * 4] = tl_ns();
 #endif
+    // The next kernel in the stream may be scheduled now; this kernel's own set-up (barriers, TMEM)
+    // overlaps the kernel before it.  What that kernel may still be writing — Q, the cache rows
+    // appended for this prompt, the work counter, the output rows — is touched after pdl_wait();
+    // with p.early (the kernel before is a prefill launch too: a reader) the first tile's loads
+    // and arithmetic do not wait, only the counter and the output stores do.
+    pdl_trigger();
 
     if (warp == 8 && lane == 0) {
         mbar_init(&sm.q_full[0], 1);
@@ -417,6 +424,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
         }
         for (int i = 0; i < kTileSlots; ++i) mbar_init(&sm.tile_ready[i], 1);
         fence_barrier_init();
+        if (!p.early) pdl_wait();
         // The first tile's first loads (Q of block 0, the first K tile, Q of block 1) start
         // at once: they fly while TMEM is allocated and the other warps reach the barrier.
         const tile_info ti = decode_tile(p, blockIdx.x);
@@ -515,13 +523,17 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
                 bool claimed = false;
                 for (uint32_t j = lo + 1; j < hi && ok; ++j) {
                     if (!claimed && j + 1 >= hi) {
+                        pdl_wait();                              // the counter is the earlier launch's until it has ended
                         next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
                         claimed = true;
                     }
                     ok = load_k(j);
                 }
                 if (!ok) break;
-                if (!claimed) next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
+                if (!claimed) {
+                    pdl_wait();
+                    next_tile = gridDim.x + (uint32_t)atomicAdd(p.sched, 1);
+                }
                 ti = decode_tile(p, next_tile);
                 const uint32_t slot = (it + 1) % kTileSlots;
                 sm.tile[slot] = ti;
@@ -532,6 +544,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             if (p.tl && blockIdx.x < kTlCtas) p.tl[kTlRoles * kTlEvents + blockIdx.x * 4 + 3] = kcount;
 #endif
         } else if (lane == 1) {
+            if (!p.early) pdl_wait();
             uint32_t vcount = 0;
             bool ok = true;
             for (uint32_t it = 0; ok; ++it) {
@@ -856,6 +869,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             if (lane == 0) mbar_arrive(&sm.o_free[b]);       // the next tile may overwrite O
             // Each thread writes its own row (512 contiguous bytes) with 16-byte stores;
             // nothing is waited for, the softmax group goes straight on to its next tile.
+            pdl_wait();                                      // output rows: after the earlier kernels have ended
             if (row < me.rows) {
                 const float inv = (l > 0.f) ? 1.0f / l : 0.f;
                 float4 *dst = reinterpret_cast<float4 *>(p.out + ((size_t)(me.tok0 + row) * p.n_q + head) * kHd);
@@ -1018,8 +1032,17 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
         ctx->attr_flags |= 2u;
     }
     const uint32_t grid = std::min<uint32_t>(p.n_tiles, (uint32_t)ctx->sm_count);
-    attn_prefill_hd128_kernel<<<grid, kThreads, sizeof(smem_layout), ctx->stream>>>(q_map, p);
+    // Back-to-back prefill launches (nothing of this library's in between, Q taken as given): the
+    // earlier one only reads, and with one CTA per SM a CTA of this launch starts where one of the
+    // earlier launch has left, so its first tile need not wait for the stragglers.
+    const bool full = grid == (uint32_t)ctx->sm_count;
+    p.early = (!convert && !host && full && ctx->pdl_index == ctx->launches &&
+               ctx->pdl_kind == WR_PDL_PREFILL_FULL) ? 1u : 0u;
+    WR_CUDA_TRY(wr_launch_pdl(attn_prefill_hd128_kernel, dim3(grid), dim3(kThreads), sizeof(smem_layout), ctx->stream,
+                              q_map, p));
     ctx->launches++;
+    ctx->pdl_kind = full ? WR_PDL_PREFILL_FULL : WR_PDL_NONE;
+    ctx->pdl_index = ctx->launches;
     WR_CUDA_TRY(cudaGetLastError());
     if (host) {
         WR_CUDA_TRY(cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));

@@ -94,7 +94,7 @@ struct wr_cuda_ctx {
     uint64_t pdl_index = ~0ull;
     int pdl_kind = 0;                // WR_PDL_*
 };
-enum { WR_PDL_NONE = 0, WR_PDL_APPEND = 1, WR_PDL_DECODE_FULL = 2, WR_PDL_DECODE_PART = 3 };
+enum { WR_PDL_NONE = 0, WR_PDL_APPEND = 1, WR_PDL_DECODE_FULL = 2, WR_PDL_DECODE_PART = 3, WR_PDL_PREFILL_FULL = 4 };
 
 struct wr_cuda_kv {
     wr_cuda_ctx *ctx = nullptr;
@@ -183,9 +183,9 @@ const void *wr_host_device_alias(const void *p);
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-template <typename Params>
-inline cudaError_t wr_launch_pdl(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                 const Params &p)
+template <typename... Params>
+inline cudaError_t wr_launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 const Params &...p)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -197,7 +197,7 @@ inline cudaError_t wr_launch_pdl(void (*kernel)(Params), dim3 grid, dim3 block, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, p);
+    return cudaLaunchKernelEx(&cfg, kernel, p...);
 }
 
 // Reference sentinel for "no score yet" / masked keys (src/core/kernels.c:1480).
