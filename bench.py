@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""bench.py — batched decode attention (BASELINE config 2) on N GPUs of one node.
+"""bench.py — batched decode attention (benchmark config 2) on N GPUs of one node.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -220,7 +220,7 @@ def workload_config(n_gpus, note=None):
     return cfg
 
 
-# ------------------------------------------------- prefill (BASELINE config 3)
+# ------------------------------------------------- prefill (benchmark config 3)
 
 PF_N, PF_HQ, PF_HKV = 2048, 32, 8
 
@@ -263,7 +263,7 @@ def measure_prefill(ctx, stream, torch, reps):
             "traffic": NCU_TRAFFIC_PREFILL_C3, "output_finite": finite}
 
 
-# ------------------------------- long-context split-KV decode (BASELINE config 4)
+# ------------------------------- long-context split-KV decode (benchmark config 4)
 
 LC_CTX = 32768
 
@@ -441,7 +441,7 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
     return res
 
 
-# --------------------- KV-head-sharded serving shape (BASELINE config 5)
+# --------------------- KV-head-sharded serving shape (benchmark config 5)
 
 C5_SESS, C5_PREFILL, C5_HKV, C5_GROUP = 8, 8192, 8, 5
 
@@ -538,7 +538,7 @@ WHOLE_MODEL_PROMPT, WHOLE_MODEL_TOKENS = 64, 32
 
 
 def measure_whole_model():
-    """BASELINE config 1 end to end through the public C API, `wayrt bench` style
+    """benchmark config 1 end to end through the public C API, `wayrt bench` style
     (src/cli/wayrt.c:694-854: prefill all prompt tokens but the last, then N
     greedy steps, wall clock around each phase), on a seeded GGUF of the
     Qwen3-0.6B shape: the unmodified reference library on the host cores, the

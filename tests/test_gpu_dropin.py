@@ -9,13 +9,15 @@ is the unmodified reference.  Both are driven through the reference's public API
   * teacher-forced greedy decoding, with the layer glue on the device (the
     default) and on the host (WR_B200_GLUE=host), the prompt through the prefill
     kernel and token by token: identical argmax at every step, logits
-    within tolerance (BASELINE config 1: Qwen3-0.6B shape, 64-token prompt),
+    within tolerance (benchmark config 1: Qwen3-0.6B shape, 64-token prompt),
     and every layer's attention output of every token within tolerance: the
     reference's rows are captured by `libwayruntime_ref_tap.so` (same sources,
     the session code's attention calls routed through a hook by the linker),
     the device rows by the session objects' own observer;
   * batched step byte-equal to serial steps (test/sdk_gen.c:209-279 contract);
-  * cursor / CTX_FULL / refusal semantics (src/core/session.c:888-999).
+  * cursor / CTX_FULL / refusal semantics (src/core/session.c:888-999);
+  * a gemma4-class model (sliding-window and shared-KV layers, per-layer head_dim,
+    per-layer-input embeddings): the same teacher-forced and batched checks.
 Skipped where the two libraries were not built (they are built where the
 reference checkout exists and travel with the repository snapshot).
 """
@@ -91,11 +93,12 @@ def test_session_self_tests_pass_on_device(libs):
 RUNS = (("device", "kernel"), ("device", "decode"), ("host", "kernel"), ("host", "decode"))
 
 
-def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol, attn_tol=2e-3, runs=RUNS):
+def _teacher_forced(libs, shape, n_prompt, n_steps, seed, logit_tol, attn_tol=2e-3, runs=RUNS,
+                    writer=_mkgguf.write_qwen3):
     ref, b = libs
     vocab = shape["vocab"]
     path = os.path.join(tempfile.mkdtemp(prefix="wr_gguf_"), "model.gguf")
-    _mkgguf.write_qwen3(path, seed=seed, **shape)
+    writer(path, seed=seed, **shape)
     rng = np.random.Generator(np.random.Philox(seed + 1))
     prompt = [int(x) for x in rng.integers(0, vocab, n_prompt)]
     out = {}
@@ -175,7 +178,7 @@ def test_small_model_teacher_forced_argmax(libs):
 
 
 def test_config1_qwen3_0p6b_shape(libs):
-    """BASELINE config 1: 28 layers, hidden 1024, 16 Q / 8 KV heads, head_dim 128,
+    """benchmark config 1: 28 layers, hidden 1024, 16 Q / 8 KV heads, head_dim 128,
     theta 1e6, QK-norm, SwiGLU 3072, vocab 151936, F16 weights ~N(0, 0.02);
     64-token prompt, then 128 teacher-forced greedy steps (24 with
     WR_TEST_QUICK=1: each step is a full CPU forward in both libraries)."""
@@ -183,6 +186,48 @@ def test_config1_qwen3_0p6b_shape(libs):
     steps = 24 if os.environ.get("WR_TEST_QUICK") == "1" else 128
     _teacher_forced(libs, shape, n_prompt=64, n_steps=steps, seed=20261125, logit_tol=2e-3,
                     runs=(("device", "kernel"), ("device", "decode"), ("host", "kernel")))
+
+
+GEMMA = dict(n_layers=6, hidden=256, n_q=4, n_kv=2, head_dim=128, head_dim_swa=64,
+             ffn=[512, 384, 512, 384, 512, 512], vocab=600, swa_pattern=[1, 1, 0, 1, 1, 0], sliding_window=16,
+             shared_kv_layers=2, pl_emb=32)
+
+
+def test_gemma_class_model_teacher_forced(libs):
+    """A gemma4-class model (src/core/session.c:251-437): sliding-window layers of head_dim 64 with
+    their own RoPE base and a 16-key window, global layers of head_dim 128 with partial rotary, the
+    last two layers attending over the caches of layers 1 and 2, sandwich norms, GeGLU, per-layer
+    FFN width, per-layer-input embeddings, embedding scale, logit soft-cap, attention scale 1.  A
+    40-token prompt (longer than the window) and 24 teacher-forced steps: every layer's attention
+    rows within tolerance, logits within tolerance, argmax identical."""
+    _teacher_forced(libs, GEMMA, n_prompt=40, n_steps=24, seed=77, logit_tol=2e-3,
+                    runs=(("host", "decode"),), writer=_mkgguf.write_gemma4)
+
+
+def test_gemma_class_batched_step_is_byte_equal_to_serial(libs):
+    _ref, b = libs
+    path = os.path.join(tempfile.mkdtemp(prefix="wr_gguf_"), "model.gguf")
+    _mkgguf.write_gemma4(path, seed=78, **GEMMA)
+    m = b.load(path)
+    n, vocab = 4, GEMMA["vocab"]
+    prompts = [[(7 * i + 3 * j + 1) % vocab for j in range(5 + 11 * i)] for i in range(n)]
+    serial, batched = [b.session(m) for _ in range(n)], [b.session(m) for _ in range(n)]
+    for s1, s2, p in zip(serial, batched, prompts):
+        assert b.prefill(s1, p) == len(p) and b.prefill(s2, p) == len(p)
+    for t in range(4):
+        toks = [(11 * i + t) % vocab for i in range(n)]
+        want = [b.step(s, tok, vocab) for s, tok in zip(serial, toks)]
+        arr = (C.c_void_p * n)(*[s.value for s in batched])
+        tk = (C.c_uint32 * n)(*toks)
+        outp = (C.POINTER(C.c_float) * n)()
+        assert b.L.wr_batch_step(arr, tk, n, outp) == n
+        for i in range(n):
+            got = np.ctypeslib.as_array(outp[i], (vocab,))
+            assert np.array_equal(got.view(np.uint32), want[i].view(np.uint32)), (t, i)
+    for s in serial + batched:
+        b.L.wr_session_destroy(s)
+    b.L.wr_model_free(m)
+    os.remove(path)
 
 
 @pytest.mark.parametrize("glue", ["device", "host"])

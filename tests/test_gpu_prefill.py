@@ -88,7 +88,7 @@ def test_prefill_f32_queries_scale_and_window(ctx):
 
 
 def test_prefill_llama3_2048(ctx):
-    """BASELINE config 3: 2048-token prompt, 32 Q / 8 KV heads, head_dim 128,
+    """benchmark config 3: 2048-token prompt, 32 Q / 8 KV heads, head_dim 128,
     RoPE theta 5e5 applied to Q and K with the reference's rotation before
     attention.  All heads on a deterministic row subset."""
     P = port()
@@ -108,7 +108,7 @@ def test_prefill_llama3_2048(ctx):
 
 
 def test_prefill_config5_8192_then_decode(ctx):
-    """BASELINE config 5 geometry: 40 Q / 8 KV heads (group of five: one lone
+    """benchmark config 5 geometry: 40 Q / 8 KV heads (group of five: one lone
     head per pair split), one session's 8192-token prompt, then a decode step
     over the 8193 cached keys.  Prefill rows: all heads on a deterministic row
     subset (first/last rows, 64-boundaries +-1, a stride); the decode row in full."""

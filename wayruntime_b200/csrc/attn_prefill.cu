@@ -270,20 +270,9 @@ __device__ __forceinline__ float max3(float a, float b, float c)
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-// 2^x on the FMA pipe: x = r + f with r the nearest integer, a degree-3
+// 2^x on the FMA pipe for a packed pair: x = r + f with r the nearest integer, a degree-3
 // polynomial for 2^f on [-0.5, 0.5] (relative error 7.6e-5, well inside the
 // F16 rounding of P), r added to the exponent field.  x <= -126 gives ~1e-38.
-__device__ __forceinline__ float ex2_poly(float x)
-{
-    x = fmaxf(x, -126.0f);
-    const float t = x + 12582912.0f;                 // 1.5 * 2^23: the integer lands in the low mantissa bits
-    const float f = x - (t - 12582912.0f);
-    float p = fmaf(0.05516839f, f, 0.24260326f);
-    p = fmaf(p, f, 0.69326085f);
-    p = fmaf(p, f, 0.99992865f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-// The same for a packed pair.
 __device__ __forceinline__ void ex2_poly2(uint64_t x2, float &p0, float &p1)
 {
     float x0, x1;
@@ -312,17 +301,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
         ::"r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
-// Tiled 2-D tensor store shared -> global; rows and columns beyond the tensor's
-// extent are dropped by the hardware.  x * 4 bytes is a multiple of 16 for the caller.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src_smem)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(src_smem))
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- work tiles -------------------------------------------------------------
 //

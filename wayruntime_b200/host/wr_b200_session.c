@@ -36,9 +36,13 @@
  * attention, and every host op runs per row with M = 1 exactly as the
  * reference's decode body does, so per-row host arithmetic is unchanged.
  *
- * Not supported (refused with WR_ERR_UNSUPPORTED at session create, never
- * mis-run): Gemma-class models (sandwich norms, per-layer head_dim, shared-KV
- * layers, per-layer-input embeddings, sliding-window layers).
+ * Gemma-class models (src/core/session.c:251-437: sandwich norms, per-layer
+ * head_dim, sliding-window layers with their own RoPE base, shared-KV layers,
+ * per-layer-input embeddings, GeGLU, embedding scale, logit soft-cap) run
+ * with host glue: every layer that owns a cache has its own device cache of
+ * that layer's head_dim, a shared layer attends over its source layer's, and
+ * the prompt is taken token by token through the decode kernels (the
+ * tensor-core prefill kernel is head_dim 128, no window).
  *
  * All row scratch (Q / K / V / attention / residual rows for a whole batch or
  * a prefill chunk) is page-locked host memory taken once at wr_session_create
@@ -59,6 +63,7 @@
 #include <string.h>
 
 #include "core/internal.h"
+#include "core/quant.h"
 #include "core/tensor.h"
 #include "wr_cuda.h"
 
@@ -108,7 +113,9 @@ typedef struct row_buffers {
 
 typedef struct b200_session {
     struct wr_session pub;     /* first member: generate.c reads s->model through it */
-    wr_cuda_kv *kv;
+    wr_cuda_kv *kv;            /* all layers (uniform head_dim); NULL for a Gemma-class model */
+    wr_cuda_kv *kv_layer[WR_MAX_LAYERS];   /* Gemma: one cache per layer; a shared layer aliases its source's */
+    float      *ple;           /* Gemma per-layer-input scratch: proj, table [n_layers*ple]; g, pli [ple]; delta [hidden] */
     wr_cuda_ctx *cuda;
     wr_cuda_model *dm;         /* the model's device mirror (shared by its sessions), or NULL: host glue */
     float      *host;          /* one page-locked block holding the scratch tensors */
@@ -143,10 +150,49 @@ static uint32_t max_ffn(const wr_model *m)
 
 static size_t pad16(size_t n) { return (n + 15u) & ~(size_t)15u; }
 
+/* Per-layer head dim (src/core/session.c:108-113). */
+static uint32_t layer_head_dim(const wr_model *m, uint32_t L)
+{
+    if (m->is_gemma && m->has_swa && m->swa_pattern[L] && m->head_dim_swa) return m->head_dim_swa;
+    return m->head_dim;
+}
+
+static uint32_t max_head_dim(const wr_model *m)
+{
+    uint32_t hd = m->head_dim;
+    for (uint32_t L = 0; L < m->n_layers; L++)
+        if (layer_head_dim(m, L) > hd) hd = layer_head_dim(m, L);
+    return hd;
+}
+
+/* The layer whose cache layer L reads: itself, or for the trailing shared layers the last
+ * non-shared layer of the same kind, sliding-window or global (src/core/session.c:122-134). */
+static uint32_t kv_source_layer(const wr_model *m, uint32_t L, int local)
+{
+    if (!m->is_gemma || m->kv_shared_layers == 0 || m->kv_shared_layers >= m->n_layers) return L;
+    const uint32_t first_shared = m->n_layers - m->kv_shared_layers;
+    if (L < first_shared) return L;
+    for (int cand = (int)first_shared - 1; cand >= 0; cand--) {
+        const int cand_local = (m->has_swa && m->swa_pattern[cand]) ? 1 : 0;
+        if (cand_local == local) return (uint32_t)cand;
+    }
+    return L;
+}
+
+/* The reference's own square root for the per-layer-input scale (src/core/session.c:98-104):
+ * 24 Newton steps, kept as they are so that the arithmetic stays bit-identical. */
+static float newton_sqrtf(float x)
+{
+    if (x <= 0.0f) return 0.0f;
+    float g = x > 1.0f ? x : 1.0f;
+    for (int i = 0; i < 24; i++) g = 0.5f * (g + x / g);
+    return g;
+}
+
 static int rows_alloc(row_buffers *rb, wr_cuda_ctx *cuda, const wr_model *m, uint32_t rows)
 {
-    const size_t hid = m->hidden_dim, nq = (size_t)m->n_q_heads * m->head_dim,
-                 nkv = (size_t)m->n_kv_heads * m->head_dim, ffn = max_ffn(m);
+    const size_t hid = m->hidden_dim, nq = (size_t)m->n_q_heads * max_head_dim(m),
+                 nkv = (size_t)m->n_kv_heads * max_head_dim(m), ffn = max_ffn(m);
     const size_t total = rows * (pad16(hid) + 2 * pad16(nq) + 2 * pad16(nkv)) + 2 * pad16(hid) +
                          2 * pad16(ffn) + 2 * WR_BATCH_MAX * pad16(hid);
     memset(rb, 0, sizeof(*rb));
@@ -204,6 +250,7 @@ static int device_glue_covers(const wr_model *m)
 {
     const char *mode = getenv("WR_B200_GLUE");
     if (mode && strcmp(mode, "host") == 0) return 0;
+    if (m->is_gemma) return 0;                       /* sandwich norms, PLE, per-layer head_dim: host glue */
     const uint32_t hid = m->hidden_dim, hd = m->head_dim, nq = m->n_q_heads * hd, nkv = m->n_kv_heads * hd;
     if ((hid & 3u) || (hd & 3u) || m->n_layers > WR_CUDA_MAX_LAYERS) return 0;
     if (!(m->embed_table.data && m->embed_table.dtype == WR_DTYPE_F32 && m->embed_table.ndim == 2 &&
@@ -299,6 +346,21 @@ static void dev_model_release(wr_cuda_model *dm)
     if (drop) wr_cuda_model_destroy(drop);
 }
 
+static void session_caches_free(b200_session *bs)
+{
+    const wr_model *m = bs->pub.model;
+    if (bs->kv) wr_cuda_kv_destroy(bs->kv);
+    bs->kv = NULL;
+    for (uint32_t L = 0; m && L < m->n_layers; L++) {
+        if (!bs->kv_layer[L]) continue;
+        const int local = (m->has_swa && m->swa_pattern[L]) ? 1 : 0;
+        if (kv_source_layer(m, L, local) == L) wr_cuda_kv_destroy(bs->kv_layer[L]);   /* owners only */
+        bs->kv_layer[L] = NULL;
+    }
+    free(bs->ple);
+    bs->ple = NULL;
+}
+
 wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_session **out)
 {
     if (!out) return WR_ERR_INVAL;
@@ -310,7 +372,7 @@ wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_ses
     if (m->n_kv_heads == 0 || m->n_q_heads == 0 || m->head_dim == 0 || m->hidden_dim == 0 ||
         m->vocab_size == 0 || m->max_context == 0)
         return WR_ERR_INVAL;
-    if (m->is_gemma || m->kv_shared_layers || m->has_swa || m->pl_emb_dim) return WR_ERR_UNSUPPORTED;
+    if (!m->is_gemma && (m->kv_shared_layers || m->has_swa || m->pl_emb_dim)) return WR_ERR_UNSUPPORTED;
 
     uint32_t max_ctx = m->max_context;
     if (params && params->max_context) {
@@ -332,7 +394,7 @@ wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_ses
     s->lock = wr_mutex_create();
     if (!s->lock) { free(bs); return WR_ERR_NOMEM; }
 
-    const uint32_t hid = m->hidden_dim, hd = m->head_dim, ffn = max_ffn(m);
+    const uint32_t hid = m->hidden_dim, hd = max_head_dim(m), ffn = max_ffn(m);
     const size_t nq = (size_t)m->n_q_heads * hd, nkv = (size_t)m->n_kv_heads * hd;
     const size_t total = pad16(hid) * 3 + pad16(nq) * 2 + pad16(nkv) * 2 + pad16(ffn) * 2 +
                          pad16(m->vocab_size);
@@ -356,15 +418,31 @@ wr_status wr_session_create(wr_model *m, const wr_session_params *params, wr_ses
     f32_tensor(&s->logits, p, 1, m->vocab_size, 0, 0);
 
     bs->cuda = cuda;
-    int rc = wr_cuda_kv_create(cuda, m->n_layers, m->n_kv_heads, hd, max_ctx, &bs->kv);
+    int rc = 0;
+    if (!m->is_gemma) {
+        rc = wr_cuda_kv_create(cuda, m->n_layers, m->n_kv_heads, hd, max_ctx, &bs->kv);
+    } else {
+        /* one cache per owning layer, of that layer's head_dim (src/core/session.c:647-674) */
+        for (uint32_t L = 0; L < m->n_layers && rc == 0; L++) {
+            const int local = (m->has_swa && m->swa_pattern[L]) ? 1 : 0;
+            const uint32_t src = kv_source_layer(m, L, local);
+            if (src != L) bs->kv_layer[L] = bs->kv_layer[src];          /* src < L: already made */
+            else rc = wr_cuda_kv_create(cuda, 1, m->n_kv_heads, layer_head_dim(m, L), max_ctx, &bs->kv_layer[L]);
+        }
+        if (rc == 0 && m->pl_emb_dim) {
+            const size_t pl = (size_t)m->n_layers * m->pl_emb_dim;
+            bs->ple = calloc(2 * pl + 2 * (size_t)m->pl_emb_dim + hid, sizeof(float));
+            if (!bs->ple) rc = WR_ERR_NOMEM;
+        }
+    }
     if (rc == 0) {
         uint32_t rows = max_ctx < WR_B200_ROWS_MAX ? max_ctx : WR_B200_ROWS_MAX;
         if (rows < WR_BATCH_MAX) rows = WR_BATCH_MAX;
         rc = rows_alloc(&bs->rb, cuda, m, rows);
-        if (rc != 0) { wr_cuda_kv_destroy(bs->kv); bs->kv = NULL; }
     }
     if (rc != 0) {
         wri_log_msg(0, "b200 session: device KV / row scratch allocation failed (rc=%d)", rc);
+        session_caches_free(bs);
         wr_cuda_host_free(cuda, bs->host);
         wr_mutex_destroy(s->lock);
         free(bs);
@@ -389,7 +467,7 @@ void wr_session_destroy(wr_session *s)
         wr_mutex_unlock(m->lock);
     }
     dev_model_release(bs->dm);
-    if (bs->kv) wr_cuda_kv_destroy(bs->kv);
+    session_caches_free(bs);
     if (bs->rb.block) wr_cuda_host_free(bs->cuda, bs->rb.block);
     if (bs->host) wr_cuda_host_free(bs->cuda, bs->host);
     if (s->lock) wr_mutex_destroy(s->lock);
@@ -530,6 +608,191 @@ static wr_status forward_rows(const wr_model *m, row_buffers *rb, uint32_t R, co
     return WR_OK;
 }
 
+/* Gemma-class layer stack (src/core/session.c:202-437) for R rows, row r = the new token of session
+ * sess[r] at position pos[r].  Host ops exactly as the reference runs them, per row with M = 1; per
+ * layer one device call for all rows: wr_cuda_decode_step on the layer's own cache (RoPE with the
+ * layer's base and rotary share, append, attention with the model's explicit scale and the layer's
+ * window), or — a shared layer — RoPE of Q on the host and wr_cuda_attn_decode over the source
+ * layer's cache.  Rows of a layer are dense [R][heads][hd_L].  Scratch for the per-layer-input
+ * arithmetic is one row's; those steps run row by row.  On success rb->resid holds the hidden rows. */
+static wr_status forward_rows_gemma(const wr_model *m, b200_session *const *sess, row_buffers *rb, uint32_t R,
+                                    const uint32_t *tokens, const uint32_t *pos)
+{
+    if (R == 0 || R > rb->rows || R > WR_BATCH_MAX) return WR_ERR_INTERNAL;
+    const uint32_t hid = m->hidden_dim, qheads = m->n_q_heads, kheads = m->n_kv_heads;
+    const size_t s_hid = pad16(hid);
+    const float eps = m->rms_eps;
+    const float theta_default = (m->rope_freq_base > 0.0f) ? m->rope_freq_base : 10000.0f;
+    const uint32_t ple = m->pl_emb_dim, pl = m->n_layers * ple;
+    const int want_ple = m->per_layer_token_embd.data && m->per_layer_model_proj.data &&
+                         m->per_layer_proj_norm.data && ple;
+    int crc = 0;
+    wr_cuda_ctx *cuda = cuda_ctx(&crc);
+    if (!cuda) return (crc < 0) ? (wr_status)crc : WR_ERR_UNSUPPORTED;
+    wr_tensor t_res, t_norm, t_q, t_k, t_v, t_a, t_proj, t_gate, t_up, t_x, t_y;
+    int rc;
+
+    for (uint32_t r = 0; r < R; r++) {
+        float *res = rb->resid + r * s_hid;
+        f32_tensor(&t_res, res, 1, hid, 0, 0);
+        rc = wri_op_embed(&m->embed_table, tokens[r], &t_res);
+        if (rc != WR_OK) return fail("embed", 0, rc);
+        if (m->embed_scale != 0.0f)
+            for (uint32_t j = 0; j < hid; j++) res[j] *= m->embed_scale;
+        if (want_ple) {                              /* per-layer-input table of this token (session.c:221-245) */
+            float *proj = sess[r]->ple, *table = proj + pl;
+            if (!proj) return WR_ERR_INTERNAL;
+            f32_tensor(&t_x, res, 2, 1, hid, 0);
+            f32_tensor(&t_y, proj, 2, 1, pl, 0);
+            rc = wri_op_matmul(&t_x, &m->per_layer_model_proj, &t_y);
+            if (rc != WR_OK) return fail("ple proj matmul", 0, rc);
+            f32_tensor(&t_y, proj, 2, m->n_layers, ple, 0);
+            rc = wri_op_rmsnorm(&t_y, &m->per_layer_proj_norm, &t_y, eps);
+            if (rc != WR_OK) return fail("ple proj norm", 0, rc);
+            f32_tensor(&t_y, table, 1, pl, 0, 0);
+            rc = wri_op_embed(&m->per_layer_token_embd, tokens[r], &t_y);
+            if (rc != WR_OK) return fail("ple table embed", 0, rc);
+            const float tscale = newton_sqrtf((float)ple), comb = 0.70710678f;
+            for (uint32_t j = 0; j < pl; j++) table[j] = (proj[j] + table[j] * tscale) * comb;
+        }
+    }
+
+    for (uint32_t L = 0; L < m->n_layers; L++) {
+        const uint32_t ffn = m->ffn_dim_per_layer[L] ? m->ffn_dim_per_layer[L] : m->ffn_dim;
+        const int local = (m->has_swa && m->swa_pattern[L]) ? 1 : 0;
+        const uint32_t hd = layer_head_dim(m, L), nq = qheads * hd, nkv = kheads * hd;
+        const float theta = (local && m->rope_freq_base_swa > 0.0f) ? m->rope_freq_base_swa : theta_default;
+        const uint32_t n_rot = local ? 0u : m->n_rot_pairs;       /* partial rotary on global layers only */
+        const uint32_t ksrc = kv_source_layer(m, L, local);
+        const int shared = (ksrc != L);
+        const uint32_t window = (local && m->swa_mode != WR_SWA_DISABLED) ? m->sliding_window : 0u;
+        const int qk_norm = m->has_qk_norm && m->q_norm[L].data && m->k_norm[L].data;
+        if ((nq & 3u) || (nkv & 3u)) return WR_ERR_UNSUPPORTED;    /* rows move as 16-byte vectors */
+
+        for (uint32_t r = 0; r < R; r++) {           /* A1-A4: norm, projections, head norms (V: weightless) */
+            f32_tensor(&t_res, rb->resid + r * s_hid, 1, hid, 0, 0);
+            f32_tensor(&t_norm, rb->normed, 1, hid, 0, 0);
+            rc = wri_op_rmsnorm(&t_res, &m->attn_norm[L], &t_norm, eps);
+            if (rc != WR_OK) return fail("attn norm", L, rc);
+            f32_tensor(&t_norm, rb->normed, 2, 1, hid, 0);
+            f32_tensor(&t_q, rb->q + (size_t)r * nq, 2, 1, nq, 0);
+            rc = wri_op_matmul(&t_norm, &m->wq[L], &t_q);
+            if (rc != WR_OK) return fail("wq matmul", L, rc);
+            if (!shared) {
+                f32_tensor(&t_k, rb->k + (size_t)r * nkv, 2, 1, nkv, 0);
+                f32_tensor(&t_v, rb->v + (size_t)r * nkv, 2, 1, nkv, 0);
+                rc = wri_op_matmul(&t_norm, &m->wk[L], &t_k);
+                if (rc != WR_OK) return fail("wk matmul", L, rc);
+                rc = wri_op_matmul(&t_norm, &m->wv[L], &t_v);
+                if (rc != WR_OK) return fail("wv matmul", L, rc);
+            }
+            if (qk_norm) {
+                f32_tensor(&t_q, rb->q + (size_t)r * nq, 2, qheads, hd, 0);
+                rc = wri_op_rmsnorm(&t_q, &m->q_norm[L], &t_q, eps);
+                if (rc != WR_OK) return fail("q norm", L, rc);
+                if (!shared) {
+                    f32_tensor(&t_k, rb->k + (size_t)r * nkv, 2, kheads, hd, 0);
+                    rc = wri_op_rmsnorm(&t_k, &m->k_norm[L], &t_k, eps);
+                    if (rc != WR_OK) return fail("k norm", L, rc);
+                }
+            }
+            if (!shared) {                           /* weightless RMS of V before the append (session.c:331-336) */
+                f32_tensor(&t_v, rb->v + (size_t)r * nkv, 2, kheads, hd, 0);
+                rc = wri_op_rmsnorm(&t_v, NULL, &t_v, eps);
+                if (rc != WR_OK) return fail("v norm", L, rc);
+            } else {                                 /* shared layer: only Q is rotated; its K is already in the cache */
+                f32_tensor(&t_q, rb->q + (size_t)r * nq, 3, 1, qheads, hd);
+                rc = wri_op_rope(&t_q, &t_q, pos[r], theta, n_rot);
+                if (rc != WR_OK) return fail("q rope", L, rc);
+            }
+        }
+        /* A5-A6: one device call for all rows */
+        wr_cuda_kv *kvs[WR_BATCH_MAX];
+        uint32_t lens[WR_BATCH_MAX];
+        for (uint32_t r = 0; r < R; r++) {
+            kvs[r] = sess[r]->kv_layer[ksrc];
+            lens[r] = pos[r] + 1;
+            if (!kvs[r]) return WR_ERR_INTERNAL;
+        }
+        if (!shared)
+            rc = wr_cuda_decode_step(cuda, R, kvs, 0, pos, rb->q, rb->k, rb->v, rb->attn, qheads, theta, n_rot,
+                                     WR_CUDA_APPEND_ROPE, m->attn_scale, window, WR_CUDA_MEM_HOST);
+        else
+            rc = wr_cuda_attn_decode(cuda, R, kvs, 0, lens, rb->q, rb->attn, qheads, m->attn_scale, window,
+                                     WR_CUDA_MEM_HOST);
+        if (rc != 0) return fail("cuda attention", L, rc);
+        WRI_CTR_ADD(WR_CTR_ATTENTION_CALLS, R);
+        if (g_attn_tap)
+            for (uint32_t r = 0; r < R; r++) g_attn_tap(g_attn_tap_user, L, pos[r], rb->attn + (size_t)r * nq, nq);
+
+        for (uint32_t r = 0; r < R; r++) {           /* A7-A9, F1-F6, per-layer input, output scale */
+            float *res = rb->resid + r * s_hid;
+            f32_tensor(&t_res, res, 1, hid, 0, 0);
+            f32_tensor(&t_a, rb->attn + (size_t)r * nq, 2, 1, nq, 0);
+            f32_tensor(&t_proj, rb->proj, 2, 1, hid, 0);
+            rc = wri_op_matmul(&t_a, &m->wo[L], &t_proj);
+            if (rc != WR_OK) return fail("wo matmul", L, rc);
+            f32_tensor(&t_proj, rb->proj, 1, hid, 0, 0);
+            rc = wri_op_rmsnorm(&t_proj, &m->post_attn_norm[L], &t_proj, eps);
+            if (rc != WR_OK) return fail("post-attn norm", L, rc);
+            rc = wri_op_add(&t_res, &t_proj, &t_res);
+            if (rc != WR_OK) return fail("attn residual", L, rc);
+
+            f32_tensor(&t_norm, rb->normed, 1, hid, 0, 0);
+            rc = wri_op_rmsnorm(&t_res, &m->ffn_norm[L], &t_norm, eps);
+            if (rc != WR_OK) return fail("ffn norm", L, rc);
+            f32_tensor(&t_norm, rb->normed, 2, 1, hid, 0);
+            f32_tensor(&t_gate, rb->gate, 2, 1, ffn, 0);
+            f32_tensor(&t_up, rb->up, 2, 1, ffn, 0);
+            rc = wri_op_matmul(&t_norm, &m->w_gate[L], &t_gate);
+            if (rc != WR_OK) return fail("gate matmul", L, rc);
+            rc = wri_op_matmul(&t_norm, &m->w_up[L], &t_up);
+            if (rc != WR_OK) return fail("up matmul", L, rc);
+            f32_tensor(&t_gate, rb->gate, 1, ffn, 0, 0);
+            f32_tensor(&t_up, rb->up, 1, ffn, 0, 0);
+            rc = wri_op_fused_gelu_mul(&t_gate, &t_up, &t_gate);
+            if (rc != WR_OK) return fail("geglu", L, rc);
+            f32_tensor(&t_gate, rb->gate, 2, 1, ffn, 0);
+            f32_tensor(&t_proj, rb->proj, 2, 1, hid, 0);
+            rc = wri_op_matmul(&t_gate, &m->w_down[L], &t_proj);
+            if (rc != WR_OK) return fail("down matmul", L, rc);
+            f32_tensor(&t_proj, rb->proj, 1, hid, 0, 0);
+            rc = wri_op_rmsnorm(&t_proj, &m->post_ffw_norm[L], &t_proj, eps);
+            if (rc != WR_OK) return fail("post-ffw norm", L, rc);
+            rc = wri_op_add(&t_res, &t_proj, &t_res);
+            if (rc != WR_OK) return fail("ffn residual", L, rc);
+
+            if (want_ple && m->inp_gate[L].data && m->pl_proj[L].data && m->post_norm[L].data) {
+                float *table = sess[r]->ple + pl, *g = table + pl, *pli = g + ple, *delta = pli + ple;
+                f32_tensor(&t_x, res, 2, 1, hid, 0);
+                f32_tensor(&t_y, g, 2, 1, ple, 0);
+                rc = wri_op_matmul(&t_x, &m->inp_gate[L], &t_y);
+                if (rc != WR_OK) return fail("ple gate matmul", L, rc);
+                memcpy(pli, table + (size_t)L * ple, (size_t)ple * sizeof(float));
+                f32_tensor(&t_x, g, 1, ple, 0, 0);
+                f32_tensor(&t_y, pli, 1, ple, 0, 0);
+                rc = wri_op_fused_gelu_mul(&t_x, &t_y, &t_x);
+                if (rc != WR_OK) return fail("ple geglu", L, rc);
+                f32_tensor(&t_x, g, 2, 1, ple, 0);
+                f32_tensor(&t_y, delta, 2, 1, hid, 0);
+                rc = wri_op_matmul(&t_x, &m->pl_proj[L], &t_y);
+                if (rc != WR_OK) return fail("ple proj matmul", L, rc);
+                f32_tensor(&t_y, delta, 1, hid, 0, 0);
+                rc = wri_op_rmsnorm(&t_y, &m->post_norm[L], &t_y, eps);
+                if (rc != WR_OK) return fail("ple post norm", L, rc);
+                rc = wri_op_add(&t_res, &t_y, &t_res);
+                if (rc != WR_OK) return fail("ple residual", L, rc);
+            }
+            if (m->layer_output_scale[L].data) {     /* applied directly, no (1+w) (session.c:430-436) */
+                const float sc = wri_read_elem_f32(&m->layer_output_scale[L], 0);
+                if (sc != 1.0f)
+                    for (uint32_t j = 0; j < hid; j++) res[j] *= sc;
+            }
+        }
+    }
+    return WR_OK;
+}
+
 /* Final RMSNorm into s->normed, then logits <- normed x lm_head (src/core/session.c:554). */
 static wr_status finish_row(wr_session *s, const float *resid_row, int compute_logits)
 {
@@ -547,6 +810,8 @@ static wr_status finish_row(wr_session *s, const float *resid_row, int compute_l
     f32_tensor(&lv, (float *)s->logits.data, 2, 1, m->vocab_size, 0);
     rc = wri_op_matmul(&nv, &lmv, &lv);
     if (rc != WR_OK) return fail("lm-head matmul", m->n_layers, rc);
+    if (m->is_gemma && m->logit_softcap > 0.0f)      /* x = cap * tanh(x / cap) (session.c:562-566) */
+        wri_softcap((float *)s->logits.data, m->vocab_size, m->logit_softcap);
     return WR_OK;
 }
 
@@ -605,7 +870,13 @@ static wr_status step_one(wr_session *s, uint32_t token, int compute_logits)
         return forward_device(s->model, priv(s)->dm, rb, 1, &token, &kv, &pos, ATTN_DECODE, 0, &s,
                               compute_logits);
     }
-    wr_status st = forward_rows(s->model, rb, 1, &token, &kv, &pos, ATTN_DECODE);
+    wr_status st;
+    if (s->model->is_gemma) {
+        b200_session *me = priv(s);
+        st = forward_rows_gemma(s->model, &me, rb, 1, &token, &pos);
+    } else {
+        st = forward_rows(s->model, rb, 1, &token, &kv, &pos, ATTN_DECODE);
+    }
     if (st == WR_OK) st = finish_row(s, rb->resid, compute_logits);
     return st;
 }
@@ -646,7 +917,8 @@ int wri_session_prefill(wr_session *s, const uint32_t *ids, uint32_t n)
         st = WR_ERR_CTX_FULL;
     } else {
         const char *mode = getenv("WR_B200_PREFILL");
-        const int by_token = (mode && strcmp(mode, "decode") == 0) || s->model->head_dim != 128;
+        const int by_token = (mode && strcmp(mode, "decode") == 0) || s->model->head_dim != 128 ||
+                             s->model->is_gemma;
         wr_cuda_kv *kv = priv(s)->kv;
         row_buffers *rb = &priv(s)->rb;
         wr_cuda_model *dm = priv(s)->dm;
@@ -659,11 +931,15 @@ int wri_session_prefill(wr_session *s, const uint32_t *ids, uint32_t n)
         } else if (by_token) {
             uint32_t pos = s->pos;
             for (uint32_t i = 0; st == WR_OK && i < n; i++, pos++) {
-                if (dm)
+                if (dm) {
                     st = forward_device(s->model, dm, rb, 1, &ids[i], &kv, &pos, ATTN_DECODE,
                                         (i + 1 == n) ? 0u : 1u, &s, 0);
-                else
+                } else if (s->model->is_gemma) {
+                    b200_session *me = priv(s);
+                    st = forward_rows_gemma(s->model, &me, rb, 1, &ids[i], &pos);
+                } else {
                     st = forward_rows(s->model, rb, 1, &ids[i], &kv, &pos, ATTN_DECODE);
+                }
             }
             if (st == WR_OK && !dm) st = finish_row(s, rb->resid, 0);
         } else if (dm) {
@@ -744,7 +1020,13 @@ int wri_batch_decode_step(wr_session *const *sessions, const uint32_t *tokens, u
             if (st == WR_OK)
                 st = forward_device(m, dm, rb, n, tokens, kvs, pos, ATTN_DECODE, 0, sessions, 1);
         } else {
-            st = forward_rows(m, rb, n, tokens, kvs, pos, ATTN_DECODE);    /* all sessions, one grid per layer */
+            if (m->is_gemma) {
+                b200_session *bss[WR_BATCH_MAX];
+                for (uint32_t i = 0; i < n; i++) bss[i] = priv(sessions[i]);
+                st = forward_rows_gemma(m, bss, rb, n, tokens, pos);
+            } else {
+                st = forward_rows(m, rb, n, tokens, kvs, pos, ATTN_DECODE);    /* all sessions, one grid per layer */
+            }
             for (uint32_t i = 0; i < n && st == WR_OK; i++)
                 st = finish_row(sessions[i], rb->resid + (size_t)i * pad16(m->hidden_dim), 1);
         }
