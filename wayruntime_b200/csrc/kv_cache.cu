@@ -42,9 +42,14 @@ extern "C" int wr_cuda_ctx_create(int device, wr_cuda_ctx **out)
     ctx->device = device;
     cudaError_t e = cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_err, sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(ctx->dev_err, 0, sizeof(int));
-    if (e == cudaSuccess) e = cudaMallocHost(&ctx->host_err, sizeof(int));
+    // The error word lives in page-locked host memory that the device sees too: a kernel that gives
+    // up writes it across the bus (rare, and slow is fine), and the host reads it after a
+    // synchronisation without a copy operation in the stream.
+    if (e == cudaSuccess) e = cudaHostAlloc((void **)&ctx->host_err, sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        *ctx->host_err = 0;
+        e = cudaHostGetDevicePointer((void **)&ctx->dev_err, ctx->host_err, 0);
+    }
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         wr_cuda_ctx_destroy(ctx);
@@ -74,8 +79,7 @@ extern "C" void wr_cuda_ctx_destroy(wr_cuda_ctx *ctx)
     if (ctx->tickets) (void)cudaFree(ctx->tickets);
     if (ctx->prefill_sched) (void)cudaFree(ctx->prefill_sched);
     if (ctx->debug_buf) (void)cudaFree(ctx->debug_buf);
-    if (ctx->dev_err) (void)cudaFree(ctx->dev_err);
-    if (ctx->host_err) (void)cudaFreeHost(ctx->host_err);
+    if (ctx->host_err) (void)cudaFreeHost(ctx->host_err);       // (dev_err is its device-side alias)
     if (ctx->stage_dev) (void)cudaFree(ctx->stage_dev);
     if (ctx->stage_host) (void)cudaFreeHost(ctx->stage_host);
     if (ctx->stream) (void)cudaStreamDestroy(ctx->stream);
@@ -85,13 +89,11 @@ extern "C" void wr_cuda_ctx_destroy(wr_cuda_ctx *ctx)
 
 int wr_ctx_sync_checked(wr_cuda_ctx *ctx)
 {
-    WR_CUDA_TRY(cudaMemcpyAsync(ctx->host_err, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost,
-                                ctx->stream));
     WR_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    if (*ctx->host_err != 0) {
-        ctx->last_err = *ctx->host_err;
-        *ctx->host_err = 0;
-        WR_CUDA_TRY(cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
+    const int word = *(volatile int *)ctx->host_err;
+    if (word != 0) {
+        ctx->last_err = word;
+        *(volatile int *)ctx->host_err = 0;
         // A kernel that gave up left its arrival tickets and work queue mid-count.
         if (ctx->tickets)
             WR_CUDA_TRY(cudaMemsetAsync(ctx->tickets, 0, ctx->ticket_count * sizeof(int), ctx->stream));

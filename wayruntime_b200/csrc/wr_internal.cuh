@@ -76,8 +76,8 @@ struct wr_cuda_ctx {
     size_t ticket_count = 0;
     int *prefill_sched = nullptr;    // prefill kernel: next work tile, CTAs that have left
     void *debug_buf = nullptr;       // development builds only (kernel timelines)
-    int *dev_err = nullptr;          // device-side error flag
-    int *host_err = nullptr;         // pinned mirror
+    int *host_err = nullptr;         // error word: page-locked host memory, mapped into the device
+    int *dev_err = nullptr;          // its device-side address (what kernels get)
     int last_err = 0;                // the last non-zero error word read back (which wait gave up)
     // staging for WR_CUDA_MEM_HOST calls
     void *stage_dev = nullptr;
