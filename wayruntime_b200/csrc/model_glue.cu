@@ -21,7 +21,7 @@
 // rows sit in shared memory, the weights stream from HBM exactly once per group
 // of up to 16 activation rows) with optional fused RMSNorm on the input, fused
 // residual add or SiLU*up on the output; per-head RMSNorm; embedding gather;
-// row RMSNorm; arg-max with the reference's tie rule (first maximum wins,
+// row RMSNorm; a two-step arg-max with the reference's tie rule (first maximum wins,
 // src/cli/wayrt.c:805-812).
 #include <math.h>
 #include <stdlib.h>
@@ -473,41 +473,68 @@ __global__ void rmsnorm_rows_kernel(const float *x, uint32_t x_stride, const flo
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) o_[i] = xr[i] * inv * w[i];
 }
 
-// First maximum of each row (strict >, so the lowest id wins a tie); one block per row.
-__global__ void argmax_rows_kernel(const float *logits, uint32_t vocab, uint32_t *out)
+// First maximum of each row (strict >, so the lowest id wins a tie), in two steps: kArgmaxParts
+// blocks per row each reduce a slice of the vocabulary to (value, index); one warp per row then
+// reduces the slices' results.  (value, index) pairs are compared as "greater value, or equal
+// value and lower index", so the order of the reduction does not matter.
+constexpr int kArgmaxParts = 64;
+
+__device__ __forceinline__ bool argmax_better(float v, uint32_t i, float bv, uint32_t bi)
 {
-    __shared__ float bv[32];
-    __shared__ uint32_t bi[32];
-    const float *row = logits + (size_t)blockIdx.x * vocab;
-    float best = -INFINITY;
-    uint32_t at = 0xffffffffu;
-    for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || at == 0xffffffffu) { best = v; at = i; }   // ascending i per thread: first maximum kept
-    }
-    auto better = [](float v, uint32_t i, float bv_, uint32_t bi_) {
-        return bi_ == 0xffffffffu || (i != 0xffffffffu && (v > bv_ || (v == bv_ && i < bi_)));
-    };
+    return bi == 0xffffffffu || (i != 0xffffffffu && (v > bv || (v == bv && i < bi)));
+}
+
+__device__ __forceinline__ void argmax_warp(float &best, uint32_t &at)
+{
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const uint32_t oi = __shfl_xor_sync(0xffffffffu, at, o);
-        if (better(ov, oi, best, at)) { best = ov; at = oi; }
+        if (argmax_better(ov, oi, best, at)) { best = ov; at = oi; }
     }
+}
+
+__global__ void __launch_bounds__(256) argmax_parts_kernel(const float *logits, uint32_t vocab, float *part_v,
+                                                           uint32_t *part_i)
+{
+    __shared__ float bv[8];
+    __shared__ uint32_t bi[8];
+    const uint32_t row = blockIdx.y, part = blockIdx.x;
+    const uint32_t per = (vocab + kArgmaxParts - 1) / kArgmaxParts;
+    const uint32_t lo = part * per, hi = min(lo + per, vocab);
+    const float *r = logits + (size_t)row * vocab;
+    float best = -INFINITY;
+    uint32_t at = 0xffffffffu;
+    for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = r[i];
+        if (argmax_better(v, i, best, at)) { best = v; at = i; }
+    }
+    argmax_warp(best, at);
     if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = at; }
     __syncthreads();
     if (threadIdx.x < 32) {
-        const bool live = threadIdx.x < (blockDim.x >> 5);
-        best = live ? bv[threadIdx.x] : -INFINITY;
-        at = live ? bi[threadIdx.x] : 0xffffffffu;
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const uint32_t oi = __shfl_xor_sync(0xffffffffu, at, o);
-            if (better(ov, oi, best, at)) { best = ov; at = oi; }
+        best = threadIdx.x < 8 ? bv[threadIdx.x] : -INFINITY;
+        at = threadIdx.x < 8 ? bi[threadIdx.x] : 0xffffffffu;
+        argmax_warp(best, at);
+        if (threadIdx.x == 0) {
+            part_v[row * kArgmaxParts + part] = best;
+            part_i[row * kArgmaxParts + part] = at;
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = at;
     }
+}
+
+__global__ void argmax_final_kernel(const float *part_v, const uint32_t *part_i, uint32_t *out)
+{
+    const uint32_t row = blockIdx.x, lane = threadIdx.x;
+    float best = -INFINITY;
+    uint32_t at = 0xffffffffu;
+    for (uint32_t i = lane; i < (uint32_t)kArgmaxParts; i += 32) {
+        const float v = part_v[row * kArgmaxParts + i];
+        const uint32_t idx = part_i[row * kArgmaxParts + i];
+        if (argmax_better(v, idx, best, at)) { best = v; at = idx; }
+    }
+    argmax_warp(best, at);
+    if (lane == 0) out[row] = at;
 }
 
 template <int RG, int NW>
@@ -572,7 +599,8 @@ struct wr_cuda_model {
     // row scratch (device)
     float *resid = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *gate = nullptr;
     float *normed = nullptr, *logits = nullptr;
-    uint32_t *tokens = nullptr, *best = nullptr;
+    uint32_t *tokens = nullptr, *best = nullptr, *part_i = nullptr;
+    float *part_v = nullptr;             // arg-max partials [16][kArgmaxParts]
     uint32_t *h_tokens = nullptr;        // pinned: token ids in, arg-max ids out
     uint32_t ffn_max = 0;
     uint64_t launches = 0;
@@ -668,7 +696,7 @@ extern "C" int wr_cuda_model_create(wr_cuda_ctx *ctx, const wr_cuda_model_desc *
     const size_t R = d->max_rows, LR = kLogitRowsMax;
     const size_t scratch = up256(R * hid * 4) + 2 * up256(R * nq * 4) + 2 * up256(R * nkv * 4) +
                            up256(R * (size_t)m->ffn_max * 4) + up256(LR * hid * 4) +
-                           up256(LR * (size_t)d->vocab * 4) + 2 * up256(R * 4);
+                           up256(LR * (size_t)d->vocab * 4) + 2 * up256(R * 4) + 2 * up256(LR * kArgmaxParts * 4);
     m->slab_bytes = total + scratch;
     cudaError_t e = cudaMalloc(&m->slab, m->slab_bytes);
     if (e != cudaSuccess) {
@@ -729,6 +757,8 @@ extern "C" int wr_cuda_model_create(wr_cuda_ctx *ctx, const wr_cuda_model_desc *
     m->logits = take(LR * (size_t)d->vocab);
     m->tokens = reinterpret_cast<uint32_t *>(take(R));
     m->best = reinterpret_cast<uint32_t *>(take(R));
+    m->part_v = take(LR * kArgmaxParts);
+    m->part_i = reinterpret_cast<uint32_t *>(take(LR * kArgmaxParts));
     if (ok && cudaStreamSynchronize(ctx->stream) != cudaSuccess) ok = false;
     if (!ok || (size_t)(cur - m->slab) > m->slab_bytes) {
         (void)cudaGetLastError();
@@ -949,8 +979,9 @@ extern "C" int wr_cuda_model_forward(wr_cuda_ctx *ctx, wr_cuda_model *m, int mod
         int rc = gemv(m, p, m->vocab);
         if (rc != WR_CUDA_OK) return rc;
         if (argmax_out) {
-            argmax_rows_kernel<<<n_fin, 1024, 0, st>>>(m->logits, m->vocab, m->best);
-            ++m->launches;
+            argmax_parts_kernel<<<dim3(kArgmaxParts, n_fin), 256, 0, st>>>(m->logits, m->vocab, m->part_v, m->part_i);
+            argmax_final_kernel<<<n_fin, 32, 0, st>>>(m->part_v, m->part_i, m->best);
+            m->launches += 2;
             WR_CUDA_TRY(cudaGetLastError());
             WR_CUDA_TRY(cudaMemcpyAsync(m->h_tokens + m->max_rows, m->best, n_fin * sizeof(uint32_t),
                                         cudaMemcpyDeviceToHost, st));
