@@ -125,9 +125,12 @@ __device__ __forceinline__ void xchg_rows_done(const params &p, uint32_t rows, u
     if (lane == 0) {
         const uint32_t total = p.n_sess * p.n_q;
         if ((uint32_t)atomicAdd(p.x_done, (int)rows) + rows == total) {
+            // One system-scope fence orders every counted row before the flags; the flag stores
+            // themselves are relaxed and go out together (a release per flag would wait for the
+            // round trip of the one before it: eight ranks, eight NVLink round trips in a row).
             __threadfence_system();
             for (uint32_t w = 0; w < p.x_world; ++w)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.x_flag[w]), "r"(p.x_step) : "memory");
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.x_flag[w]), "r"(p.x_step) : "memory");
             *p.x_done = 0;                       // ready for the next launch
         }
     }

@@ -10,7 +10,8 @@
 //   1. stores its own triples into every rank's exchange buffer (plain 16-byte
 //      stores to peer memory mapped through CUDA IPC; its own buffer included),
 //   2. publishes them: the last CTA to finish sets this rank's flag in every
-//      peer's buffer to the step number (system-scope release),
+//      peer's buffer to the step number (one system-scope fence, then relaxed
+//      stores that go out together),
 //   3. waits — with a time limit — until its own buffer carries every rank's
 //      flag for this step (system-scope acquire),
 //   4. merges the world's triples from its own buffer into the output rows.
@@ -48,9 +49,9 @@ struct xchg_params {
     long long wait_limit;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t *addr, uint32_t v)
+__device__ __forceinline__ void st_relaxed_sys(uint32_t *addr, uint32_t v)
 {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *addr)
 {
@@ -91,9 +92,11 @@ __global__ void __launch_bounds__(256) attn_exchange_combine_kernel(const xchg_p
     if (threadIdx.x == 0) {
         s_ok = 1;
         if (!p.skip_store && atomicAdd(p.done, 1) == (int)gridDim.x - 1) {
+            // one fence, then the flags as relaxed stores that travel together (a release per flag
+            // would serialise one NVLink round trip per rank)
             __threadfence_system();
             for (uint32_t peer = 0; peer < p.world; ++peer)
-                st_release_sys(slot_flag(p.peer[peer], p.parity, p.rank, p), p.step);
+                st_relaxed_sys(slot_flag(p.peer[peer], p.parity, p.rank, p), p.step);
             *p.done = 0;                                  // ready for the next launch
         }
     }
