@@ -276,11 +276,14 @@ int wr_cuda_attn_exchange_combine(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_
 /* Key-sharded decode with the exchange fused into the decode kernel (no
  * reference counterpart, as above): wr_cuda_attn_decode_partial and
  * wr_cuda_attn_exchange_combine in one call.  The decode kernel's own warps
- * store every finished (session, q head) triple into all ranks' buffers and
- * publish the step; a small second kernel waits (bounded) for every rank's
- * step and merges in rank order into out (device, F32 [n_sess, n_q_heads,
- * head_dim]).  q is device memory; head_dim 128.  Identical bits to the
- * two-call sequence.  Every rank makes the same sequence of calls. */
+ * store every finished (session, q head) triple into all ranks' buffers,
+ * flag each row there, wait (bounded) for the same rows from every rank and
+ * merge them in rank order into out (device, F32 [n_sess, n_q_heads,
+ * head_dim]) — one kernel.  Where a session of this rank has fewer than two
+ * key chunks (a short or empty shard) the rows are published per step instead
+ * and a small second kernel does the waiting and merging.  q is device
+ * memory; head_dim 128.  Identical bits to the two-call sequence.  Every rank
+ * makes the same sequence of calls. */
 int wr_cuda_attn_decode_exchange(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_sess,
                                  wr_cuda_kv *const *kv, uint32_t layer,
                                  const uint32_t *seq_lens, const float *q, float *out,

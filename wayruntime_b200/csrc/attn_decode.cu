@@ -216,7 +216,7 @@ void wr_decode_plan(uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer, cons
 // ctx->lock and has validated the arguments.
 int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
                      const uint32_t *seq_lens, const float *dq, float *dout, uint32_t n_q,
-                     float scale_override, uint32_t window, int emit_triples, const wr_decode_xchg *xchg,
+                     float scale_override, uint32_t window, int emit_triples, wr_decode_xchg *xchg,
                      bool early_tiles)
 {
     const uint32_t n_kv = kv[0]->n_kv, hd = kv[0]->hd;
@@ -242,14 +242,29 @@ int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, u
         p.x_world = 0;
         p.x_step = 0;
         p.x_done = nullptr;
+        p.x_recv = 0;
+        p.x_max_rows = 0;
+        p.x_rows_in = nullptr;
+        p.x_row_flag_in = nullptr;
         if (xchg) {
             for (uint32_t w = 0; w < xchg->world; ++w) {
                 p.x_rows[w] = xchg->rows[w];
                 p.x_flag[w] = xchg->flag[w];
+                p.x_row_flag[w] = xchg->row_flag[w];
             }
             p.x_done = xchg->done;
             p.x_world = xchg->world;
             p.x_step = xchg->step;
+            p.x_max_rows = xchg->max_rows;
+            p.x_rows_in = xchg->rows_in;
+            p.x_row_flag_in = xchg->row_flag_in;
+            // The merge warps can take the other ranks' rows and finish the output themselves when
+            // every row of this rank goes through them, i.e. every session has at least two chunks.
+            bool all_merged = xchg->want_recv;
+            for (uint32_t s = 0; s < n_sess; ++s)
+                if (p.n_chunks[s] < 2) all_merged = false;
+            p.x_recv = all_merged ? 1u : 0u;
+            xchg->did_recv = all_merged;
         }
         if (!(ctx->attr_flags & 1u)) {
             WR_CUDA_TRY(cudaFuncSetAttribute(attn_decode_hd128_kernel<1>,

@@ -110,18 +110,29 @@ struct params {
     uint32_t *x_flag[WR_CUDA_XCHG_MAX_WORLD];    // per rank: this rank's step flag in that rank's buffer
     int *x_done;                                 // rows of this launch that have been stored everywhere
     uint32_t x_world, x_step;
+    uint32_t *x_row_flag[WR_CUDA_XCHG_MAX_WORLD];// per rank: this rank's per-row flags in that rank's buffer
+    const float *x_rows_in;                      // this rank's buffer: every rank's rows of this step, [world][max_rows][132]
+    const uint32_t *x_row_flag_in;               // ... and their per-row flags, [world][max_rows]
+    uint32_t x_max_rows;
+    uint32_t x_recv;                             // merge warps also receive, merge across ranks and write `out` (final rows)
     // An engine may request its first K/V tile before the earlier kernels have completed, unless
     // that tile is the session's last page (where the row appended just before this launch lands).
     // Set by the host only where it knows that every other page is settled (wr_cuda_decode_step).
     uint32_t early_tiles;
 };
 
-// Stores of one finished warp's rows are done: count them, and when every row of the launch
-// has been stored on every rank, publish the step number to all ranks (system-scope release).
-__device__ __forceinline__ void xchg_rows_done(const params &p, uint32_t rows, uint32_t lane)
+// Stores of one finished warp's rows (row_first .. row_first + rows - 1) are done: flag each row on
+// every rank, count them, and when every row of the launch has been stored on every rank, publish the
+// step number to all ranks as well.
+__device__ __forceinline__ void xchg_rows_done(const params &p, uint32_t row_first, uint32_t rows, uint32_t lane)
 {
-    __threadfence_system();                      // this lane's peer stores are ordered before the count
+    __threadfence_system();                      // this lane's peer stores are ordered before the flags and the count
     __syncwarp();
+    // per-row flags, for receivers that take rows one by one (relaxed stores after the fence above)
+    for (uint32_t i = lane; i < rows * p.x_world; i += 32) {
+        const uint32_t w = i % p.x_world, r = row_first + i / p.x_world;
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.x_row_flag[w] + r), "r"(p.x_step) : "memory");
+    }
     if (lane == 0) {
         const uint32_t total = p.n_sess * p.n_q;
         if ((uint32_t)atomicAdd(p.x_done, (int)rows) + rows == total) {
@@ -284,7 +295,38 @@ __device__ __forceinline__ void merge_head_pair(const params &p, size_t row0, si
             reinterpret_cast<float4 *>(p.out + (row0 + hs) * kHd)[lane] = a4;
         }
     }
-    if (p.x_world > 0 && !dry_run) xchg_rows_done(p, min(2u, heads_here - hs0), lane);
+    if (p.x_world > 0 && !dry_run) {
+        const uint32_t nrow = min(2u, heads_here - hs0), first = (uint32_t)row0 + hs0;
+        xchg_rows_done(p, first, nrow, lane);
+        if (p.x_recv) {
+            // Take the same rows from every rank (bounded wait on their per-row flags in this rank's
+            // buffer), merge in rank order and write the final rows: no second kernel.
+            const long long t0 = clock64();
+            for (;;) {
+                bool mine = true;
+                for (uint32_t i = lane; i < nrow * p.x_world; i += 32) {
+                    const uint32_t g = i % p.x_world, r = first + i / p.x_world;
+                    uint32_t seen;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];"
+                                 : "=r"(seen)
+                                 : "l"(p.x_row_flag_in + (size_t)g * p.x_max_rows + r)
+                                 : "memory");
+                    mine = mine && (seen == p.x_step);
+                }
+                if (__all_sync(0xffffffffu, mine)) break;
+                const bool late = clock64() - t0 > p.wait_limit;
+                if (__any_sync(0xffffffffu, late)) {
+                    if (lane == 0) atomicCAS(p.err, 0, 22);
+                    return;
+                }
+            }
+            __syncwarp();
+            for (uint32_t e = 0; e < nrow; ++e) {
+                const float4 r4 = wr_merge_ranks(p.x_rows_in, p.x_world, p.x_max_rows, kTripleStride, first + e, lane);
+                reinterpret_cast<float4 *>(p.out + (size_t)(first + e) * kHd)[lane] = r4;
+            }
+        }
+    }
 }
 
 // One tile of work, with everything the compute loop needs to know about it.
@@ -381,13 +423,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
             if (p.n_chunks[s] != 0) continue;
             if (p.x_world > 0) {
                 // engine warp w writes rows w, w + kWarps, ... of the session to every rank
-                uint32_t mine = 0;
-                for (uint32_t r = warp; r < p.n_q; r += kWarps, ++mine)
+                for (uint32_t r = warp; r < p.n_q; r += kWarps) {
                     for (uint32_t w = 0; w < p.x_world; ++w) {
                         float *tr = p.x_rows[w] + ((size_t)p.row[s] * p.n_q + r) * kTripleStride;
                         for (uint32_t i = lane; i < (uint32_t)kTripleStride; i += 32) tr[i] = (i == 0) ? WR_NEG_SENTINEL : 0.f;
                     }
-                if (mine) xchg_rows_done(p, mine, lane);
+                    xchg_rows_done(p, p.row[s] * p.n_q + r, 1, lane);
+                }
                 continue;
             }
             float *base = p.out + (size_t)p.row[s] * p.n_q * kTripleStride;
@@ -706,7 +748,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_hd128_kernel(const pa
                 }
             }
 
-            if (direct && p.x_world > 0) xchg_rows_done(p, heads_here, lane);
+            if (direct && p.x_world > 0) xchg_rows_done(p, (uint32_t)row0, heads_here, lane);
             if (!direct) {
                 // Note the arrival (signalled as described above).  __syncwarp
                 // orders every lane's partial stores before lane 0's release; the

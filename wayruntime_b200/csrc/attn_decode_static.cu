@@ -147,6 +147,10 @@ extern "C" int wr_cuda_attn_decode_static(wr_cuda_ctx *ctx, uint32_t n_sess, wr_
     p.x_world = 0;
     p.x_step = 0;
     p.early_tiles = 0;
+    p.x_recv = 0;
+    p.x_max_rows = 0;
+    p.x_rows_in = nullptr;
+    p.x_row_flag_in = nullptr;
     p.x_done = nullptr;
     p.scale = (scale_override > 0.0f) ? scale_override : 1.0f / sqrtf((float)hd);
     // The array keeps whatever the previous call (or an aborted one) left:

@@ -36,7 +36,13 @@ struct wr_cuda_xchg {
 
 namespace {
 
-constexpr size_t kFlagBytes = 1024;              // flags[2][world] at the head of a buffer
+// Buffer of one rank: step flags [2][world] (kFlagBytes), per-row flags [2][world][max_rows], then the
+// rows [2][world][max_rows][4 + hd]; the first index is the step's parity.
+constexpr size_t kFlagBytes = 1024;
+__host__ __device__ inline size_t row_flag_bytes(uint32_t world, uint32_t max_rows)
+{
+    return (((size_t)2 * world * max_rows * sizeof(uint32_t)) + 255u) & ~(size_t)255u;
+}
 
 struct xchg_params {
     char *peer[WR_CUDA_XCHG_MAX_WORLD];
@@ -62,7 +68,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *addr)
 __device__ __forceinline__ float *slot_rows(char *buf, uint32_t parity, uint32_t src, const xchg_params &p)
 {
     const size_t stride = WR_CUDA_TRIPLE_PAD + p.hd;
-    return reinterpret_cast<float *>(buf + kFlagBytes) + ((size_t)parity * p.world + src) * p.max_rows * stride;
+    return reinterpret_cast<float *>(buf + kFlagBytes + row_flag_bytes(p.world, p.max_rows)) +
+           ((size_t)parity * p.world + src) * p.max_rows * stride;
 }
 __device__ __forceinline__ uint32_t *slot_flag(char *buf, uint32_t parity, uint32_t src, const xchg_params &p)
 {
@@ -121,24 +128,10 @@ __global__ void __launch_bounds__(256) attn_exchange_combine_kernel(const xchg_p
     // 4. merge in rank order: one thread per four output elements
     const uint32_t out_f4 = p.hd / 4;
     const uint32_t total_out = p.n_rows * out_f4;
+    const float *rows_in = slot_rows(p.peer[p.rank], p.parity, 0, p);
     for (uint32_t i = gtid; i < total_out; i += gsize) {
         const uint32_t row = i / out_f4, c = i % out_f4;
-        float mstar = WR_NEG_SENTINEL;
-        for (uint32_t g = 0; g < p.world; ++g)
-            mstar = fmaxf(mstar, __ldcg(slot_rows(p.peer[p.rank], p.parity, g, p) + (size_t)row * stride));
-        float L = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t g = 0; g < p.world; ++g) {
-            const float *tr = slot_rows(p.peer[p.rank], p.parity, g, p) + (size_t)row * stride;
-            const float m = __ldcg(tr);
-            const float wgt = (m == WR_NEG_SENTINEL) ? 0.f : __expf(m - mstar);
-            L += wgt * __ldcg(tr + 1);
-            const float4 o = __ldcg(reinterpret_cast<const float4 *>(tr + WR_CUDA_TRIPLE_PAD) + c);
-            acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
-        }
-        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (L > 0.f) r = make_float4(acc.x / L, acc.y / L, acc.z / L, acc.w / L);
-        reinterpret_cast<float4 *>(p.out)[i] = r;
+        reinterpret_cast<float4 *>(p.out)[i] = wr_merge_ranks(rows_in, p.world, p.max_rows, stride, row, c);
     }
 }
 
@@ -160,7 +153,8 @@ extern "C" int wr_cuda_xchg_create(wr_cuda_ctx *ctx, uint32_t world, uint32_t ra
     x->rank = rank;
     x->max_rows = max_rows;
     x->hd = head_dim;
-    x->bytes = kFlagBytes + (size_t)2 * world * max_rows * (WR_CUDA_TRIPLE_PAD + head_dim) * sizeof(float);
+    x->bytes = kFlagBytes + row_flag_bytes(world, max_rows) +
+               (size_t)2 * world * max_rows * (WR_CUDA_TRIPLE_PAD + head_dim) * sizeof(float);
     if (cudaMalloc((void **)&x->local, x->bytes) != cudaSuccess ||
         cudaMalloc((void **)&x->done, sizeof(int)) != cudaSuccess) {
         (void)cudaGetLastError();
@@ -283,9 +277,11 @@ extern "C" int wr_cuda_attn_exchange_combine(wr_cuda_ctx *ctx, wr_cuda_xchg *x, 
 }
 
 // Key-sharded decode with the exchange fused into the decode kernel: the warps that finish
-// a (session, q head) triple store it straight into every rank's exchange buffer, the last
-// one publishes this rank's step flag, and a small second kernel waits for every rank's
-// flag and merges.  Same result bits as wr_cuda_attn_decode_partial + wr_cuda_attn_exchange_combine.
+// a (session, q head) triple store it straight into every rank's exchange buffer, flag the row
+// there, then wait for the same row from every rank and merge — all inside the decode kernel
+// when every session of this rank has at least two key chunks.  Otherwise the last warp
+// publishes this rank's step flag and a small second kernel waits for every rank's flag and
+// merges.  Same result bits as wr_cuda_attn_decode_partial + wr_cuda_attn_exchange_combine.
 extern "C" int wr_cuda_attn_decode_exchange(wr_cuda_ctx *ctx, wr_cuda_xchg *x, uint32_t n_sess,
                                             wr_cuda_kv *const *kv, uint32_t layer, const uint32_t *seq_lens,
                                             const float *q, float *out, uint32_t n_q_heads, float scale_override)
@@ -316,16 +312,27 @@ extern "C" int wr_cuda_attn_decode_exchange(wr_cuda_ctx *ctx, wr_cuda_xchg *x, u
     p.parity = x->step & 1u;
     wr_decode_xchg dx;
     const size_t stride = WR_CUDA_TRIPLE_PAD + x->hd;
+    const size_t rows_off = kFlagBytes + row_flag_bytes(x->world, x->max_rows);
     for (uint32_t w = 0; w < x->world; ++w) {
-        dx.rows[w] = reinterpret_cast<float *>(x->peer[w] + kFlagBytes) +
+        dx.rows[w] = reinterpret_cast<float *>(x->peer[w] + rows_off) +
                      ((size_t)p.parity * x->world + x->rank) * x->max_rows * stride;
         dx.flag[w] = reinterpret_cast<uint32_t *>(x->peer[w]) + p.parity * x->world + x->rank;
+        dx.row_flag[w] = reinterpret_cast<uint32_t *>(x->peer[w] + kFlagBytes) +
+                         ((size_t)p.parity * x->world + x->rank) * x->max_rows;
     }
+    dx.rows_in = reinterpret_cast<const float *>(x->local + rows_off) + (size_t)p.parity * x->world * x->max_rows * stride;
+    dx.row_flag_in = reinterpret_cast<const uint32_t *>(x->local + kFlagBytes) + (size_t)p.parity * x->world * x->max_rows;
     dx.done = x->done;
     dx.world = x->world;
     dx.step = p.step;
+    dx.max_rows = x->max_rows;
+    dx.want_recv = true;
+    dx.did_recv = false;
     rc = wr_decode_launch(ctx, n_sess, kv, layer, seq_lens, q, out, n_q_heads, scale_override, 0, 1, &dx);
     if (rc != WR_CUDA_OK) return rc;
+    // Every session of this rank had at least two chunks: the decode kernel's merge warps have also
+    // received the other ranks' rows and written the result; nothing is left for a second kernel.
+    if (dx.did_recv) return WR_CUDA_OK;
     const uint32_t work = n_rows * (x->hd / 4);
     const uint32_t blocks = std::max(1u, std::min((work + 255u) / 256u, (uint32_t)ctx->sm_count));
     attn_exchange_combine_kernel<<<blocks, 256, 0, ctx->stream>>>(p);

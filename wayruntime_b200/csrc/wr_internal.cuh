@@ -127,15 +127,20 @@ struct wr_batch_desc {
 struct wr_decode_xchg {
     float *rows[WR_CUDA_XCHG_MAX_WORLD];       // per rank: this rank's row slot in that rank's buffer
     uint32_t *flag[WR_CUDA_XCHG_MAX_WORLD];    // per rank: this rank's step flag in that rank's buffer
+    uint32_t *row_flag[WR_CUDA_XCHG_MAX_WORLD];// per rank: this rank's per-row flags in that rank's buffer
+    const float *rows_in;                      // this rank's own buffer: every rank's rows of this step ...
+    const uint32_t *row_flag_in;               // ... and their per-row flags, [world][max_rows]
     int *done;
-    uint32_t world, step;
+    uint32_t world, step, max_rows;
+    bool want_recv;                            // merge in the decode kernel itself where the plan allows it
+    bool did_recv;                             // out: it did (no second kernel needed)
 };
 int wr_decode_validate(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
                        const uint32_t *seq_lens, const void *q, const void *out, uint32_t n_q, int mem,
                        int emit_triples);
 int wr_decode_launch(wr_cuda_ctx *ctx, uint32_t n_sess, wr_cuda_kv *const *kv, uint32_t layer,
                      const uint32_t *seq_lens, const float *dq, float *dout, uint32_t n_q,
-                     float scale_override, uint32_t window, int emit_triples, const wr_decode_xchg *xchg,
+                     float scale_override, uint32_t window, int emit_triples, wr_decode_xchg *xchg,
                      bool early_tiles = false);
 
 int wr_ctx_reserve_stage(wr_cuda_ctx *ctx, size_t dev_bytes, size_t host_bytes);
@@ -334,6 +339,30 @@ __device__ __forceinline__ void split_half2(float x, float y, uint32_t &hi, uint
     __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
     hi = *reinterpret_cast<uint32_t *>(&h);
     lo = *reinterpret_cast<uint32_t *>(&l);
+}
+
+// Cross-rank merge of one row's (m, l, o) triples, rank order, for output elements 4c .. 4c+3: the
+// reference's online-softmax update (src/core/kernels.c:1503-1506) across shards.  One function for
+// every kernel that merges, so that they all give the same bits.  rows: [world][max_rows][4 + hd].
+__device__ __forceinline__ float4 wr_merge_ranks(const float *rows, uint32_t world, uint32_t max_rows,
+                                                 uint32_t stride, uint32_t row, uint32_t c)
+{
+    float mstar = WR_NEG_SENTINEL;
+    for (uint32_t g = 0; g < world; ++g)
+        mstar = fmaxf(mstar, __ldcg(rows + ((size_t)g * max_rows + row) * stride));
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t g = 0; g < world; ++g) {
+        const float *tr = rows + ((size_t)g * max_rows + row) * stride;
+        const float m = __ldcg(tr);
+        const float wgt = (m == WR_NEG_SENTINEL) ? 0.f : __expf(m - mstar);
+        L += wgt * __ldcg(tr + 1);
+        const float4 o = __ldcg(reinterpret_cast<const float4 *>(tr + WR_CUDA_TRIPLE_PAD) + c);
+        acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
+    }
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (L > 0.f) r = make_float4(acc.x / L, acc.y / L, acc.z / L, acc.w / L);
+    return r;
 }
 
 // The reference's truncating F32 -> F16 (src/core/quant.c:121-136).
