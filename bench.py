@@ -335,6 +335,24 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
         ms = float(t.item())
     finite = bool(torch.isfinite(out).all().item())
 
+    # ---- this rank's share of the step on its own: the partial attention, no exchange (max over ranks)
+    for _ in range(3):
+        ctx.attn_decode_partial(batch, 0, lens, q, triples, HQ)
+    ctx.sync()
+    if world > 1:
+        dist.barrier()
+    a.record(stream)
+    for _ in range(reps):
+        ctx.attn_decode_partial(batch, 0, lens, q, triples, HQ)
+    b.record(stream)
+    ctx.sync()
+    torch.cuda.synchronize()
+    partial_ms = a.elapsed_time(b) / reps
+    if world > 1:
+        t = torch.tensor([partial_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        partial_ms = float(t.item())
+
     # ---- parity of session 0 (all heads) against the CPU reference, on rank 0
     want0 = None
     parity = None
@@ -433,6 +451,7 @@ def measure_split_kv(ctx, stream, torch, rank, world, reps):
     res = {"cfg": f"c4 16x{LC_CTX} keys sharded over {world} GPU(s)", "ms_per_step": r4(ms),
            "tok_s": r4(N_SESS / (ms * 1e-3)), "hbm_gbs_per_gpu": r4(per_gpu),
            "frac_per_gpu": r4(per_gpu / peak), "peak_source": f"of {src}",
+           "partial_attention_only_ms": r4(partial_ms),
            "collective": "none" if world == 1 else "NCCL all-gather of triples",
            "parity_max_abs_err": r4(parity), "parity_sample": "session 0, 32 heads, 32768 keys vs CPU reference",
            "output_finite": finite}

@@ -113,3 +113,56 @@ def test_wait_limit_argument_is_checked():
         ctx.set_wait_limit(0)
     assert e.value.status == -4
     ctx.close()
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_in_kernel_receive_over_a_world_of_local_ranks(world):
+    """Key-sharded decode with the receive fused into the decode kernel, for 4 and 8
+    ranks whose exchange objects live in this process on one device.  Ranks cannot
+    wait for each other here (their kernels run one after another), so ranks
+    1 .. world-1 step first with a short wait limit: each delivers its rows and flags
+    to every rank's buffer, then gives up waiting for the ranks that have not run yet —
+    reported as WR_ERR_INTERNAL, nothing faults.  Rank 0 steps last, finds every
+    rank's rows, and must produce the bits of wr_cuda_attn_decode_partial per shard +
+    wr_cuda_attn_combine."""
+    import torch
+    import wayruntime_b200 as wr
+    ctx = wr.Context(0, attn_max_seq=65536)
+    P = port()
+    hq, hkv, hd, n_sess, shard = 8, 2, HD, 3, 640            # 10 tiles per shard: several chunks, so merge warps carry the rows
+    rows = n_sess * hq
+    q = torch.from_numpy(_gen.normal(4000, (n_sess, hq, hd))).cuda()
+    shards, triples = [], []
+    for r in range(world):
+        kvs = []
+        for s in range(n_sess):
+            k = P.f32_to_f16(_gen.normal(4100 + 10 * r + s, (shard, hkv, hd)))
+            v = P.f32_to_f16(_gen.normal(4500 + 10 * r + s, (shard, hkv, hd)))
+            kvs.append(make_cache(ctx, k, v))
+        t = torch.empty((rows, wr.TRIPLE_PAD + hd), dtype=torch.float32, device="cuda")
+        ctx.attn_decode_partial(kvs, 0, [shard] * n_sess, q, t, hq)
+        shards.append(kvs)
+        triples.append(t)
+    want = torch.empty((rows, hd), dtype=torch.float32, device="cuda")
+    ctx.attn_combine(world, rows, hd, torch.stack(triples).contiguous(), want)
+    ctx.sync()
+    xs = [wr.Exchange(ctx, world, r, rows, hd) for r in range(world)]
+    wr.Exchange.connect_local(xs)
+    for r in range(1, world):
+        out = torch.empty((n_sess, hq, hd), dtype=torch.float32, device="cuda")
+        ctx.set_wait_limit(SHORT)
+        xs[r].decode(shards[r], 0, [shard] * n_sess, q, out, hq)
+        ctx.set_wait_limit(4_000_000_000)
+        with pytest.raises(wr.WrCudaError) as e:
+            ctx.sync()                                          # the ranks it waited for have not run
+        assert e.value.status == -10
+    got = torch.full((n_sess, hq, hd), float("nan"), dtype=torch.float32, device="cuda")
+    xs[0].decode(shards[0], 0, [shard] * n_sess, q, got, hq)
+    ctx.sync()
+    assert torch.equal(got.view(rows, hd), want)
+    for x in xs:
+        x.close()
+    for kvs in shards:
+        for kv in kvs:
+            kv.close()
+    ctx.close()
