@@ -857,10 +857,14 @@ def run_gpu_arm(args):
     hv = torch.randn((N_SESS, HKV, HD), dtype=torch.float32).pin_memory()
     hout = torch.empty((N_SESS, HQ, HD), dtype=torch.float32).pin_memory()
 
+    # the call a C host makes: arguments are pointers it already holds, so they are resolved once
+    host_step = ctx.prepared_decode_step(batch, pos_arr, hq_src, hk, hv, hout, HQ, theta=THETA)
+    hout_view = hout.numpy()
+
     def step_host(i):
         # Host Q/K/V in, attention rows out: copies and sync are inside the call.
-        ctx.decode_step(batch, i % N_ROT_LAYERS, pos_arr, hq_src, hk, hv, hout, HQ, theta=THETA)
-        return float(hout[0, 0, 0])                     # the step's result is read on the host
+        host_step(i % N_ROT_LAYERS)
+        return float(hout_view[0, 0, 0])                # the step's result is read on the host
 
     for i in range(max(args.warmup, 3)):
         step_host(i)

@@ -266,3 +266,41 @@ def test_decode_step_page_locked_views_at_odd_offsets_are_staged(ctx):
         kv.write_rows(0, 0, 0, dev)
     assert e.value.status == -4
     kv.close()
+
+
+def test_prepared_decode_step_is_the_same_call(ctx):
+    """Context.prepared_decode_step resolves the arguments once; each step(layer) must be
+    wr_cuda_decode_step on those arguments: same attention rows, same cache bytes."""
+    import torch
+    import wayruntime_b200 as wr
+    hq, hkv, hd = 8, 2, 128
+    lens = [70, 3, 200]
+    n = len(lens)
+    q = torch.from_numpy(_gen.normal(71, (n, hq, hd))).pin_memory()
+    k = torch.from_numpy(_gen.normal(72, (n, hkv, hd))).pin_memory()
+    v = torch.from_numpy(_gen.normal(73, (n, hkv, hd))).pin_memory()
+    results = []
+    for prepared in (False, True):
+        kvs = [ctx.kv_create(2, hkv, hd, 256) for _ in lens]
+        out = torch.full((n, hq, hd), float("nan")).pin_memory()
+        pos = wr.Batch.u32([ln - 1 for ln in lens])
+        batch = wr.Batch(kvs)
+        step = ctx.prepared_decode_step(batch, pos, q, k, v, out, hq, theta=5e5) if prepared else None
+        outs = []
+        for t in range(3):
+            layer = t % 2
+            if prepared:
+                step(layer)
+            else:
+                ctx.decode_step(batch, layer, pos, q, k, v, out, hq, theta=5e5)
+            outs.append(out.numpy().copy())
+            for i in range(n):
+                pos[i] += 1 if layer == 1 else 0          # the caller's own array: advanced in place
+        rows = [kv.read_rows(0, 0, lens[i] - 1, 2) for i, kv in enumerate(kvs)]
+        results.append((outs, rows))
+        for kv in kvs:
+            kv.close()
+    for a, b in zip(results[0][0], results[1][0]):
+        assert np.array_equal(bits(a), bits(b))
+    for a, b in zip(results[0][1], results[1][1]):
+        assert np.array_equal(a, b)

@@ -243,6 +243,32 @@ class Context:
                                            mem)
         _check(rc, "wr_cuda_decode_step")
 
+    def prepared_decode_step(self, kvs, positions, q, k_rows, v_rows, out, n_q_heads, theta=10000.0,
+                             n_rot_pairs=0, rope=True, scale=0.0, window=0):
+        """wr_cuda_decode_step with everything but the layer resolved once: returns `step(layer)`.
+        For a serving loop that steps the same sessions and buffers over and over — the C caller's
+        situation, where the arguments are pointers it already holds — so that a call costs the
+        library's work and not the marshalling of its arguments.  positions: a list (copied once) or
+        a ctypes array from Batch.u32 that the caller updates in place between steps."""
+        qp, qm, _q = _buf(q)
+        kp, km, _k = _buf(k_rows)
+        vp, vm, _v = _buf(v_rows)
+        op, om, _o = _buf(out)
+        mem = _same_mem(qm, km, vm, om)
+        handles, pos = self._handles(kvs), self._u32s(positions)
+        n = len(kvs)
+        fn, ctx_h = self._lib.wr_cuda_decode_step, self._h
+        flags = APPEND_ROPE if rope else 0
+        keep = (_q, _k, _v, _o, handles, pos)
+
+        def step(layer, _keep=keep):
+            rc = fn(ctx_h, n, handles, layer, pos, qp, kp, vp, op, n_q_heads, theta, n_rot_pairs, flags, scale,
+                    window, mem)
+            if rc != 0:
+                raise WrCudaError(int(rc), "wr_cuda_decode_step")
+
+        return step
+
     def kv_append(self, kvs, layer, positions, k_rows, v_rows, q_rows=None, n_q_heads=0,
                   theta=10000.0, n_rot_pairs=0, rope=True, n_tokens=1):
         kp, km, _k = _buf(k_rows)
