@@ -554,6 +554,7 @@ def measure_kv_head_sharded(ctx, stream, torch, rank, world, reps):
 
 WHOLE_MODEL_SHAPE = dict(n_layers=28, hidden=1024, n_q=16, n_kv=8, head_dim=128, ffn=3072, vocab=151936)
 WHOLE_MODEL_PROMPT, WHOLE_MODEL_TOKENS = 64, 32
+WHOLE_MODEL_BATCH_PROMPT, WHOLE_MODEL_BATCH_STEPS = 8, 6
 
 
 def measure_whole_model():
@@ -604,7 +605,37 @@ def measure_whole_model():
                          "attention_calls": res["counters"][3], "matmul_calls": res["counters"][0]}
     finally:
         os.environ.pop("WR_B200_GLUE", None)
-        os.remove(path)
+        batch_path = path + ".batch"
+        os.replace(path, batch_path)                      # kept for the batched section below
+    # the batched step (wr_batch_step, 16 sessions): reference against the device layer stack
+    try:
+        bprompts = [wb.seeded_prompt(WHOLE_MODEL_BATCH_PROMPT + i, shape["vocab"], SEED + 100 + i)
+                    for i in range(N_SESS)]
+        batch = {}
+        for name, lib_path, glue in (("reference", ref_path, None), ("b200_device_glue", b200_path, "device")):
+            if glue:
+                os.environ["WR_B200_GLUE"] = glue
+            lib = wb.Library(lib_path)
+            try:
+                rb = wb.bench_batch(lib, batch_path, bprompts, WHOLE_MODEL_BATCH_STEPS, shape["vocab"])
+            finally:
+                lib.close()
+                os.environ.pop("WR_B200_GLUE", None)
+            batch[name] = {"decode_tok_s": r4(wb.rate(rb["sessions"] * rb["steps"], rb["decode_s"])),
+                           "ms_per_batched_step": r4(1e3 * rb["decode_s"] / rb["steps"]),
+                           "prefill_tok_s": r4(wb.rate(rb["n_prefill"], rb["prefill_s"])), "ids": rb["ids"]}
+        same_b = sum(a == b for a, b in zip(batch["reference"].pop("ids"), batch["b200_device_glue"].pop("ids")))
+        batch["workload"] = (f"wr_batch_step, {N_SESS} sessions, prompts of {WHOLE_MODEL_BATCH_PROMPT}-"
+                             f"{WHOLE_MODEL_BATCH_PROMPT + N_SESS - 1} tokens, {WHOLE_MODEL_BATCH_STEPS} greedy steps")
+        batch["sessions_with_identical_greedy_ids"] = f"{same_b} of {N_SESS}"
+        batch["decode_speedup_vs_reference"] = r4(batch["b200_device_glue"]["decode_tok_s"] /
+                                                  batch["reference"]["decode_tok_s"])
+        out["batched_step"] = batch
+    except Exception as exc:
+        out["batched_step"] = {"error": f"{type(exc).__name__}: {exc}"}
+    finally:
+        if os.path.exists(batch_path):
+            os.remove(batch_path)
     for name in ("b200_attention_only", "b200_device_glue"):
         same = 0
         for a, b in zip(ids["reference"], ids[name]):

@@ -112,13 +112,14 @@ __device__ __forceinline__ bool reduce_writer(int lane)
 // y[r][n] = sum_k W[n][k] * x[r][k], optionally with RMSNorm fused on x, and a
 // residual add or SiLU(gate)*up on the way out.  Two kernels, one arithmetic:
 // K is cut into four quarters; inside a quarter lane l takes the 16-byte
-// vectors l, l+32, ... in ascending order with fused multiply-adds; a quarter's
-// lane partials are added by the xor butterfly (offsets 16, 8, 4, 2, 1); the
-// four quarter sums are added in order.  The fused norm multiplies x by the
-// norm weight first and the finished sum by 1/sqrt(mean(x^2)+eps) last, the sum
-// of squares following the same quarter / lane / butterfly order.  Because both
-// kernels compute every output by exactly this recipe, a row's bits do not
-// depend on how many rows share the call or on which kernel served it.
+// vectors l, l+32, ... in ascending order with fused multiply-adds, starting
+// from zero; lane l then adds its four quarter sums in order; the 32 lane sums
+// are added by the xor butterfly (offsets 16, 8, 4, 2, 1).  The fused norm
+// multiplies x by the norm weight first and the finished sum by
+// 1/sqrt(mean(x^2)+eps) last, the sum of squares following the same quarter /
+// lane / butterfly order.  Because both kernels compute every output by exactly
+// this recipe, a row's bits do not depend on how many rows share the call or on
+// which kernel served it.
 //
 //   gemv_splitk_kernel (<= 4 activation rows): a CTA owns C weight rows and
 //     its four warps take one quarter each, so every lane has all its loads in
@@ -181,7 +182,8 @@ constexpr int kPrefetchRegs = 16;        // 16-byte weight vectors a lane holds 
 template <int RG, int C>
 __global__ void __launch_bounds__(kGemvThreads) gemv_splitk_kernel(const GemvParams p)
 {
-    __shared__ float red[kGemvWarps][C * RG + RG];
+    __shared__ float part[kGemvWarps][C * RG + RG][32];      // per quarter (= warp): every lane's partial sums
+    __shared__ float red[C * RG + RG];
     pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t r0 = blockIdx.y * RG;
@@ -251,17 +253,22 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_splitk_kernel(const GemvPar
         for (int c = 0; c < C; ++c) w[c] = ldg_stream(wrow[c] + 4 * v);
         step(v, w);
     }
-    {
-        constexpr int M = C * RG;
-        float v[M];
+    constexpr int M = C * RG;
 #pragma unroll
-        for (int i = 0; i < M; ++i) v[i] = acc[i / RG][i % RG];
-        const int idx = warp_reduce_many<M>(v, lane);
-        if (reduce_writer<M>(lane)) red[warp][idx] = v[0];
-        if (p.norm_w) {
-            const int ir = warp_reduce_many<RG>(ss, lane);
-            if (reduce_writer<RG>(lane)) red[warp][M + ir] = ss[0];
-        }
+    for (int i = 0; i < M; ++i) part[warp][i][lane] = acc[i / RG][i % RG];
+    if (p.norm_w) {
+#pragma unroll
+        for (int r = 0; r < RG; ++r) part[warp][M + r][lane] = ss[r];
+    }
+    __syncthreads();
+    // every lane adds its four quarter sums in order, then the butterfly over the lanes
+    for (int idx = warp; idx < M + (p.norm_w ? RG : 0); idx += kGemvWarps) {
+        float t = part[0][idx][lane];
+#pragma unroll
+        for (int q = 1; q < kGemvWarps; ++q) t = __fadd_rn(t, part[q][idx][lane]);
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, o));
+        if (lane == 0) red[idx] = t;
     }
     __syncthreads();
     const int n_out = p.swiglu ? H * RG : C * RG;
@@ -269,22 +276,10 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_splitk_kernel(const GemvPar
         const int c = tid / RG, r = tid % RG;
         const uint32_t n = n0 + c, row = r0 + r;
         if (n < seg.n && row < p.rows) {
-            float inv = 1.0f;
-            if (p.norm_w) {
-                float t = red[0][C * RG + r];
-#pragma unroll
-                for (int w_ = 1; w_ < kGemvWarps; ++w_) t = __fadd_rn(t, red[w_][C * RG + r]);
-                inv = inv_rms_of(t, p.k, p.eps);
-            }
-            float y = red[0][c * RG + r];
-#pragma unroll
-            for (int w_ = 1; w_ < kGemvWarps; ++w_) y = __fadd_rn(y, red[w_][c * RG + r]);
-            y = __fmul_rn(y, inv);
+            const float inv = p.norm_w ? inv_rms_of(red[M + r], p.k, p.eps) : 1.0f;
+            float y = __fmul_rn(red[c * RG + r], inv);
             if (p.swiglu) {
-                float u = red[0][(c + H) * RG + r];
-#pragma unroll
-                for (int w_ = 1; w_ < kGemvWarps; ++w_) u = __fadd_rn(u, red[w_][(c + H) * RG + r]);
-                u = __fmul_rn(u, inv);
+                const float u = __fmul_rn(red[(c + H) * RG + r], inv);
                 seg.out[(size_t)row * seg.out_stride + n] = silu_mul(y, u);
             } else {
                 if (p.add) y = __fadd_rn(p.add[(size_t)row * p.add_stride + n], y);
@@ -327,11 +322,11 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(const GemvParam
                     float ss = 0.f;
                     for (uint32_t v = kq.lo(q) + lane; v < kq.hi(q); v += 32)
                         ss = sumsq4(ss, *reinterpret_cast<const float4 *>(xr + 4 * v));
-#pragma unroll
-                    for (int o = 16; o >= 1; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
                     t = (q == 0) ? ss : __fadd_rn(t, ss);
                 }
             }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, o));
             if (lane == 0) inv_rms[r] = inv_rms_of(t, p.k, p.eps);
         }
     }
@@ -339,10 +334,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(const GemvParam
     constexpr int M = NW * RG;
     constexpr int G = (M > 32) ? 32 : M;
     constexpr int NG = M / G;
-    float tot[NG];
-    int tot_idx[NG];
-#pragma unroll
-    for (int g = 0; g < NG; ++g) { tot[g] = 0.f; tot_idx[g] = 0; }
+    float lane_tot[NW][RG];                          // this lane's quarter sums, added in quarter order
 
 #pragma unroll 1
     for (uint32_t q = 0; q < 4; ++q) {
@@ -378,15 +370,21 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(const GemvParam
                 }
             }
         }
-        // this quarter's lane partials -> warp totals, added to the running sums in quarter order
 #pragma unroll
-        for (int g = 0; g < NG; ++g) {
-            float v[G];
+        for (int c = 0; c < NW; ++c)
 #pragma unroll
-            for (int i = 0; i < G; ++i) v[i] = acc[(g * G + i) / RG][(g * G + i) % RG];
-            tot_idx[g] = warp_reduce_many<G>(v, lane) + g * G;
-            tot[g] = (q == 0) ? v[0] : __fadd_rn(tot[g], v[0]);
-        }
+            for (int r = 0; r < RG; ++r) lane_tot[c][r] = (q == 0) ? acc[c][r] : __fadd_rn(lane_tot[c][r], acc[c][r]);
+    }
+    // the butterfly over the lanes, once, for all NW * RG sums
+    float tot[NG];
+    int tot_idx[NG];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+        float v[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) v[i] = lane_tot[(g * G + i) / RG][(g * G + i) % RG];
+        tot_idx[g] = warp_reduce_many<G>(v, lane) + g * G;
+        tot[g] = v[0];
     }
     __syncthreads();                                 // inv_rms is complete (and visible) for every warp
 

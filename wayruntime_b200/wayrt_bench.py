@@ -122,6 +122,58 @@ def bench(lib: Library, model_path: str, prompt_ids, n_tokens: int, vocab: int) 
     }
 
 
+def bench_batch(lib: Library, model_path: str, prompts, n_steps: int, vocab: int) -> dict:
+    """len(prompts) sessions of one model: each prefills its own prompt (all tokens but the last),
+    then the batch decodes n_steps tokens per session greedily through wr_batch_step
+    (include/wayruntime/wayruntime.h:423-444), one call per step for all sessions."""
+    L = lib.L
+    L.wr_batch_step.restype = C.c_int
+    model = C.c_void_p()
+    params = (C.c_uint8 * 512)()
+    rc = L.wr_model_load(lib.engine, model_path.encode(), params, C.byref(model))
+    if rc != 0:
+        raise RuntimeError(f"wr_model_load returned {rc}")
+    n = len(prompts)
+    sessions = []
+    try:
+        for _ in range(n):
+            s = C.c_void_p()
+            rc = L.wr_session_create(model, None, C.byref(s))
+            if rc != 0:
+                raise RuntimeError(f"wr_session_create returned {rc}")
+            sessions.append(s)
+        t0 = time.clock_gettime(time.CLOCK_MONOTONIC)
+        n_prefill = 0
+        for s, ids in zip(sessions, prompts):
+            if len(ids) > 1:
+                arr = (C.c_uint32 * (len(ids) - 1))(*ids[:-1])
+                pf = L.wr_prefill(s, arr, len(ids) - 1)
+                if pf < 0:
+                    raise RuntimeError(f"wr_prefill returned {pf}")
+                n_prefill += len(ids) - 1
+        prefill_s = time.clock_gettime(time.CLOCK_MONOTONIC) - t0
+        handles = (C.c_void_p * n)(*[s.value for s in sessions])
+        toks = (C.c_uint32 * n)(*[int(ids[-1]) for ids in prompts])
+        outp = (C.POINTER(C.c_float) * n)()
+        ids_out = [[] for _ in range(n)]
+        t0 = time.clock_gettime(time.CLOCK_MONOTONIC)
+        for _ in range(n_steps):
+            rc = L.wr_batch_step(handles, toks, n, outp)
+            if rc != n:
+                raise RuntimeError(f"wr_batch_step returned {rc}")
+            for i in range(n):
+                nxt = int(np.argmax(np.ctypeslib.as_array(outp[i], (vocab,))))
+                toks[i] = nxt
+                ids_out[i].append(nxt)
+        decode_s = time.clock_gettime(time.CLOCK_MONOTONIC) - t0
+    finally:
+        for s in sessions:
+            L.wr_session_destroy(s)
+        L.wr_model_free(model)
+    return {"sessions": n, "n_prefill": n_prefill, "prefill_s": prefill_s, "steps": n_steps, "decode_s": decode_s,
+            "ids": ids_out}
+
+
 def rate(n: int, s: float) -> float:
     return n / s if s > 0 else 0.0
 
