@@ -104,7 +104,6 @@ struct prefill_params {
     const uint64_t *pages;      // page table of (session, layer)
     const char *page_base;      // non-null: page t = page_base + t * page_bytes
     uint64_t page_bytes;
-    float *out;                 // [n, n_q, hd] F32
     int *err;
     int *sched;                 // [0] next work tile, [1] CTAs that have left
     uint32_t n, p0, n_q, n_kv, group, window, n_qtiles, n_tiles;
@@ -134,8 +133,9 @@ struct smem_layout {
     uint64_t tile_ready[kTileSlots];
     tile_info tile[kTileSlots];
     uint32_t tmem_base;
-    // per softmax warp: 32 rows x 32 output values on their way out (16-byte pieces swizzled by row)
-    alignas(128) uint8_t out_stage[8][32 * 128];
+    // per softmax warp: 32 rows x 32 output values on their way out (16-byte pieces swizzled by row:
+    // the 128-byte swizzle of the output tensor map)
+    alignas(1024) uint8_t out_stage[8][32 * 128];
 };
 static_assert(sizeof(smem_layout) <= 232448, "the CTA's shared memory is 227 KB at most");
 
@@ -307,6 +307,20 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
         ::"r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+// Tiled 2-D tensor copy shared -> global (rows past the tensor's extent are dropped), tracked by
+// the issuing thread's bulk group.  x in elements; x * 4 bytes is a multiple of 16 for the caller.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *src_smem, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src_smem)), "r"(x), "r"(y)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// The issuing thread's earlier bulk stores have finished reading shared memory.
+__device__ __forceinline__ void tma_store_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 
 // ---- work tiles -------------------------------------------------------------
 //
@@ -375,7 +389,8 @@ __device__ __forceinline__ block_range range_of(const prefill_params &p, uint32_
 // ---- the kernel ------------------------------------------------------------
 
 __global__ void __launch_bounds__(kThreads, 1)
-attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefill_params p)
+attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap o_map,
+                          const prefill_params p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     smem_layout &sm = *reinterpret_cast<smem_layout *>(smem_raw);
@@ -860,38 +875,35 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const prefi
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.o_free[b]);       // the next tile may overwrite O
-            // A thread holds one row, but a store instruction in which every lane writes to a row of
+            // A thread holds one row, and a store instruction in which every lane writes to a row of
             // its own touches 32 cache lines for 512 bytes (measured: 6500 clk to get a tile's 128 KB
-            // out, with every shared-memory access of the CTA queued behind it).  So the warp turns
-            // its 32 x 32 pieces through shared memory: each store instruction then writes four
-            // whole 128-byte lines.  Nothing is waited for; the warp goes straight on to its next tile.
+            // out, with every shared-memory access of the CTA queued behind it).  So the warp puts
+            // its 32 x 32 pieces into shared memory, swizzled, and the TMA unit writes them out as
+            // whole lines (rows past the prompt are outside the tensor and dropped).  A piece is
+            // waited for only when its buffer is needed again.
             pdl_wait();                                      // output rows: after the earlier kernels have ended
             {
                 const float inv = (l > 0.f) ? 1.0f / l : 0.f;
                 uint8_t *stage = sm.out_stage[warp];
-                const uint32_t sub = lane >> 3, piece = lane & 7u;       // read side: row within a group of four, 16-byte piece
 #pragma unroll
                 for (int c = 0; c < kHd / 32; ++c) {
+                    if (lane == 0) tma_store_wait_read();        // the piece before has left the buffer
+                    __syncwarp();
 #pragma unroll
                     for (int k = 0; k < 8; ++k)
                         *reinterpret_cast<float4 *>(stage + lane * 128 + ((k ^ (lane & 7u)) << 4)) =
                             make_float4(o[32 * c + 4 * k] * inv, o[32 * c + 4 * k + 1] * inv, o[32 * c + 4 * k + 2] * inv,
                                         o[32 * c + 4 * k + 3] * inv);
+                    fence_proxy_async();                         // generic writes -> the TMA unit's reads
                     __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint32_t rr = 4 * i + sub, grow = wq * 32u + rr;
-                        const float4 v = *reinterpret_cast<const float4 *>(stage + rr * 128 + ((piece ^ (rr & 7u)) << 4));
-                        if (grow < me.rows)
-                            *reinterpret_cast<float4 *>(p.out + ((size_t)(me.tok0 + grow) * p.n_q + head) * kHd + 32 * c +
-                                                        4 * piece) = v;
-                    }
-                    __syncwarp();
+                    if (lane == 0 && wq * 32u < me.rows)         // (a piece wholly past the prompt is not issued)
+                        tma_store_2d(&o_map, stage, (int)(head * kHd + 32 * c), (int)(me.tok0 + wq * 32u));
                 }
             }
             TLST(5);                                             // output rows issued
         }
         if (!ok) atomicCAS(p.err, 0, 13);
+        if (lane == 0) tma_store_wait_read();                    // shared memory stays valid until the last piece is read
     }
 
     tc_fence_before();
@@ -1014,6 +1026,15 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return WR_CUDA_ERR_INTERNAL;
 
+    // output rows [n][n_q * 128] F32, written in pieces of 32 rows x 32 values
+    CUtensorMap o_map;
+    const cuuint64_t o_strides[1] = {(cuuint64_t)n_q_heads * kHd * 4};
+    const cuuint32_t o_box[2] = {32, 32};
+    if (encode(&o_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)dout, dims, o_strides, o_box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return WR_CUDA_ERR_INTERNAL;
+
     prefill_params p;
     p.pages = kv->d_pages + (size_t)layer * kv->n_pages;
     p.page_base = kv->contig[layer] ? (const char *)kv->pages[(size_t)layer * kv->n_pages] : nullptr;
@@ -1025,7 +1046,6 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
     WR_CUDA_TRY(cudaMemsetAsync(ctx->debug_buf, 0, (kTlRoles * kTlEvents + 4 * kTlCtas) * sizeof(long long), ctx->stream));
     p.tl = (long long *)ctx->debug_buf;
 #endif
-    p.out = dout;
     p.err = ctx->dev_err;
     p.sched = ctx->prefill_sched;
     p.wait_limit = ctx->wait_limit;
@@ -1052,7 +1072,7 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
     p.early = (!convert && !host && full && ctx->pdl_index == ctx->launches &&
                ctx->pdl_kind == WR_PDL_PREFILL_FULL) ? 1u : 0u;
     WR_CUDA_TRY(wr_launch_pdl(attn_prefill_hd128_kernel, dim3(grid), dim3(kThreads), sizeof(smem_layout), ctx->stream,
-                              q_map, p));
+                              q_map, o_map, p));
     ctx->launches++;
     ctx->pdl_kind = full ? WR_PDL_PREFILL_FULL : WR_PDL_NONE;
     ctx->pdl_index = ctx->launches;
