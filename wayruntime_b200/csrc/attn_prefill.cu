@@ -36,7 +36,9 @@
 //     here — and write P as F16 back into TMEM.  O stays in TMEM; it is rescaled
 //     only when the row maximum has grown by more than 2^8 (exact: the final
 //     division by l uses the same reference maximum), read once at the end,
-//     normalised, and written out row by row.
+//     normalised, and sent out in 32 x 32 pieces through a swizzled shared-memory
+//     buffer as TMA tensor stores (a store instruction whose lanes each write a
+//     row of their own touches 32 cache lines for 512 bytes).
 // Every wait has a time limit; on expiry the kernel records an error, still
 // frees its TMEM and returns.
 #include <cuda.h>
