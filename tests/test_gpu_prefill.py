@@ -193,3 +193,31 @@ def test_prefill_row_maximum_grows_for_some_rows_only(ctx):
     assert rc == 0
     assert np.isfinite(out).all()
     assert np.abs(out[rows] - want).max() <= TOL
+
+
+@pytest.mark.parametrize("n", [1, 33, 70, 128 + 31])
+def test_prefill_writes_every_row_of_the_prompt_and_nothing_after_it(ctx, n):
+    """The output leaves the kernel in pieces of 32 rows x 32 values; pieces that straddle the
+    prompt's last row are cut there and pieces wholly past it are not sent.  Device buffers:
+    rows [0, n) are all written, the rows behind them keep what they held."""
+    import torch
+    P = port()
+    hq, hkv, tail = 8, 2, 40
+    k16 = P.f32_to_f16(_gen.normal(901 + n, (n, hkv, 128)))
+    v16 = P.f32_to_f16(_gen.normal(902 + n, (n, hkv, 128)))
+    q16 = P.f32_to_f16(_gen.normal(903 + n, (n, hq, 128)))
+    kv = make_cache(ctx, k16, v16, max_ctx=n + 70)
+    q = torch.from_numpy(q16.view(np.int16)).cuda().view(torch.float16)
+    buf = torch.full((n + tail, hq, 128), float("nan"), device="cuda")
+    buf[n:] = 7.0
+    torch.cuda.synchronize()
+    ctx.attn_prefill(kv, 0, 0, n, q, buf[:n], hq)
+    ctx.sync()
+    got = buf.cpu().numpy()
+    kv.close()
+    assert np.isfinite(got[:n]).all()
+    assert (got[n:] == 7.0).all()
+    rows = np.arange(n, dtype=np.uint32)
+    rc, want = P.causal_prefill_rows(q16, k16, v16, rows, p0=0, threads=8, max_seq=32768)
+    assert rc == 0
+    assert np.abs(got[:n] - want).max() <= TOL
