@@ -36,8 +36,8 @@
 //     here — and write P as F16 back into TMEM.  O stays in TMEM; it is rescaled
 //     only when the row maximum has grown by more than 2^8 (exact: the final
 //     division by l uses the same reference maximum), read once at the end,
-//     normalised, and sent out in 32 x 32 pieces through a swizzled shared-memory
-//     buffer as TMA tensor stores (a store instruction whose lanes each write a
+//     normalised, and sent out in pieces of 32 rows x 16 values through two swizzled
+//     shared-memory buffers as TMA tensor stores (a store instruction whose lanes each write a
 //     row of their own touches 32 cache lines for 512 bytes).
 // Every wait has a time limit; on expiry the kernel records an error, still
 // frees its TMEM and returns.
@@ -135,9 +135,9 @@ struct smem_layout {
     uint64_t tile_ready[kTileSlots];
     tile_info tile[kTileSlots];
     uint32_t tmem_base;
-    // per softmax warp: 32 rows x 32 output values on their way out (16-byte pieces swizzled by row:
-    // the 128-byte swizzle of the output tensor map)
-    alignas(1024) uint8_t out_stage[8][32 * 128];
+    // per softmax warp: two buffers of 32 rows x 16 output values on their way out (16-byte pieces
+    // swizzled by row pair: the 64-byte swizzle of the output tensor map)
+    alignas(1024) uint8_t out_stage[8][2][32 * 64];
 };
 static_assert(sizeof(smem_layout) <= 232448, "the CTA's shared memory is 227 KB at most");
 
@@ -318,10 +318,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void 
                  : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-// The issuing thread's earlier bulk stores have finished reading shared memory.
+// The issuing thread's bulk stores, except the N latest, have finished reading shared memory.
+template <int N>
 __device__ __forceinline__ void tma_store_wait_read()
 {
-    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
 // ---- work tiles -------------------------------------------------------------
@@ -880,32 +881,32 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             // A thread holds one row, and a store instruction in which every lane writes to a row of
             // its own touches 32 cache lines for 512 bytes (measured: 6500 clk to get a tile's 128 KB
             // out, with every shared-memory access of the CTA queued behind it).  So the warp puts
-            // its 32 x 32 pieces into shared memory, swizzled, and the TMA unit writes them out as
-            // whole lines (rows past the prompt are outside the tensor and dropped).  A piece is
-            // waited for only when its buffer is needed again.
+            // pieces of 32 rows x 16 values into shared memory, swizzled, and the TMA unit writes them
+            // out as whole sectors (rows past the prompt are outside the tensor and dropped).  Two
+            // buffers take turns: a piece is waited for only when its buffer is needed again.
             pdl_wait();                                      // output rows: after the earlier kernels have ended
             {
                 const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-                uint8_t *stage = sm.out_stage[warp];
+                const bool send = (lane == 0) && (wq * 32u < me.rows);   // (a piece wholly past the prompt is not sent)
 #pragma unroll
-                for (int c = 0; c < kHd / 32; ++c) {
-                    if (lane == 0) tma_store_wait_read();        // the piece before has left the buffer
+                for (int c = 0; c < kHd / 16; ++c) {
+                    uint8_t *stage = sm.out_stage[warp][c & 1];
+                    if (lane == 0) tma_store_wait_read<1>();     // the piece before the last has left this buffer
                     __syncwarp();
 #pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        *reinterpret_cast<float4 *>(stage + lane * 128 + ((k ^ (lane & 7u)) << 4)) =
-                            make_float4(o[32 * c + 4 * k] * inv, o[32 * c + 4 * k + 1] * inv, o[32 * c + 4 * k + 2] * inv,
-                                        o[32 * c + 4 * k + 3] * inv);
+                    for (int k = 0; k < 4; ++k)
+                        *reinterpret_cast<float4 *>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3u)) << 4)) =
+                            make_float4(o[16 * c + 4 * k] * inv, o[16 * c + 4 * k + 1] * inv, o[16 * c + 4 * k + 2] * inv,
+                                        o[16 * c + 4 * k + 3] * inv);
                     fence_proxy_async();                         // generic writes -> the TMA unit's reads
                     __syncwarp();
-                    if (lane == 0 && wq * 32u < me.rows)         // (a piece wholly past the prompt is not issued)
-                        tma_store_2d(&o_map, stage, (int)(head * kHd + 32 * c), (int)(me.tok0 + wq * 32u));
+                    if (send) tma_store_2d(&o_map, stage, (int)(head * kHd + 16 * c), (int)(me.tok0 + wq * 32u));
                 }
             }
             TLST(5);                                             // output rows issued
         }
         if (!ok) atomicCAS(p.err, 0, 13);
-        if (lane == 0) tma_store_wait_read();                    // shared memory stays valid until the last piece is read
+        if (lane == 0) tma_store_wait_read<0>();                 // shared memory stays valid until the last piece is read
     }
 
     tc_fence_before();
@@ -1028,12 +1029,12 @@ extern "C" int wr_cuda_attn_prefill(wr_cuda_ctx *ctx, wr_cuda_kv *kv, uint32_t l
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return WR_CUDA_ERR_INTERNAL;
 
-    // output rows [n][n_q * 128] F32, written in pieces of 32 rows x 32 values
+    // output rows [n][n_q * 128] F32, written in pieces of 32 rows x 16 values
     CUtensorMap o_map;
     const cuuint64_t o_strides[1] = {(cuuint64_t)n_q_heads * kHd * 4};
-    const cuuint32_t o_box[2] = {32, 32};
+    const cuuint32_t o_box[2] = {16, 32};
     if (encode(&o_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)dout, dims, o_strides, o_box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return WR_CUDA_ERR_INTERNAL;
 
