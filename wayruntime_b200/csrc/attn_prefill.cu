@@ -125,7 +125,7 @@ struct smem_layout {
     alignas(1024) uint8_t k[kStages][kKVTile];           // [64-dim half][128 keys][128 B]
     alignas(1024) uint8_t v[kStages][kKVTile];           // [page][64-dim half][64 keys][128 B]
     alignas(8) uint64_t q_full[2];                       // per block
-    uint64_t q_free;
+    uint64_t q_free[2];                                  // per block: its last scores of the tile have completed
     uint64_t k_full[kStages], k_free[kStages];
     uint64_t v_full[kStages], v_free[kStages];
     uint64_t s_full[2];                                  // per block: scores are in TMEM
@@ -411,7 +411,8 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
     if (warp == 8 && lane == 0) {
         mbar_init(&sm.q_full[0], 1);
         mbar_init(&sm.q_full[1], 1);
-        mbar_init(&sm.q_free, 1);
+        mbar_init(&sm.q_free[0], 1);
+        mbar_init(&sm.q_free[1], 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sm.k_full[i], 1);
             mbar_init(&sm.k_free[i], 1);
@@ -480,19 +481,21 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
         // again long before its V tile is, so the two rings run independently).
         if (lane == 0) {
             uint32_t kcount = 0;
+            uint32_t q_loads[2] = {0, 0};                        // Q blocks requested per buffer
             tile_info ti = decode_tile(p, blockIdx.x);
             bool ok = true;
             for (uint32_t it = 0; ok && ti.valid; ++it) {
-                if (it > 0) {                                    // the previous tile's scores have all been issued
-                    ok = mbar_wait(&sm.q_free, (it - 1) & 1, limit);
-                    if (!ok) break;
-                }
                 const block_range r0 = range_of(p, ti.qt[0]), r1 = range_of(p, ti.qt[ti.nblk - 1]);
                 const uint32_t lo = min(r0.lo, r1.lo), hi = max(r0.hi, r1.hi);
-                auto load_q = [&](uint32_t b, uint32_t head, uint32_t qt) {
+                // (a block's buffer is free again when the block's last scores of the tile before have
+                // completed — block 0's come half a step before block 1's)
+                auto load_q = [&](uint32_t b, uint32_t head, uint32_t qt) -> bool {
+                    if (q_loads[b] > 0 && !mbar_wait(&sm.q_free[b], (q_loads[b] - 1) & 1, limit)) return false;
+                    ++q_loads[b];
                     mbar_expect_tx(&sm.q_full[b], kQBytes);
                     tma_load_2d(sm.q[b], &q_map, (int)(head * kHd), (int)(qt * kBM), &sm.q_full[b]);
                     tma_load_2d(sm.q[b] + kQHalfBytes, &q_map, (int)(head * kHd + 64), (int)(qt * kBM), &sm.q_full[b]);
+                    return true;
                 };
                 auto load_k = [&](uint32_t j) -> bool {
                     const uint32_t st = kcount % kStages;
@@ -511,11 +514,13 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 // what the first scores need goes first: Q of block 0, the first K tile, Q of block 1
                 // (the CTA's first tile had these issued before the CTA-wide barrier)
                 if (it > 0) {
-                    load_q(0, ti.head[0], ti.qt[0]);
-                    ok = load_k(lo);
-                    if (ti.nblk > 1) load_q(1, ti.head[1], ti.qt[1]);
+                    ok = load_q(0, ti.head[0], ti.qt[0]);
+                    ok = ok && load_k(lo);
+                    if (ti.nblk > 1) ok = ok && load_q(1, ti.head[1], ti.qt[1]);
                 } else {
                     kcount = 1;
+                    q_loads[0] = 1;
+                    q_loads[1] = ti.nblk > 1 ? 1u : 0u;
                 }
                 // The next tile is claimed late — when this tile's last K tile is being
                 // requested, a step or two before its end — so that the tiles still unclaimed
@@ -640,16 +645,15 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
             if (!ok) break;
             tc_fence_after();
             if (lo >= rg0.lo && lo < rg0.hi) issue_s(0, k_st);
+            if (lead && rg0.hi == lo + 1) umma_commit(&sm.q_free[0]);        // block 0's Q is no longer read
             if (two) {
                 ok = mbar_wait(&sm.q_full[1], (q_uses1++) & 1, limit);
                 if (!ok) break;
                 tc_fence_after();
                 if (lo >= lo1 && lo < hi1) issue_s(1, k_st);
+                if (lead && hi1 == lo + 1) umma_commit(&sm.q_free[1]);
             }
-            if (lead) {
-                umma_commit(&sm.k_free[k_st]);
-                if (lo + 1 == hi) umma_commit(&sm.q_free);       // Q is no longer read
-            }
+            if (lead) umma_commit(&sm.k_free[k_st]);
             if (++k_st == kStages) { k_st = 0; k_par ^= 1; }
             if (lane == 0) TLT(4, 2);                            // first scores issued
             for (uint32_t j = lo; j < hi && ok; ++j) {
@@ -679,7 +683,10 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                             ++o_uses;
                         }
                     }
-                    if (more && j + 1 >= blo && j + 1 < bhi) issue_s(b, k_st);      // (P_b of step j was consumed just above)
+                    if (more && j + 1 >= blo && j + 1 < bhi) {
+                        issue_s(b, k_st);                        // (P_b of step j was consumed just above)
+                        if (lead && j + 2 == bhi) umma_commit(&sm.q_free[b]);       // the block's last scores
+                    }
                     if (lane == 0) TL(2);                        // P.V and next scores issued
                     return true;
                 };
@@ -688,10 +695,7 @@ attn_prefill_hd128_kernel(const __grid_constant__ CUtensorMap q_map, const __gri
                 if (!ok) break;
                 if (lead) {
                     umma_commit(&sm.v_free[v_st]);
-                    if (more) {
-                        umma_commit(&sm.k_free[k_st]);
-                        if (j + 2 == hi) umma_commit(&sm.q_free);
-                    }
+                    if (more) umma_commit(&sm.k_free[k_st]);
                 }
                 if (++v_st == kStages) { v_st = 0; v_par ^= 1; }
                 if (more && ++k_st == kStages) { k_st = 0; k_par ^= 1; }
